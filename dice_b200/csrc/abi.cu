@@ -1,0 +1,30 @@
+// Version / error-text entry points of the C ABI.
+#include "common.cuh"
+
+extern "C" int dice_abi_version(void) { return DICE_ABI_VERSION; }
+
+extern "C" const char* dice_strerror(int code) {
+  switch (code) {
+    case DICE_OK: return "ok";
+    case DICE_ERR_ARG: return "invalid argument (null pointer or negative size)";
+    case DICE_ERR_SHAPE: return "unsupported shape or divisibility";
+    case DICE_ERR_DTYPE: return "unsupported element type";
+    case DICE_ERR_ALIGN: return "pointer is not 16-byte aligned";
+    case DICE_ERR_SCRATCH: return "scratch buffer too small";
+    case DICE_ERR_CUDA: return "a CUDA call failed";
+    case DICE_ERR_LIMIT: return "size exceeds a documented maximum";
+    default: return "unknown dice_b200 error code";
+  }
+}
+
+extern "C" const char* dice_status_message(uint32_t status) {
+  switch (status) {
+    case DICE_STATUS_OK: return "ok";
+    case DICE_STATUS_WAIT_SMEM_FULL: return "timed out waiting for operand tiles to arrive in shared memory";
+    case DICE_STATUS_WAIT_SMEM_EMPTY: return "timed out waiting for a shared-memory ring slot to be released";
+    case DICE_STATUS_WAIT_ACC_FULL: return "timed out waiting for an accumulator to complete";
+    case DICE_STATUS_WAIT_ACC_EMPTY: return "timed out waiting for an accumulator to be drained";
+    case DICE_STATUS_BAD_SEGMENTS: return "segment offsets are not monotone or exceed the row count";
+    default: return "unknown device status";
+  }
+}

@@ -1,0 +1,53 @@
+// Shared helpers for the dice_b200 kernels (sm_100a only).
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/dice_b200.h"
+
+#define DICE_CHECK_ARG(cond, code) \
+  do {                             \
+    if (!(cond)) return (code);    \
+  } while (0)
+
+#define DICE_CUDA_OK(expr)                         \
+  do {                                             \
+    if ((expr) != cudaSuccess) return DICE_ERR_CUDA; \
+  } while (0)
+
+// device status codes written by kernels whose bounded waits expired
+#define DICE_STATUS_OK 0u
+#define DICE_STATUS_WAIT_SMEM_FULL 1u   // tensor-core warp: operand tiles never arrived
+#define DICE_STATUS_WAIT_SMEM_EMPTY 2u  // loader warp: ring slot never released
+#define DICE_STATUS_WAIT_ACC_FULL 3u    // epilogue warps: accumulator never completed
+#define DICE_STATUS_WAIT_ACC_EMPTY 4u   // tensor-core warp: accumulator never drained
+#define DICE_STATUS_BAD_SEGMENTS 5u     // segment offsets not monotone / beyond n_rows
+
+static inline bool dice_aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+static inline size_t dice_dtype_size(int dtype) {
+  return dtype == DICE_BF16 ? 2 : (dtype == DICE_F32 ? 4 : 0);
+}
+
+__device__ __forceinline__ uint4 ldg_stream16(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+
+__device__ __forceinline__ void stg_stream16(void* p, const uint4& v) {
+  asm volatile("st.global.L1::no_allocate.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y),
+               "r"(v.z), "r"(v.w)
+               : "memory");
+}
+
+__device__ __forceinline__ float bf16lo_to_f32(uint32_t packed) { return __uint_as_float(packed << 16); }
+__device__ __forceinline__ float bf16hi_to_f32(uint32_t packed) { return __uint_as_float(packed & 0xffff0000u); }
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}

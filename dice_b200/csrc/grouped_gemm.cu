@@ -1,0 +1,513 @@
+// Grouped (per-expert-segment) GEMM on the sm_100a tensor cores.
+//
+//   out[r, :] = epilogue( a[r, :] * w[slab(segment(r))]^T )
+//
+// A persistent, warp-specialised kernel, one CTA per SM:
+//   warp 0      loader: one lane issues TMA tile loads (128B-swizzled, K-major)
+//               into a 4-deep shared-memory ring;
+//   warp 1      tensor-core warp: allocates tensor memory, one lane issues
+//               tcgen05.mma (128 x N x 16, bf16 in, fp32 accumulate in tensor
+//               memory) and commits ring slots / accumulators to mbarriers;
+//   warps 2..5  epilogue: tcgen05.ld the accumulator (one 32-lane quadrant
+//               each), apply the activation in fp32, store bf16 rows.
+// Two 256-column accumulators alternate, so the epilogue of tile i overlaps
+// the main loop of tile i+1.
+//
+// Raggedness: segments start at arbitrary rows.  The tile list is derived on
+// the device from the segment offsets (no host synchronisation): m-blocks are
+// counted per segment, a tile's rows start at seg_start + 128*j, the loads may
+// run past the segment end (into the next segment or the zero-filled region
+// past the last row) and the epilogue stores only the rows that belong to the
+// segment.
+//
+// Every mbarrier wait is bounded by wall time; when one expires the kernel
+// records a status code, all roles leave their loops, tensor memory is freed
+// and the kernel returns.
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int BM = 128;          // rows per tile (tensor-memory lanes)
+constexpr int BN = 256;          // weight rows per tile (accumulator columns)
+constexpr int BK = 64;           // reduction elements per ring slot (128 bytes of bf16)
+constexpr int UMMA_K = 16;       // reduction elements per tcgen05.mma
+constexpr int kStages = 4;
+constexpr int kAccStages = 2;
+constexpr int kTileABytes = BM * BK * 2;
+constexpr int kTileBBytes = BN * BK * 2;
+constexpr int kStageBytes = kTileABytes + kTileBBytes;
+constexpr int kThreads = 192;
+constexpr int kEpilogueWarps = 4;
+constexpr int kMaxSeg = 256;
+constexpr int kTmemCols = 512;
+constexpr uint64_t kWaitLimitNs = 1000ull * 1000ull * 1000ull;  // 1 s per wait
+constexpr int kAuxBytes = 4096;  // barriers, flags and the segment tables
+constexpr int kSmemBytes = kStages * kStageBytes + kAuxBytes + 1024;  // +1024: manual alignment
+
+struct GemmParams {
+  const int* seg_offsets;
+  const int* seg_slab;
+  int n_seg;
+  int n_rows;
+  int n_kblk;      // ceil(k_dim / BK)
+  int n_nblk;      // ceil(w_rows / BN)
+  int w_rows;      // weight rows per slab
+  int n_out;       // logical output columns
+  int epilogue;
+  __nv_bfloat16* out;
+  int64_t ld_out;
+  uint32_t* status;
+};
+
+// ---- PTX wrappers ---------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ uint64_t global_timer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+// Wait for `parity` of `bar`; give up after kWaitLimitNs or when another role
+// has already given up.  Returns false when the caller must leave its loop.
+__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag,
+                                            uint32_t* status, uint32_t code) {
+  const uint64_t t0 = global_timer_ns();
+  uint32_t spins = 0;
+  for (;;) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((++spins & 127u) == 0) {
+      if (*abort_flag != 0) return false;
+      if (global_timer_ns() - t0 > kWaitLimitNs) {
+        if (status != nullptr) atomicCAS(status, 0u, code);
+        *abort_flag = 1;
+        __threadfence_block();
+        return false;
+      }
+    }
+  }
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag,
+                                          uint32_t* status, uint32_t code) {
+  if (mbar_try_wait(bar, parity)) return true;
+  return mbar_wait_slow(bar, parity, abort_flag, status, code);
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(bar)
+      : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after_sync() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_alloc(uint32_t slot_smem_addr, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot_smem_addr), "r"(cols) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+
+// Shared-memory operand descriptor: K-major tile of 128-byte rows written by
+// TMA with the 128-byte swizzle; 8-row groups are 1024 bytes apart.
+__device__ __forceinline__ uint64_t make_operand_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);  // start address / 16
+  d |= static_cast<uint64_t>(1) << 16;                        // leading byte offset (unused with swizzle)
+  d |= static_cast<uint64_t>(1024 >> 4) << 32;                // stride byte offset: 8 rows * 128 B
+  d |= static_cast<uint64_t>(1) << 46;                        // descriptor version (sm_100)
+  d |= static_cast<uint64_t>(2) << 61;                        // 128-byte swizzle
+  return d;
+}
+
+// Instruction descriptor: bf16 x bf16 -> fp32, both operands K-major.
+__device__ __forceinline__ uint32_t make_instr_desc(int m, int n) {
+  uint32_t d = 0;
+  d |= 1u << 4;                              // accumulator format: fp32
+  d |= 1u << 7;                              // A format: bf16
+  d |= 1u << 10;                             // B format: bf16
+  d |= static_cast<uint32_t>(n >> 3) << 17;  // N / 8
+  d |= static_cast<uint32_t>(m >> 4) << 24;  // M / 16
+  return d;
+}
+
+__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+__device__ __forceinline__ float gelu_tanh_f(float x) {
+  const float u = 0.7978845608028654f * fmaf(0.044715f * x * x, x, x);
+  float t;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(u));
+  return 0.5f * x * (1.0f + t);
+}
+__device__ __forceinline__ float silu_f(float x) { return __fdividef(x, 1.0f + __expf(-x)); }
+
+// Store 32 consecutive output columns of one row; columns at or beyond
+// `n_valid` (relative to the first of the 32) are dropped in groups of 8.
+__device__ __forceinline__ void store_row_chunk(__nv_bfloat16* dst, const float (&v)[32], int n_valid, bool row_ok) {
+  if (!row_ok) return;
+#pragma unroll
+  for (int g = 0; g < 4; ++g) {
+    if (g * 8 < n_valid) {
+      uint4 o = make_uint4(pack_bf16x2(v[g * 8 + 0], v[g * 8 + 1]), pack_bf16x2(v[g * 8 + 2], v[g * 8 + 3]),
+                           pack_bf16x2(v[g * 8 + 4], v[g * 8 + 5]), pack_bf16x2(v[g * 8 + 6], v[g * 8 + 7]));
+      *reinterpret_cast<uint4*>(dst + g * 8) = o;
+    }
+  }
+}
+
+// ---- the kernel -------------------------------------------------------------------
+__global__ void __launch_bounds__(kThreads, 1)
+grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+                    const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* aux = smem + kStages * kStageBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(aux);
+  const uint32_t full_bar = smem_u32(bars);                       // [kStages]
+  const uint32_t empty_bar = smem_u32(bars + kStages);            // [kStages]
+  const uint32_t acc_full_bar = smem_u32(bars + 2 * kStages);     // [kAccStages]
+  const uint32_t acc_empty_bar = smem_u32(bars + 2 * kStages + kAccStages);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 2 * kAccStages);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+  int* s_seg_off = reinterpret_cast<int*>(tmem_slot + 4);         // [n_seg + 1]
+  int* s_mprefix = s_seg_off + (kMaxSeg + 1);                     // [n_seg + 1] m-blocks before segment s
+  const uint32_t tiles_smem = smem_u32(smem);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  for (int i = threadIdx.x; i <= p.n_seg; i += kThreads) s_seg_off[i] = p.seg_offsets[i];
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(full_bar + 8 * s, 1);
+      mbar_init(empty_bar + 8 * s, 1);
+    }
+    for (int a = 0; a < kAccStages; ++a) {
+      mbar_init(acc_full_bar + 8 * a, 1);
+      mbar_init(acc_empty_bar + 8 * a, kEpilogueWarps);
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int run = 0;
+    bool ok = s_seg_off[0] >= 0;
+    for (int s = 0; s < p.n_seg; ++s) {
+      const int cnt = s_seg_off[s + 1] - s_seg_off[s];
+      ok = ok && cnt >= 0;
+      s_mprefix[s] = run;
+      run += cnt > 0 ? (cnt + BM - 1) / BM : 0;
+    }
+    ok = ok && s_seg_off[p.n_seg] <= p.n_rows;
+    if (!ok) {
+      run = 0;
+      if (p.status != nullptr) atomicCAS(p.status, 0u, DICE_STATUS_BAD_SEGMENTS);
+    }
+    s_mprefix[p.n_seg] = run;
+  }
+  if (warp == 1) tmem_alloc(smem_u32(tmem_slot), kTmemCols);
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+
+  const uint32_t tmem_base = *tmem_slot;
+  const int total_mblk = s_mprefix[p.n_seg];
+  const int64_t total_tiles = static_cast<int64_t>(total_mblk) * p.n_nblk;
+
+  if (warp == 0) {
+    // ---------------- loader ----------------
+    if (lane == 0) {
+      int stage = 0, seg = 0;
+      uint32_t phase = 0;
+      bool alive = true;
+      for (int64_t t = blockIdx.x; alive && t < total_tiles; t += gridDim.x) {
+        const int mb = static_cast<int>(t / p.n_nblk);
+        const int nb = static_cast<int>(t - static_cast<int64_t>(mb) * p.n_nblk);
+        while (mb >= s_mprefix[seg + 1]) ++seg;
+        const int row0 = s_seg_off[seg] + (mb - s_mprefix[seg]) * BM;
+        const int slab = p.seg_slab != nullptr ? p.seg_slab[seg] : seg;
+        const int wrow0 = slab * p.w_rows + nb * BN;
+        for (int kb = 0; kb < p.n_kblk; ++kb) {
+          if (!mbar_wait(empty_bar + 8 * stage, phase ^ 1u, abort_flag, p.status, DICE_STATUS_WAIT_SMEM_EMPTY)) {
+            alive = false;
+            break;
+          }
+          const uint32_t a_dst = tiles_smem + stage * kStageBytes;
+          mbar_expect_tx(full_bar + 8 * stage, kStageBytes);
+          tma_load_2d(a_dst, &tm_a, kb * BK, row0, full_bar + 8 * stage);
+          tma_load_2d(a_dst + kTileABytes, &tm_b, kb * BK, wrow0, full_bar + 8 * stage);
+          if (++stage == kStages) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- tensor-core issue ----------------
+    if (lane == 0) {
+      int stage = 0, acc = 0;
+      uint32_t phase = 0, acc_phase = 0;
+      bool alive = true;
+      for (int64_t t = blockIdx.x; alive && t < total_tiles; t += gridDim.x) {
+        const int nb = static_cast<int>(t % p.n_nblk);
+        int n_valid = p.w_rows - nb * BN;
+        if (n_valid > BN) n_valid = BN;
+        const uint32_t idesc = make_instr_desc(BM, (n_valid + 15) & ~15);
+        if (!mbar_wait(acc_empty_bar + 8 * acc, acc_phase ^ 1u, abort_flag, p.status, DICE_STATUS_WAIT_ACC_EMPTY)) break;
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
+        for (int kb = 0; kb < p.n_kblk; ++kb) {
+          if (!mbar_wait(full_bar + 8 * stage, phase, abort_flag, p.status, DICE_STATUS_WAIT_SMEM_FULL)) {
+            alive = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t a_addr = tiles_smem + stage * kStageBytes;
+          const uint64_t a_desc = make_operand_desc(a_addr);
+          const uint64_t b_desc = make_operand_desc(a_addr + kTileABytes);
+#pragma unroll
+          for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+            // advance both operands by 16 elements (32 bytes) along K inside the swizzled row
+            umma_bf16(d_tmem, a_desc + static_cast<uint64_t>(kk * 2), b_desc + static_cast<uint64_t>(kk * 2), idesc,
+                      static_cast<uint32_t>((kb | kk) != 0));
+          }
+          umma_commit(empty_bar + 8 * stage);  // slot reusable once these MMAs have read it
+          if (++stage == kStages) { stage = 0; phase ^= 1u; }
+        }
+        if (!alive) break;
+        umma_commit(acc_full_bar + 8 * acc);   // accumulator complete
+        if (++acc == kAccStages) { acc = 0; acc_phase ^= 1u; }
+      }
+    }
+  } else {
+    // ---------------- epilogue ----------------
+    const int quad = warp & 3;  // tensor-memory lanes [32*quad, 32*quad+32) belong to this warp
+    int acc = 0, seg = 0;
+    uint32_t acc_phase = 0;
+    for (int64_t t = blockIdx.x; t < total_tiles; t += gridDim.x) {
+      const int mb = static_cast<int>(t / p.n_nblk);
+      const int nb = static_cast<int>(t - static_cast<int64_t>(mb) * p.n_nblk);
+      while (mb >= s_mprefix[seg + 1]) ++seg;
+      const int row0 = s_seg_off[seg] + (mb - s_mprefix[seg]) * BM;
+      const int rows_valid = s_seg_off[seg + 1] - row0;  // may exceed BM
+      if (!mbar_wait(acc_full_bar + 8 * acc, acc_phase, abort_flag, p.status, DICE_STATUS_WAIT_ACC_FULL)) break;
+      tc_fence_after_sync();
+      const int r = quad * 32 + lane;
+      const bool row_ok = r < rows_valid;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + static_cast<uint32_t>(acc * BN);
+      __nv_bfloat16* out_row = p.out + static_cast<int64_t>(row0 + r) * p.ld_out;
+      if (p.epilogue == DICE_EPI_SWIGLU) {
+        const int col0 = nb * (BN / 2);
+        int n_valid = p.n_out - col0;
+        if (n_valid > BN / 2) n_valid = BN / 2;
+        for (int c = 0; c < n_valid; c += 32) {
+          uint32_t g[32], u[32];
+          tmem_ld32(taddr + c, g);
+          tmem_ld32(taddr + BN / 2 + c, u);
+          tmem_ld_wait();
+          float v[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = silu_f(__uint_as_float(g[j])) * __uint_as_float(u[j]);
+          store_row_chunk(out_row + col0 + c, v, n_valid - c, row_ok);
+        }
+      } else {
+        const int col0 = nb * BN;
+        int n_valid = p.n_out - col0;
+        if (n_valid > BN) n_valid = BN;
+        const bool gelu = p.epilogue == DICE_EPI_GELU_TANH;
+        for (int c = 0; c < n_valid; c += 32) {
+          uint32_t a[32];
+          tmem_ld32(taddr + c, a);
+          tmem_ld_wait();
+          float v[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const float f = __uint_as_float(a[j]);
+            v[j] = gelu ? gelu_tanh_f(f) : f;
+          }
+          store_row_chunk(out_row + col0 + c, v, n_valid - c, row_ok);
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(acc_empty_bar + 8 * acc);
+      if (++acc == kAccStages) { acc = 0; acc_phase ^= 1u; }
+    }
+  }
+
+  // ---------------- teardown ----------------
+  tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag != 0) {
+    // a wait expired: give copies and MMAs still in flight time to land before the CTA's
+    // shared and tensor memory are released
+    const uint64_t t0 = global_timer_ns();
+    while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ---- host side ----------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) != cudaSuccess ||
+        qres != cudaDriverEntryPointSuccess)
+      return nullptr;
+    fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
+// 2-D bf16 tensor [rows, cols] row-major, box = [box_rows, 64 columns], 128-byte swizzle.
+int encode_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (fn == nullptr) return DICE_ERR_CUDA;
+  const cuuint64_t dims[2] = {cols, rows};
+  const cuuint64_t strides[1] = {cols * 2};
+  const cuuint32_t box[2] = {BK, box_rows};
+  const cuuint32_t elem_strides[2] = {1, 1};
+  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box,
+                        elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? DICE_OK : DICE_ERR_CUDA;
+}
+
+int sm_count() {
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
+    if (cudaFuncSetAttribute(grouped_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) !=
+        cudaSuccess)
+      return 0;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
+}  // namespace
+
+extern "C" int dice_grouped_gemm(const void* a, int64_t n_rows, int k_dim, const void* w, int n_slabs, int64_t w_rows,
+                                 const int32_t* seg_offsets, const int32_t* seg_slab, int n_seg, int epilogue,
+                                 void* out, int64_t ld_out, int n_out, uint32_t* status, void* stream) {
+  DICE_CHECK_ARG(n_rows >= 0 && k_dim > 0 && n_slabs > 0 && w_rows > 0 && n_seg >= 0, DICE_ERR_ARG);
+  DICE_CHECK_ARG(n_seg <= kMaxSeg, DICE_ERR_LIMIT);
+  DICE_CHECK_ARG(epilogue == DICE_EPI_STORE || epilogue == DICE_EPI_GELU_TANH || epilogue == DICE_EPI_SWIGLU,
+                 DICE_ERR_ARG);
+  DICE_CHECK_ARG(k_dim % 8 == 0 && ld_out % 8 == 0 && n_out % 8 == 0 && n_out > 0 && n_out <= ld_out, DICE_ERR_SHAPE);
+  if (epilogue == DICE_EPI_SWIGLU)
+    DICE_CHECK_ARG(w_rows % 256 == 0 && static_cast<int64_t>(n_out) <= w_rows / 2, DICE_ERR_SHAPE);
+  else
+    DICE_CHECK_ARG(static_cast<int64_t>(n_out) <= w_rows, DICE_ERR_SHAPE);
+  DICE_CHECK_ARG(n_rows < 0x7fffff00LL && static_cast<int64_t>(n_slabs) * w_rows < 0x7fffff00LL, DICE_ERR_LIMIT);
+  if (n_rows == 0 || n_seg == 0) return DICE_OK;
+  DICE_CHECK_ARG(a && w && seg_offsets && out, DICE_ERR_ARG);
+  DICE_CHECK_ARG(dice_aligned16(a) && dice_aligned16(w) && dice_aligned16(out), DICE_ERR_ALIGN);
+
+  const int sms = sm_count();
+  if (sms <= 0) return DICE_ERR_CUDA;
+  CUtensorMap tm_a, tm_b;
+  int rc = encode_map(&tm_a, a, static_cast<uint64_t>(n_rows), static_cast<uint64_t>(k_dim), BM);
+  if (rc != DICE_OK) return rc;
+  rc = encode_map(&tm_b, w, static_cast<uint64_t>(n_slabs) * static_cast<uint64_t>(w_rows),
+                  static_cast<uint64_t>(k_dim), BN);
+  if (rc != DICE_OK) return rc;
+
+  GemmParams p;
+  p.seg_offsets = seg_offsets;
+  p.seg_slab = seg_slab;
+  p.n_seg = n_seg;
+  p.n_rows = static_cast<int>(n_rows);
+  p.n_kblk = (k_dim + BK - 1) / BK;
+  p.n_nblk = static_cast<int>((w_rows + BN - 1) / BN);
+  p.w_rows = static_cast<int>(w_rows);
+  p.n_out = n_out;
+  p.epilogue = epilogue;
+  p.out = static_cast<__nv_bfloat16*>(out);
+  p.ld_out = ld_out;
+  p.status = status;
+
+  const int64_t max_tiles = ((n_rows + BM - 1) / BM + n_seg) * p.n_nblk;
+  const int grid = static_cast<int>(max_tiles < sms ? max_tiles : sms);
+  grouped_gemm_kernel<<<grid, kThreads, kSmemBytes, static_cast<cudaStream_t>(stream)>>>(tm_a, tm_b, p);
+  return cudaGetLastError() == cudaSuccess ? DICE_OK : DICE_ERR_CUDA;
+}
+
+extern "C" int dice_grouped_ffn(const void* rows_in, int64_t n_rows, int hidden, int ffn, int act, const void* w1,
+                                const void* w2, int n_slabs, const int32_t* seg_offsets, const int32_t* seg_slab,
+                                int n_seg, void* inter, void* rows_out, uint32_t* status, void* stream) {
+  DICE_CHECK_ARG(act == DICE_ACT_SWIGLU || act == DICE_ACT_GELU_TANH, DICE_ERR_ARG);
+  DICE_CHECK_ARG(hidden > 0 && ffn > 0, DICE_ERR_ARG);
+  if (n_rows > 0 && n_seg > 0) DICE_CHECK_ARG(inter != nullptr, DICE_ERR_ARG);
+  int rc;
+  if (act == DICE_ACT_SWIGLU)
+    rc = dice_grouped_gemm(rows_in, n_rows, hidden, w1, n_slabs, dice_w13_rows(ffn), seg_offsets, seg_slab, n_seg,
+                           DICE_EPI_SWIGLU, inter, ffn, ffn, status, stream);
+  else
+    rc = dice_grouped_gemm(rows_in, n_rows, hidden, w1, n_slabs, ffn, seg_offsets, seg_slab, n_seg, DICE_EPI_GELU_TANH,
+                           inter, ffn, ffn, status, stream);
+  if (rc != DICE_OK) return rc;
+  return dice_grouped_gemm(inter, n_rows, ffn, w2, n_slabs, hidden, seg_offsets, seg_slab, n_seg, DICE_EPI_STORE,
+                           rows_out, hidden, hidden, status, stream);
+}

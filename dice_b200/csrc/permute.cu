@@ -1,0 +1,296 @@
+// Token permutation for the MoE block: a stable counting sort of the
+// (token, slot) rows by expert, the 128-bit row gather into expert-sorted
+// order, and the inverse gather fused with the gate-weighted pair sum.
+//
+// The plan works on 4-byte indices only (a few hundred KB); the two row movers
+// read and write every activation byte exactly once and are bounded by HBM
+// bandwidth.
+#include "common.cuh"
+
+namespace {
+
+constexpr int kChunkRows = 256;  // rows ranked by one thread block
+constexpr int kMaxExperts = 64;
+
+// ---- plan, pass 1: per-chunk expert histogram -------------------------------
+__global__ void __launch_bounds__(kChunkRows)
+plan_count_kernel(const int64_t* __restrict__ flat_idx, int64_t n_rows, int n_experts, int* __restrict__ chunk_hist) {
+  __shared__ int s_hist[kMaxExperts];
+  if (threadIdx.x < kMaxExperts) s_hist[threadIdx.x] = 0;
+  __syncthreads();
+  const int64_t r = static_cast<int64_t>(blockIdx.x) * kChunkRows + threadIdx.x;
+  if (r < n_rows) {
+    const int64_t e = flat_idx[r];
+    if (e >= 0 && e < n_experts) atomicAdd(&s_hist[e], 1);
+  }
+  __syncthreads();
+  if (threadIdx.x < n_experts) chunk_hist[static_cast<int64_t>(blockIdx.x) * n_experts + threadIdx.x] = s_hist[threadIdx.x];
+}
+
+// ---- plan, pass 2: exclusive scan over chunks (per expert) and experts -------
+// chunk_hist[c][e] becomes the first sorted position of chunk c's rows of
+// expert e; seg_offsets[e] the first position of expert e.
+__global__ void __launch_bounds__(2 * kMaxExperts)
+plan_scan_kernel(int* __restrict__ chunk_hist, int n_chunks, int n_experts, int* __restrict__ seg_offsets) {
+  __shared__ int s_total[kMaxExperts];
+  __shared__ int s_base[kMaxExperts + 1];
+  const int e = threadIdx.x;
+  if (e < n_experts) {
+    int run = 0;
+    for (int c = 0; c < n_chunks; ++c) {
+      const int v = chunk_hist[static_cast<int64_t>(c) * n_experts + e];
+      chunk_hist[static_cast<int64_t>(c) * n_experts + e] = run;
+      run += v;
+    }
+    s_total[e] = run;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int run = 0;
+    for (int i = 0; i < n_experts; ++i) { s_base[i] = run; run += s_total[i]; }
+    s_base[n_experts] = run;
+  }
+  __syncthreads();
+  if (e <= n_experts) seg_offsets[e] = s_base[e];
+  if (e < n_experts) {
+    const int base = s_base[e];
+    for (int c = 0; c < n_chunks; ++c) chunk_hist[static_cast<int64_t>(c) * n_experts + e] += base;
+  }
+}
+
+// ---- plan, pass 3: stable rank of every row inside its chunk -----------------
+__global__ void __launch_bounds__(kChunkRows)
+plan_rank_kernel(const int64_t* __restrict__ flat_idx, int64_t n_rows, int n_experts,
+                 const int* __restrict__ chunk_base, int* __restrict__ pos, int* __restrict__ order) {
+  constexpr int kWarps = kChunkRows / 32;
+  __shared__ int s_warp_count[kWarps][kMaxExperts];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int i = threadIdx.x; i < kWarps * kMaxExperts; i += kChunkRows) (&s_warp_count[0][0])[i] = 0;
+  __syncthreads();
+  const int64_t r = static_cast<int64_t>(blockIdx.x) * kChunkRows + threadIdx.x;
+  int e = -1;
+  if (r < n_rows) {
+    const int64_t v = flat_idx[r];
+    if (v >= 0 && v < n_experts) e = static_cast<int>(v);
+  }
+  // lanes of this warp holding the same expert (rows are in lane order)
+  const unsigned peers = __match_any_sync(0xffffffffu, e);
+  const int rank_in_warp = __popc(peers & ((1u << lane) - 1u));
+  if (e >= 0 && rank_in_warp == 0) s_warp_count[warp][e] = __popc(peers);
+  __syncthreads();
+  if (e >= 0) {
+    int before = 0;
+    for (int w = 0; w < warp; ++w) before += s_warp_count[w][e];
+    const int p = chunk_base[static_cast<int64_t>(blockIdx.x) * n_experts + e] + before + rank_in_warp;
+    pos[r] = p;
+    if (order != nullptr) order[p] = static_cast<int>(r);
+  } else if (r < n_rows) {
+    pos[r] = -1;
+  }
+}
+
+// ---- row gather: out_rows[pos[t*k+s]] = x[t] ---------------------------------
+template <int K>
+__global__ void __launch_bounds__(256)
+permute_rows_kernel(const uint4* __restrict__ x, const int* __restrict__ pos, int64_t n_tokens, int row_vec,
+                    uint4* __restrict__ out) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t t = static_cast<int64_t>(blockIdx.x) * 8 + warp;
+  if (t >= n_tokens) return;
+  int64_t dst[K];
+#pragma unroll
+  for (int s = 0; s < K; ++s) dst[s] = static_cast<int64_t>(pos[t * K + s]) * row_vec;
+  const uint4* src = x + t * row_vec;
+#pragma unroll 4
+  for (int c = lane; c < row_vec; c += 32) {
+    const uint4 v = ldg_stream16(src + c);
+#pragma unroll
+    for (int s = 0; s < K; ++s)
+      if (dst[s] >= 0) stg_stream16(out + dst[s] + c, v);
+  }
+}
+
+// ---- inverse gather + weighted pair sum ---------------------------------------
+template <typename T>
+struct Vec16;
+template <>
+struct Vec16<__nv_bfloat16> {
+  static constexpr int kElems = 8;
+  __device__ static void to_float(const uint4& v, float* f) {
+    f[0] = bf16lo_to_f32(v.x); f[1] = bf16hi_to_f32(v.x); f[2] = bf16lo_to_f32(v.y); f[3] = bf16hi_to_f32(v.y);
+    f[4] = bf16lo_to_f32(v.z); f[5] = bf16hi_to_f32(v.z); f[6] = bf16lo_to_f32(v.w); f[7] = bf16hi_to_f32(v.w);
+  }
+  __device__ static uint4 from_float(const float* f) {
+    return make_uint4(pack_bf16x2(f[0], f[1]), pack_bf16x2(f[2], f[3]), pack_bf16x2(f[4], f[5]), pack_bf16x2(f[6], f[7]));
+  }
+};
+template <>
+struct Vec16<float> {
+  static constexpr int kElems = 4;
+  __device__ static void to_float(const uint4& v, float* f) {
+    f[0] = __uint_as_float(v.x); f[1] = __uint_as_float(v.y); f[2] = __uint_as_float(v.z); f[3] = __uint_as_float(v.w);
+  }
+  __device__ static uint4 from_float(const float* f) {
+    return make_uint4(__float_as_uint(f[0]), __float_as_uint(f[1]), __float_as_uint(f[2]), __float_as_uint(f[3]));
+  }
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+unpermute_combine_kernel(const uint4* __restrict__ src0, const int* __restrict__ idx0, int idx0_stride,
+                         const uint4* __restrict__ src1, const int* __restrict__ idx1, int idx1_stride,
+                         const float* __restrict__ w0, const float* __restrict__ w1, int w_stride,
+                         const uint4* __restrict__ addend, int64_t n_tokens, int row_vec, uint4* __restrict__ out) {
+  constexpr int EL = Vec16<T>::kElems;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t t = static_cast<int64_t>(blockIdx.x) * 8 + warp;
+  if (t >= n_tokens) return;
+  const int64_t i0 = idx0 ? static_cast<int64_t>(idx0[t * idx0_stride]) : t;
+  const int64_t i1 = src1 ? (idx1 ? static_cast<int64_t>(idx1[t * idx1_stride]) : t) : -1;
+  const float a0 = w0 ? w0[t * w_stride] : 1.f;
+  const float a1 = w1 ? w1[t * w_stride] : 1.f;
+  const uint4* p0 = (i0 >= 0) ? src0 + i0 * row_vec : nullptr;
+  const uint4* p1 = (i1 >= 0) ? src1 + i1 * row_vec : nullptr;
+  const uint4* pa = addend ? addend + t * row_vec : nullptr;
+  uint4* po = out + t * row_vec;
+#pragma unroll 2
+  for (int c = lane; c < row_vec; c += 32) {
+    float acc[EL];
+#pragma unroll
+    for (int j = 0; j < EL; ++j) acc[j] = 0.f;
+    if (p0) {
+      float f[EL];
+      Vec16<T>::to_float(ldg_stream16(p0 + c), f);
+#pragma unroll
+      for (int j = 0; j < EL; ++j) acc[j] = a0 * f[j];
+    }
+    if (p1) {
+      float f[EL];
+      Vec16<T>::to_float(ldg_stream16(p1 + c), f);
+#pragma unroll
+      for (int j = 0; j < EL; ++j) acc[j] = fmaf(a1, f[j], acc[j]);
+    }
+    if (pa) {
+      float f[EL];
+      Vec16<T>::to_float(ldg_stream16(pa + c), f);
+#pragma unroll
+      for (int j = 0; j < EL; ++j) acc[j] += f[j];
+    }
+    stg_stream16(po + c, Vec16<T>::from_float(acc));
+  }
+}
+
+// ---- SwiGLU weight packing ------------------------------------------------------
+__global__ void pack_w13_kernel(const uint4* __restrict__ gate, const uint4* __restrict__ up, int row_vec, int ffn,
+                                int64_t out_rows, uint4* __restrict__ out) {
+  const int64_t total = out_rows * row_vec;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t row = i / row_vec;
+    const int c = static_cast<int>(i - row * row_vec);
+    const int64_t blk = row / 256;
+    const int within = static_cast<int>(row - blk * 256);
+    const int64_t src_row = blk * 128 + (within & 127);
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (src_row < ffn) v = (within < 128 ? gate : up)[src_row * row_vec + c];
+    out[i] = v;
+  }
+}
+
+}  // namespace
+
+extern "C" size_t dice_permute_scratch_bytes(int64_t n_rows, int n_experts) {
+  if (n_rows < 0 || n_experts <= 0) return 0;
+  const int64_t chunks = (n_rows + kChunkRows - 1) / kChunkRows;
+  return static_cast<size_t>((chunks > 0 ? chunks : 1) * n_experts) * sizeof(int);
+}
+
+extern "C" int dice_permute_plan(const int64_t* flat_idx, int64_t n_rows, int n_experts, void* scratch,
+                                 size_t scratch_bytes, int32_t* out_pos, int32_t* out_order,
+                                 int32_t* out_seg_offsets, void* stream) {
+  DICE_CHECK_ARG(n_rows >= 0 && out_seg_offsets != nullptr, DICE_ERR_ARG);
+  DICE_CHECK_ARG(n_experts >= 1 && n_experts <= kMaxExperts, DICE_ERR_SHAPE);
+  DICE_CHECK_ARG(n_rows <= 0x7fffffffLL - kChunkRows, DICE_ERR_LIMIT);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (n_rows == 0) {
+    DICE_CUDA_OK(cudaMemsetAsync(out_seg_offsets, 0, sizeof(int32_t) * (n_experts + 1), s));
+    return DICE_OK;
+  }
+  DICE_CHECK_ARG(flat_idx && scratch && out_pos, DICE_ERR_ARG);
+  DICE_CHECK_ARG(scratch_bytes >= dice_permute_scratch_bytes(n_rows, n_experts), DICE_ERR_SCRATCH);
+  const int chunks = static_cast<int>((n_rows + kChunkRows - 1) / kChunkRows);
+  int* chunk_hist = static_cast<int*>(scratch);
+  plan_count_kernel<<<chunks, kChunkRows, 0, s>>>(flat_idx, n_rows, n_experts, chunk_hist);
+  plan_scan_kernel<<<1, 2 * kMaxExperts, 0, s>>>(chunk_hist, chunks, n_experts, out_seg_offsets);
+  plan_rank_kernel<<<chunks, kChunkRows, 0, s>>>(flat_idx, n_rows, n_experts, chunk_hist, out_pos, out_order);
+  return cudaGetLastError() == cudaSuccess ? DICE_OK : DICE_ERR_CUDA;
+}
+
+extern "C" int dice_permute_rows(const void* x, const int32_t* pos, int64_t n_tokens, int k, int hidden, int dtype,
+                                 void* out_rows, void* stream) {
+  DICE_CHECK_ARG(n_tokens >= 0 && hidden > 0, DICE_ERR_ARG);
+  DICE_CHECK_ARG(k == 1 || k == 2, DICE_ERR_SHAPE);
+  const size_t es = dice_dtype_size(dtype);
+  DICE_CHECK_ARG(es != 0, DICE_ERR_DTYPE);
+  DICE_CHECK_ARG((hidden * es) % 16 == 0, DICE_ERR_SHAPE);
+  if (n_tokens == 0) return DICE_OK;
+  DICE_CHECK_ARG(x && pos && out_rows, DICE_ERR_ARG);
+  DICE_CHECK_ARG(dice_aligned16(x) && dice_aligned16(out_rows), DICE_ERR_ALIGN);
+  const int row_vec = static_cast<int>(hidden * es / 16);
+  const int64_t blocks = (n_tokens + 7) / 8;
+  DICE_CHECK_ARG(blocks <= 0x7fffffffLL, DICE_ERR_LIMIT);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (k == 2)
+    permute_rows_kernel<2><<<static_cast<unsigned>(blocks), 256, 0, s>>>(static_cast<const uint4*>(x), pos, n_tokens,
+                                                                        row_vec, static_cast<uint4*>(out_rows));
+  else
+    permute_rows_kernel<1><<<static_cast<unsigned>(blocks), 256, 0, s>>>(static_cast<const uint4*>(x), pos, n_tokens,
+                                                                        row_vec, static_cast<uint4*>(out_rows));
+  return cudaGetLastError() == cudaSuccess ? DICE_OK : DICE_ERR_CUDA;
+}
+
+extern "C" int dice_unpermute_combine(const void* src0, const int32_t* idx0, int idx0_stride, const void* src1,
+                                      const int32_t* idx1, int idx1_stride, const float* w0, const float* w1,
+                                      int w_stride, const void* addend, int64_t n_tokens, int hidden, int dtype,
+                                      void* out, void* stream) {
+  DICE_CHECK_ARG(n_tokens >= 0 && hidden > 0, DICE_ERR_ARG);
+  const size_t es = dice_dtype_size(dtype);
+  DICE_CHECK_ARG(es != 0, DICE_ERR_DTYPE);
+  DICE_CHECK_ARG((hidden * es) % 16 == 0, DICE_ERR_SHAPE);
+  if (n_tokens == 0) return DICE_OK;
+  DICE_CHECK_ARG(src0 && out, DICE_ERR_ARG);
+  DICE_CHECK_ARG(dice_aligned16(src0) && dice_aligned16(out) && dice_aligned16(src1) && dice_aligned16(addend),
+                 DICE_ERR_ALIGN);
+  const int row_vec = static_cast<int>(hidden * es / 16);
+  const int64_t blocks = (n_tokens + 7) / 8;
+  DICE_CHECK_ARG(blocks <= 0x7fffffffLL, DICE_ERR_LIMIT);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dtype == DICE_BF16)
+    unpermute_combine_kernel<__nv_bfloat16><<<static_cast<unsigned>(blocks), 256, 0, s>>>(
+        static_cast<const uint4*>(src0), idx0, idx0_stride, static_cast<const uint4*>(src1), idx1, idx1_stride, w0, w1,
+        w_stride, static_cast<const uint4*>(addend), n_tokens, row_vec, static_cast<uint4*>(out));
+  else
+    unpermute_combine_kernel<float><<<static_cast<unsigned>(blocks), 256, 0, s>>>(
+        static_cast<const uint4*>(src0), idx0, idx0_stride, static_cast<const uint4*>(src1), idx1, idx1_stride, w0, w1,
+        w_stride, static_cast<const uint4*>(addend), n_tokens, row_vec, static_cast<uint4*>(out));
+  return cudaGetLastError() == cudaSuccess ? DICE_OK : DICE_ERR_CUDA;
+}
+
+extern "C" int64_t dice_w13_rows(int ffn) { return ffn <= 0 ? 0 : (static_cast<int64_t>(ffn) + 127) / 128 * 256; }
+
+extern "C" int dice_pack_w13(const void* gate_proj, const void* up_proj, int hidden, int ffn, int dtype,
+                             void* out_w13, void* stream) {
+  DICE_CHECK_ARG(gate_proj && up_proj && out_w13 && hidden > 0 && ffn > 0, DICE_ERR_ARG);
+  const size_t es = dice_dtype_size(dtype);
+  DICE_CHECK_ARG(es != 0, DICE_ERR_DTYPE);
+  DICE_CHECK_ARG((hidden * es) % 16 == 0, DICE_ERR_SHAPE);
+  DICE_CHECK_ARG(dice_aligned16(gate_proj) && dice_aligned16(up_proj) && dice_aligned16(out_w13), DICE_ERR_ALIGN);
+  const int row_vec = static_cast<int>(hidden * es / 16);
+  const int64_t out_rows = dice_w13_rows(ffn);
+  const int64_t total = out_rows * row_vec;
+  const int blocks = static_cast<int>(total / 256 + 1 < 4096 ? total / 256 + 1 : 4096);
+  pack_w13_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(gate_proj), static_cast<const uint4*>(up_proj), row_vec, ffn, out_rows,
+      static_cast<uint4*>(out_w13));
+  return cudaGetLastError() == cudaSuccess ? DICE_OK : DICE_ERR_CUDA;
+}

@@ -1,0 +1,303 @@
+"""Device operations of the MoE block: thin wrappers that hand torch CUDA
+tensors (device memory + stream only) to the C-ABI kernels.
+
+Every function requires CUDA tensors and the built native library; there is no
+CPU or PyTorch fallback.  Names follow the reference's vocabulary: *rows* are
+the (token, slot) rows of ``ep_fwd.py:100-111``, *segments* the per-expert runs
+of expert-sorted rows.
+"""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib
+
+DICE_BF16, DICE_F32 = 0, 1
+ACT_SWIGLU, ACT_GELU_TANH = 0, 1
+EPI_STORE, EPI_GELU_TANH, EPI_SWIGLU = 0, 1, 2
+ACT_CODES = {"swiglu": ACT_SWIGLU, "gelu_tanh": ACT_GELU_TANH}
+
+
+def _dtype_code(t: torch.Tensor) -> int:
+    if t.dtype == torch.bfloat16:
+        return DICE_BF16
+    if t.dtype == torch.float32:
+        return DICE_F32
+    raise TypeError(f"dice_b200 kernels take bfloat16 or float32 tensors, got {t.dtype}")
+
+
+def _require_cuda(*tensors: Optional[torch.Tensor]) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError(
+                "dice_b200 operations run on CUDA tensors only (no CPU fallback); got a tensor on " + str(t.device)
+            )
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def check_status(status: torch.Tensor, what: str = "dice_b200 kernel") -> None:
+    """Read a device status word (synchronises) and raise if a kernel's bounded
+    wait expired."""
+    code = int(status.item())
+    if code != 0:
+        msg = _lib.load().dice_status_message(code).decode()
+        status.zero_()
+        raise RuntimeError(f"{what}: device status {code}: {msg}")
+
+
+# --------------------------------------------------------------------------- #
+# router
+# --------------------------------------------------------------------------- #
+
+
+def router_top2(
+    x2d: torch.Tensor, w_gate: torch.Tensor, renorm: bool = False, want_logits: bool = False
+) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, Optional[torch.Tensor]]:
+    """Fused gate: returns ``(topk_idx int64 [N,2], topk_weight fp32 [N,2],
+    hist int32 [E], logits or None)``; replaces ``MoEGate.forward``
+    (models.py:179-217) and the ``bincount`` of ep_fwd.py:70."""
+    _require_cuda(x2d, w_gate)
+    assert x2d.dim() == 2 and w_gate.dim() == 2 and x2d.shape[1] == w_gate.shape[1]
+    assert x2d.dtype == w_gate.dtype, "router weight must have the activation dtype"
+    x2d = x2d.contiguous()
+    w_gate = w_gate.contiguous()
+    n, h = x2d.shape
+    e = w_gate.shape[0]
+    idx = torch.empty((n, 2), dtype=torch.int64, device=x2d.device)
+    w = torch.empty((n, 2), dtype=torch.float32, device=x2d.device)
+    hist = torch.empty((e,), dtype=torch.int32, device=x2d.device)
+    logits = torch.empty((n, e), dtype=x2d.dtype, device=x2d.device) if want_logits else None
+    lib = _lib.load()
+    _lib.check(
+        lib.dice_router_top2(
+            _ptr(x2d), _ptr(w_gate), n, h, e, _dtype_code(x2d), int(renorm), _ptr(idx), _ptr(w), _ptr(hist),
+            _ptr(logits), _stream(),
+        ),
+        "dice_router_top2",
+    )
+    return idx, w, hist, logits
+
+
+def top2_from_logits(logits: torch.Tensor, renorm: bool = False):
+    """Selection stage only (softmax + top-2 of models.py:186-196)."""
+    _require_cuda(logits)
+    logits = logits.contiguous()
+    n, e = logits.shape
+    idx = torch.empty((n, 2), dtype=torch.int64, device=logits.device)
+    w = torch.empty((n, 2), dtype=torch.float32, device=logits.device)
+    hist = torch.empty((e,), dtype=torch.int32, device=logits.device)
+    lib = _lib.load()
+    _lib.check(
+        lib.dice_top2_from_logits(_ptr(logits), n, e, _dtype_code(logits), int(renorm), _ptr(idx), _ptr(w), _ptr(hist), _stream()),
+        "dice_top2_from_logits",
+    )
+    return idx, w, hist
+
+
+# --------------------------------------------------------------------------- #
+# permutation
+# --------------------------------------------------------------------------- #
+
+
+def permute_plan(flat_idx: torch.Tensor, n_experts: int, want_order: bool = False):
+    """Stable counting sort of rows by expert.  Returns ``(pos int32 [R],
+    seg_offsets int32 [E+1], order int32 [R] or None)`` where ``pos[r]`` is the
+    sorted position of row ``r`` (the inverse of the reference's
+    ``flat_expert_indices.argsort()``, ep_fwd.py:100) and ``order`` is that
+    argsort itself."""
+    _require_cuda(flat_idx)
+    assert flat_idx.dtype == torch.int64 and flat_idx.dim() == 1
+    flat_idx = flat_idx.contiguous()
+    r = flat_idx.shape[0]
+    lib = _lib.load()
+    nbytes = lib.dice_permute_scratch_bytes(r, n_experts)
+    scratch = torch.empty((max(nbytes, 4) // 4,), dtype=torch.int32, device=flat_idx.device)
+    pos = torch.empty((r,), dtype=torch.int32, device=flat_idx.device)
+    order = torch.empty((r,), dtype=torch.int32, device=flat_idx.device) if want_order else None
+    seg = torch.empty((n_experts + 1,), dtype=torch.int32, device=flat_idx.device)
+    _lib.check(
+        lib.dice_permute_plan(_ptr(flat_idx), r, n_experts, _ptr(scratch), scratch.numel() * 4, _ptr(pos), _ptr(order),
+                              _ptr(seg), _stream()),
+        "dice_permute_plan",
+    )
+    return pos, seg, order
+
+
+def permute_rows(x2d: torch.Tensor, pos: torch.Tensor, k: int, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``out[pos[t*k+s]] = x[t]`` — the row gather of ep_fwd.py:107-111."""
+    _require_cuda(x2d, pos, out)
+    x2d = x2d.contiguous()
+    n, h = x2d.shape
+    assert pos.dtype == torch.int32 and pos.numel() == n * k
+    if out is None:
+        out = torch.empty((n * k, h), dtype=x2d.dtype, device=x2d.device)
+    assert out.is_contiguous() and out.shape[1] == h and out.shape[0] >= n * k and out.dtype == x2d.dtype
+    _lib.check(
+        _lib.load().dice_permute_rows(_ptr(x2d), _ptr(pos), n, k, h, _dtype_code(x2d), _ptr(out), _stream()),
+        "dice_permute_rows",
+    )
+    return out
+
+
+def unpermute_combine(
+    src0: torch.Tensor,
+    idx0: Optional[torch.Tensor],
+    src1: Optional[torch.Tensor],
+    idx1: Optional[torch.Tensor],
+    w0: Optional[torch.Tensor],
+    w1: Optional[torch.Tensor],
+    n_tokens: int,
+    addend: Optional[torch.Tensor] = None,
+    out: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """``out[t] = w0[t]*src0[idx0[t]] + w1[t]*src1[idx1[t]] + addend[t]``.
+
+    ``idx*`` and ``w*`` may be strided 1-D views (e.g. ``pos[0::2]``); the two
+    weight views must share one stride.  Replaces ep_fwd.py:172-195."""
+    _require_cuda(src0, idx0, src1, idx1, w0, w1, addend, out)
+    h = src0.shape[1]
+    assert src0.is_contiguous() and (src1 is None or (src1.is_contiguous() and src1.dtype == src0.dtype))
+    for i in (idx0, idx1):
+        assert i is None or (i.dtype == torch.int32 and i.dim() == 1 and i.shape[0] == n_tokens)
+    w_stride = 1
+    for w in (w0, w1):
+        if w is not None:
+            assert w.dtype == torch.float32 and w.dim() == 1 and w.shape[0] == n_tokens
+            w_stride = w.stride(0) if n_tokens > 1 else 1
+    if w0 is not None and w1 is not None and n_tokens > 1:
+        assert w0.stride(0) == w1.stride(0)
+    if addend is not None:
+        assert addend.is_contiguous() and addend.shape == (n_tokens, h) and addend.dtype == src0.dtype
+    if out is None:
+        out = torch.empty((n_tokens, h), dtype=src0.dtype, device=src0.device)
+    assert out.is_contiguous() and out.shape == (n_tokens, h) and out.dtype == src0.dtype
+    s0 = idx0.stride(0) if (idx0 is not None and n_tokens > 1) else 1
+    s1 = idx1.stride(0) if (idx1 is not None and n_tokens > 1) else 1
+    _lib.check(
+        _lib.load().dice_unpermute_combine(
+            _ptr(src0), _ptr(idx0), s0, _ptr(src1), _ptr(idx1), s1, _ptr(w0), _ptr(w1), w_stride, _ptr(addend),
+            n_tokens, h, _dtype_code(src0), _ptr(out), _stream(),
+        ),
+        "dice_unpermute_combine",
+    )
+    return out
+
+
+# --------------------------------------------------------------------------- #
+# expert weights and the grouped FFN
+# --------------------------------------------------------------------------- #
+
+
+def w13_rows(ffn: int) -> int:
+    return int(_lib.load().dice_w13_rows(ffn))
+
+
+def pack_w13(gate_proj: torch.Tensor, up_proj: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Interleave ``gate_proj``/``up_proj`` ([F, h] each, models.py:246-247)
+    in 128-row blocks for the SwiGLU epilogue."""
+    _require_cuda(gate_proj, up_proj, out)
+    gate_proj, up_proj = gate_proj.contiguous(), up_proj.contiguous()
+    f, h = gate_proj.shape
+    assert up_proj.shape == (f, h) and up_proj.dtype == gate_proj.dtype
+    rows = w13_rows(f)
+    if out is None:
+        out = torch.empty((rows, h), dtype=gate_proj.dtype, device=gate_proj.device)
+    assert out.shape == (rows, h) and out.is_contiguous()
+    _lib.check(
+        _lib.load().dice_pack_w13(_ptr(gate_proj), _ptr(up_proj), h, f, _dtype_code(gate_proj), _ptr(out), _stream()),
+        "dice_pack_w13",
+    )
+    return out
+
+
+def grouped_gemm(
+    a: torch.Tensor,
+    w: torch.Tensor,
+    seg_offsets: torch.Tensor,
+    epilogue: int,
+    n_out: int,
+    status: torch.Tensor,
+    seg_slab: Optional[torch.Tensor] = None,
+    out: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """One grouped GEMM stage on the tensor cores (bf16):
+    ``out[r] = epilogue(a[r] @ w[slab(seg(r))].T)``."""
+    _require_cuda(a, w, seg_offsets, status, seg_slab, out)
+    assert a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and a.is_contiguous() and w.is_contiguous()
+    assert w.dim() == 3 and a.dim() == 2 and w.shape[2] == a.shape[1]
+    assert seg_offsets.dtype == torch.int32 and status.dtype == torch.int32
+    n_rows, k_dim = a.shape
+    n_slabs, w_rows, _ = w.shape
+    n_seg = seg_offsets.numel() - 1
+    if out is None:
+        out = torch.empty((n_rows, n_out), dtype=torch.bfloat16, device=a.device)
+    assert out.dim() == 2 and out.stride(1) == 1 and out.shape[0] >= n_rows
+    _lib.check(
+        _lib.load().dice_grouped_gemm(
+            _ptr(a), n_rows, k_dim, _ptr(w), n_slabs, w_rows, _ptr(seg_offsets), _ptr(seg_slab), n_seg, epilogue,
+            _ptr(out), out.stride(0), n_out, _ptr(status), _stream(),
+        ),
+        "dice_grouped_gemm",
+    )
+    return out
+
+
+def grouped_ffn(
+    rows: torch.Tensor,
+    w1: torch.Tensor,
+    w2: torch.Tensor,
+    seg_offsets: torch.Tensor,
+    act: str,
+    ffn: int,
+    status: Optional[torch.Tensor] = None,
+    seg_slab: Optional[torch.Tensor] = None,
+    inter: Optional[torch.Tensor] = None,
+    out: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """Expert FFN over expert-sorted rows (ep_fwd.py:199-211; models.py:368-376).
+
+    ``w1``: packed gate/up ``[S, w13_rows(F), h]`` (swiglu) or fc1 ``[S, F, h]``
+    (gelu_tanh); ``w2``: ``[S, h, F]``.  bf16 runs on the tensor cores, fp32 on
+    the CUDA cores."""
+    _require_cuda(rows, w1, w2, seg_offsets, status, seg_slab, inter, out)
+    assert rows.is_contiguous() and w1.is_contiguous() and w2.is_contiguous()
+    assert seg_offsets.dtype == torch.int32
+    n_rows, h = rows.shape
+    n_slabs = w1.shape[0]
+    n_seg = seg_offsets.numel() - 1
+    assert w2.shape == (n_slabs, h, ffn) and w1.shape[2] == h
+    if inter is None:
+        inter = torch.empty((max(n_rows, 1), ffn), dtype=rows.dtype, device=rows.device)
+    if out is None:
+        out = torch.empty((n_rows, h), dtype=rows.dtype, device=rows.device)
+    assert inter.is_contiguous() and out.is_contiguous() and inter.shape[1] == ffn and inter.shape[0] >= n_rows
+    lib = _lib.load()
+    if rows.dtype == torch.bfloat16:
+        assert status is not None and status.dtype == torch.int32
+        _lib.check(
+            lib.dice_grouped_ffn(
+                _ptr(rows), n_rows, h, ffn, ACT_CODES[act], _ptr(w1), _ptr(w2), n_slabs, _ptr(seg_offsets),
+                _ptr(seg_slab), n_seg, _ptr(inter), _ptr(out), _ptr(status), _stream(),
+            ),
+            "dice_grouped_ffn",
+        )
+    elif rows.dtype == torch.float32:
+        _lib.check(
+            lib.dice_grouped_ffn_f32(
+                _ptr(rows), n_rows, h, ffn, ACT_CODES[act], _ptr(w1), _ptr(w2), n_slabs, _ptr(seg_offsets),
+                _ptr(seg_slab), n_seg, _ptr(inter), _ptr(out), _stream(),
+            ),
+            "dice_grouped_ffn_f32",
+        )
+    else:
+        raise TypeError(f"unsupported dtype {rows.dtype}")
+    return out

@@ -1,0 +1,192 @@
+/*
+ * dice_b200 — C ABI of the B200 (sm_100a) kernels behind the DiT-MoE block.
+ *
+ * The reference project (DICE) is pure Python on PyTorch and has no FFI of its
+ * own; each entry point below states which reference lines it replaces (paths
+ * relative to the reference project's root).  The Python host code in
+ * dice_b200/ binds these with ctypes and mirrors the reference's module
+ * interface on top of them.
+ *
+ * Conventions
+ *  - every pointer is a DEVICE pointer owned by the caller unless stated;
+ *    nothing here allocates, frees or synchronises;
+ *  - work is enqueued on `stream` (a cudaStream_t passed as void*);
+ *  - return value: 0 = enqueued, negative = argument error found on the host
+ *    (nothing was enqueued); see dice_strerror();
+ *  - kernels that wait on hardware barriers bound every wait; when a wait
+ *    expires the kernel stores a non-zero code into the caller's `status`
+ *    word, releases what it holds and returns.  The host reads the word when
+ *    it next synchronises (dice_status_message() names the code);
+ *  - row-major everywhere; "rows" are token-expert rows (one per routed
+ *    (token, slot) pair) sorted by expert, "segments" are the per-expert runs
+ *    of rows.
+ */
+#ifndef DICE_B200_H_
+#define DICE_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define DICE_ABI_VERSION 1
+
+#if defined(__GNUC__)
+#define DICE_API __attribute__((visibility("default")))
+#else
+#define DICE_API
+#endif
+
+/* element types of activations and weights */
+#define DICE_BF16 0
+#define DICE_F32 1
+
+/* expert activation variants */
+#define DICE_ACT_SWIGLU 0    /* down(silu(gate(x)) * up(x))      models.py:271 */
+#define DICE_ACT_GELU_TANH 1 /* fc2(gelu_tanh(fc1(x)))            no reference counterpart */
+
+/* epilogue modes of dice_grouped_gemm */
+#define DICE_EPI_STORE 0     /* out = A * W^T                                   */
+#define DICE_EPI_GELU_TANH 1 /* out = gelu_tanh(A * W^T)                        */
+#define DICE_EPI_SWIGLU 2    /* W holds 128-row gate/up blocks interleaved;
+                                out[:, j] = silu(gate_j) * up_j                 */
+
+/* error codes (negative) */
+#define DICE_OK 0
+#define DICE_ERR_ARG -1         /* null pointer, negative size                  */
+#define DICE_ERR_SHAPE -2       /* unsupported shape / divisibility             */
+#define DICE_ERR_DTYPE -3       /* unsupported element type                     */
+#define DICE_ERR_ALIGN -4       /* pointer not 16-byte aligned                  */
+#define DICE_ERR_SCRATCH -5     /* scratch buffer too small                     */
+#define DICE_ERR_CUDA -6        /* a CUDA runtime/driver call failed            */
+#define DICE_ERR_LIMIT -7       /* size beyond a documented maximum             */
+
+DICE_API int dice_abi_version(void);
+DICE_API const char* dice_strerror(int code);
+/* text for a device status word written by a kernel (0 = "ok") */
+DICE_API const char* dice_status_message(uint32_t status);
+
+/* ---------------------------------------------------------------------------
+ * Router: logits -> softmax -> top-2 (+ expert histogram), one fused kernel.
+ * Replaces MoEGate.forward in eval mode (models.py:179-217: F.linear :184,
+ * softmax :186, topk :191, optional renormalisation :194-196) and the
+ * bincount of ep_fwd.py:70-76 / models.py:366.
+ *   x        [n_tokens, hidden]   dtype
+ *   w_gate   [n_experts, hidden]  dtype
+ *   out_idx  [n_tokens, 2] int64  slot 0 = larger score; equal scores: lower
+ *                                 expert index first
+ *   out_w    [n_tokens, 2] fp32   softmax scores of the two (renormalised to
+ *                                 sum 1 when renorm != 0)
+ *   out_hist [n_experts]  int32   rows per expert (zeroed by the call)
+ *   out_logits  optional [n_tokens, n_experts] dtype (NULL to skip)
+ * Logits are accumulated in fp32 and rounded to dtype before the softmax,
+ * which is evaluated in fp32.  hidden*sizeof(dtype) must be a multiple of 16,
+ * n_experts in [2, 64].
+ */
+DICE_API int dice_router_top2(const void* x, const void* w_gate, int64_t n_tokens, int hidden, int n_experts,
+                     int dtype, int renorm, int64_t* out_idx, float* out_w, int32_t* out_hist,
+                     void* out_logits, void* stream);
+
+/* The selection stage alone, on logits supplied by the caller (same outputs
+ * as above).  Lets the selection be checked bit-exactly against
+ * softmax+topk (models.py:186-196) on the reference's own logits. */
+DICE_API int dice_top2_from_logits(const void* logits, int64_t n_tokens, int n_experts, int dtype, int renorm,
+                          int64_t* out_idx, float* out_w, int32_t* out_hist, void* stream);
+
+/* ---------------------------------------------------------------------------
+ * Permutation plan: stable counting sort of rows by expert.
+ * Replaces flat_expert_indices.argsort() + bincount (ep_fwd.py:70-76, :100;
+ * models.py:365-366); the order inside an expert is the stable one.
+ *   flat_idx        [n_rows] int64   expert of each (token, slot) row
+ *   scratch         dice_permute_scratch_bytes(n_rows, n_experts) bytes
+ *   out_pos         [n_rows] int32   row -> position in expert-sorted order
+ *   out_order       [n_rows] int32   position -> row (NULL to skip)
+ *   out_seg_offsets [n_experts+1] int32  first position of each expert's run
+ * Rows whose expert is outside [0, n_experts) get position -1 and are
+ * counted in no segment.
+ */
+DICE_API size_t dice_permute_scratch_bytes(int64_t n_rows, int n_experts);
+DICE_API int dice_permute_plan(const int64_t* flat_idx, int64_t n_rows, int n_experts, void* scratch,
+                      size_t scratch_bytes, int32_t* out_pos, int32_t* out_order,
+                      int32_t* out_seg_offsets, void* stream);
+
+/* Row gather into expert-sorted order (ep_fwd.py:107-111, :344-347;
+ * models.py:374): out_rows[pos[t*k + s]] = x[t] for s < k.  Negative
+ * positions are skipped. */
+DICE_API int dice_permute_rows(const void* x, const int32_t* pos, int64_t n_tokens, int k, int hidden,
+                      int dtype, void* out_rows, void* stream);
+
+/* ---------------------------------------------------------------------------
+ * Un-permute + gate-weighted sum of a token's two rows (+ optional addend).
+ * Replaces _local_combine (ep_fwd.py:349-354), the conditional-communication
+ * merge (ep_fwd.py:177-187), mul_ by the gate weights (:190-193) and the
+ * pair sum (:195); on one device the mul_/scatter_reduce_ of
+ * models.py:377-381 and the shared-expert add of models.py:357.
+ *   out[t] = w0[t*w_stride] * src0[i0] + w1[t*w_stride] * src1[i1] + addend[t]
+ * with i0 = idx0 ? idx0[t*idx0_stride] : t (same for i1).  src1 == NULL drops
+ * the second term, w0/w1 == NULL mean weight 1, addend == NULL means 0.
+ * A negative index contributes 0.  Sums are formed in fp32.
+ */
+DICE_API int dice_unpermute_combine(const void* src0, const int32_t* idx0, int idx0_stride, const void* src1,
+                           const int32_t* idx1, int idx1_stride, const float* w0, const float* w1,
+                           int w_stride, const void* addend, int64_t n_tokens, int hidden, int dtype,
+                           void* out, void* stream);
+
+/* ---------------------------------------------------------------------------
+ * Expert weights.  SwiGLU experts (models.py:246-247) are packed once at load
+ * time so that one 256-wide output tile of the first GEMM holds 128 gate and
+ * the matching 128 up columns:
+ *   out_w13 [dice_w13_rows(ffn), hidden]; block j = gate[128j:128j+128] then
+ *   up[128j:128j+128]; rows beyond ffn are zero.
+ */
+DICE_API int64_t dice_w13_rows(int ffn);
+DICE_API int dice_pack_w13(const void* gate_proj, const void* up_proj, int hidden, int ffn, int dtype,
+                  void* out_w13, void* stream);
+
+/* ---------------------------------------------------------------------------
+ * Grouped (per-segment) GEMM on the 5th-generation tensor cores:
+ *   out[r, :] = epilogue( a[r, :] * w[slab(seg(r))]^T )
+ * Replaces the per-expert nn.Linear calls driven from Python loops
+ * (ep_fwd.py:199-211, models.py:368-376, MoeMLP.forward models.py:252-273).
+ *   a            [n_rows, k_dim]            bf16, 16-byte aligned
+ *   w            [n_slabs, w_rows, k_dim]   bf16 (nn.Linear layout: out x in)
+ *   seg_offsets  [n_seg+1] int32 (device)   rows of segment s are
+ *                                           [seg_offsets[s], seg_offsets[s+1])
+ *   seg_slab     [n_seg] int32 (device) weight slab of each segment, or NULL
+ *                                           for slab = segment index
+ *   out          [n_rows, ld_out]           bf16; columns [0, n_out)
+ *   n_out        logical output width: w_rows for STORE/GELU_TANH, ffn for
+ *                SWIGLU (where w_rows = dice_w13_rows(ffn))
+ *   status       device uint32, non-zero after a bounded wait expired
+ * k_dim, ld_out, n_out multiples of 8; n_seg <= 256.  The tile list is derived
+ * on the device from seg_offsets, so no host synchronisation is needed.
+ */
+DICE_API int dice_grouped_gemm(const void* a, int64_t n_rows, int k_dim, const void* w, int n_slabs,
+                      int64_t w_rows, const int32_t* seg_offsets, const int32_t* seg_slab, int n_seg,
+                      int epilogue, void* out, int64_t ld_out, int n_out, uint32_t* status,
+                      void* stream);
+
+/* The expert FFN over expert-sorted rows: two dice_grouped_gemm launches
+ * (ep_fwd.py:199-211 proc_experts; models.py:368-376).
+ *   act = DICE_ACT_SWIGLU   : w1 = packed gate/up [n_slabs, dice_w13_rows(ffn), hidden]
+ *   act = DICE_ACT_GELU_TANH: w1 = fc1 [n_slabs, ffn, hidden]
+ *   w2  [n_slabs, hidden, ffn];  inter = caller's scratch [n_rows, ffn] bf16.
+ */
+DICE_API int dice_grouped_ffn(const void* rows_in, int64_t n_rows, int hidden, int ffn, int act, const void* w1,
+                     const void* w2, int n_slabs, const int32_t* seg_offsets, const int32_t* seg_slab,
+                     int n_seg, void* inter, void* rows_out, uint32_t* status, void* stream);
+
+/* fp32 variant of the expert FFN on the CUDA cores (no tensor-core rounding;
+ * used where fp32 parity at 1e-5 is asked for).  Same arguments as
+ * dice_grouped_ffn with fp32 tensors; SwiGLU takes the packed layout too. */
+DICE_API int dice_grouped_ffn_f32(const void* rows_in, int64_t n_rows, int hidden, int ffn, int act,
+                         const void* w1, const void* w2, int n_slabs, const int32_t* seg_offsets,
+                         const int32_t* seg_slab, int n_seg, void* inter, void* rows_out,
+                         void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DICE_B200_H_ */

@@ -1,0 +1,296 @@
+"""Parity of each CUDA kernel (called through the C ABI) with the CPU oracle."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import moe_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+def _ops():
+    from dice_b200 import ops
+
+    return ops
+
+
+# --------------------------------------------------------------------------- #
+# router
+# --------------------------------------------------------------------------- #
+
+
+@pytest.mark.parametrize("n,h,e", [(1, 64, 8), (2, 1152, 8), (127, 1152, 8), (512, 1152, 8), (129, 1792, 16), (333, 256, 5), (64, 128, 32), (40, 128, 64)])
+@pytest.mark.parametrize("renorm", [False, True])
+def test_router_fp32_bit_exact_routing(cuda_device, n, h, e, renorm):
+    ops = _ops()
+    g = torch.Generator().manual_seed(n * 7 + h + e)
+    x = torch.randn(n, h, generator=g)
+    wg = torch.randn(e, h, generator=g) * 0.02
+    idx_o, w_o, _ = O.gate_top2(x, wg, renorm)
+    idx, w, hist, logits = ops.router_top2(x.to(cuda_device), wg.to(cuda_device), renorm, want_logits=True)
+    assert torch.equal(idx.cpu(), idx_o)
+    torch.testing.assert_close(w.cpu(), w_o, rtol=1e-5, atol=1e-7)
+    assert torch.equal(hist.cpu().long(), O.expert_histogram(idx_o.reshape(-1), e))
+    torch.testing.assert_close(logits.cpu(), x @ wg.t(), rtol=1e-5, atol=1e-6)
+
+
+@pytest.mark.parametrize("n,h,e", [(512, 1152, 8), (2048, 1792, 16), (4096, 1408, 16)])
+def test_router_bf16_against_oracle(cuda_device, n, h, e):
+    """bf16: logits may differ from the oracle's by one bf16 ulp (summation
+    order); every routing mismatch must be such a near-tie."""
+    ops = _ops()
+    g = torch.Generator().manual_seed(n + h + e)
+    x = torch.randn(n, h, generator=g).bfloat16()
+    wg = (torch.randn(e, h, generator=g) * 0.05).bfloat16()
+    idx_o, w_o, logits_o = O.gate_top2(x, wg)
+    idx, w, hist, logits = ops.router_top2(x.to(cuda_device), wg.to(cuda_device), False, want_logits=True)
+    idx, w, logits = idx.cpu(), w.cpu(), logits.cpu()
+    # logits within one bf16 ulp of the oracle's
+    lf, lo = logits.float(), logits_o.float()
+    ulp = torch.maximum(lo.abs(), torch.tensor(2.0 ** -126)).log2().floor().exp2() * 2.0 ** -7
+    assert ((lf - lo).abs() <= ulp + 1e-12).all()
+    # the kernel's selection is exactly the oracle's selection on the kernel's own logits
+    w_sel, idx_sel = O.top2_from_scores(logits.float().softmax(-1))
+    assert torch.equal(idx, idx_sel)
+    torch.testing.assert_close(w, w_sel, rtol=2e-6, atol=1e-8)
+    mism = (idx != idx_o).any(-1)
+    # mismatching tokens: the logits of the disputed experts differ by <= 1 ulp in the oracle
+    for t in mism.nonzero().flatten().tolist():
+        a = set(idx[t].tolist()) ^ set(idx_o[t].tolist())
+        vals = lo[t, sorted(a)]
+        assert (vals.max() - vals.min()).abs() <= 2 * ulp[t].max() or set(idx[t].tolist()) == set(idx_o[t].tolist())
+    assert mism.float().mean() < 0.02
+    assert int(hist.sum()) == 2 * n
+
+
+def test_selection_tie_rule_matches_cuda_topk(cuda_device):
+    """Crafted ties: the selection must reproduce torch.topk(k=2, sorted=False)
+    of the CUDA backend on the softmax scores (models.py:186-191)."""
+    ops = _ops()
+    rows = [
+        [0.1, 0.3, 0.3, 0.3, 0.0, 0.0, 0.0, 0.0],
+        [0.25, 0.25, 0.25, 0.25, 0.0, 0.0, 0.0, 0.0],
+        [1.0, 1.0, 1.0, 1.0, 1.0, 1.0, 1.0, 1.0],
+        [0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 2.0, 2.0],
+        [3.0, 0.0, 0.0, 3.0, 0.0, 1.0, 0.0, 0.0],
+        [0.0, 1.0, 0.5, 0.5, 0.5, 0.0, 0.0, 0.0],
+        [-1.0, -1.0, -2.0, -3.0, -1.0, -4.0, -5.0, -6.0],
+    ]
+    g = torch.Generator().manual_seed(5)
+    rnd = (torch.randn(4096, 8, generator=g) * 2).bfloat16().float()  # many exact ties after bf16 rounding
+    logits = torch.cat([torch.tensor(rows), rnd]).to(cuda_device)
+    idx, w, hist = ops.top2_from_logits(logits)
+    scores = logits.softmax(-1)
+    tw, ti = torch.topk(scores, k=2, dim=-1, sorted=False)
+    assert torch.equal(idx, ti)
+    torch.testing.assert_close(w, tw, rtol=2e-6, atol=1e-8)
+    w_o, idx_o = O.top2_from_scores(logits.cpu().softmax(-1))
+    assert torch.equal(idx.cpu(), idx_o)
+
+
+# --------------------------------------------------------------------------- #
+# permutation
+# --------------------------------------------------------------------------- #
+
+
+@pytest.mark.parametrize("n,e,k", [(1, 8, 2), (2, 8, 2), (127, 8, 2), (128, 8, 2), (129, 8, 2), (5000, 16, 2), (777, 8, 1), (300, 64, 2)])
+def test_permute_plan_is_stable_argsort(cuda_device, n, e, k):
+    ops = _ops()
+    g = torch.Generator().manual_seed(n + e)
+    flat = torch.randint(0, e, (n * k,), generator=g)
+    if n >= 127:
+        flat[flat == 3] = 2  # an empty expert
+    pos, seg, order = ops.permute_plan(flat.to(cuda_device), e, want_order=True)
+    order_o = O.stable_expert_order(flat)
+    assert torch.equal(order.cpu().long(), order_o)
+    inv = torch.empty_like(order_o)
+    inv[order_o] = torch.arange(n * k)
+    assert torch.equal(pos.cpu().long(), inv)
+    hist = O.expert_histogram(flat, e)
+    assert torch.equal(seg.cpu().long(), torch.cat([torch.zeros(1, dtype=torch.long), hist.cumsum(0)]))
+
+
+def test_permute_plan_all_rows_one_expert_and_empty(cuda_device):
+    ops = _ops()
+    flat = torch.full((1000,), 5, dtype=torch.int64)
+    pos, seg, order = ops.permute_plan(flat.to(cuda_device), 8, want_order=True)
+    assert torch.equal(pos.cpu().long(), torch.arange(1000))
+    assert seg.cpu().tolist() == [0] * 6 + [1000] * 3
+    pos, seg, _ = ops.permute_plan(torch.empty(0, dtype=torch.int64, device=cuda_device), 8)
+    assert seg.cpu().tolist() == [0] * 9 and pos.numel() == 0
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("n,h,e", [(1, 64, 8), (129, 1152, 8), (512, 1792, 16)])
+def test_permute_rows_and_unpermute_combine(cuda_device, dtype, n, h, e):
+    ops = _ops()
+    g = torch.Generator().manual_seed(n + h)
+    x = torch.randn(n, h, generator=g).to(dtype)
+    flat = torch.randint(0, e, (n * 2,), generator=g)
+    w = torch.rand(n, 2, generator=g)
+    shared = torch.randn(n, h, generator=g).to(dtype)
+    pos, seg, _ = ops.permute_plan(flat.to(cuda_device), e)
+    rows = ops.permute_rows(x.to(cuda_device), pos, 2)
+    rows_o, order_o = O.permute_rows(x, flat, 2)
+    assert torch.equal(rows.cpu(), rows_o)  # pure data movement: bit exact
+    # combine: weighted pair sum of the (here: identity-processed) rows + addend
+    wd = w.to(cuda_device)
+    out = ops.unpermute_combine(rows, pos[0::2], rows, pos[1::2], wd[:, 0], wd[:, 1], n, addend=shared.to(cuda_device))
+    flat_rows = O.unpermute_rows(rows_o, order_o)
+    want = (flat_rows.float().view(n, 2, h) * w.view(n, 2, 1)).sum(1) + shared.float()
+    tol = dict(rtol=1e-6, atol=1e-6) if dtype == torch.float32 else dict(rtol=1e-2, atol=1e-2)
+    torch.testing.assert_close(out.cpu().float(), want, **tol)
+    # single-source form with identity index and unit weight = plain un-permute of slot 0
+    slot0 = ops.unpermute_combine(rows, pos[0::2], None, None, None, None, n)
+    assert torch.equal(slot0.cpu(), x)
+
+
+def test_permute_round_trip_full_size(cuda_device):
+    """Size-independent property at the benchmark's size: permute then
+    un-permute with weights (1, 0) returns the input."""
+    ops = _ops()
+    n, h, e = 16384, 1152, 8
+    g = torch.Generator(device="cuda").manual_seed(3)
+    x = torch.randn(n, h, generator=g, device=cuda_device).bfloat16()
+    flat = torch.randint(0, e, (2 * n,), generator=g, device=cuda_device)
+    pos, seg, order = ops.permute_plan(flat, e, want_order=True)
+    assert int(seg[-1]) == 2 * n
+    srt = flat[order.long()]
+    assert bool((srt[1:] >= srt[:-1]).all())  # sortedness
+    rows = ops.permute_rows(x, pos, 2)
+    ones = torch.ones(n, 2, device=cuda_device)
+    zeros = torch.zeros(n, 2, device=cuda_device)
+    back = ops.unpermute_combine(rows, pos[0::2], rows, pos[1::2], ones[:, 0], zeros[:, 1], n)
+    assert torch.equal(back, x)
+
+
+# --------------------------------------------------------------------------- #
+# grouped GEMM / FFN
+# --------------------------------------------------------------------------- #
+
+
+def _segments(counts, device):
+    return torch.tensor([0] + list(np.cumsum(counts)), dtype=torch.int32, device=device)
+
+
+@pytest.mark.parametrize(
+    "counts,k,n",
+    [
+        ([128], 64, 256),        # one tile, one k-block
+        ([128], 16, 32),         # a single MMA
+        ([128], 128, 256),       # two k-blocks
+        ([128], 1152, 256),      # full reduction depth, ring wrap-around
+        ([256], 320, 512),       # 2x2 tiles
+        ([100], 64, 64),         # ragged rows, narrow n
+        ([1, 0, 129, 37], 1152, 1152),  # ragged segments, empty segment, n = 4.5 tiles
+        ([300, 300, 300, 300, 300, 300, 300, 300], 1152, 4608),
+        ([511, 513], 4608, 1152),
+    ],
+)
+def test_grouped_gemm_store(cuda_device, counts, k, n):
+    ops = _ops()
+    g = torch.Generator().manual_seed(sum(counts) + k + n)
+    r, s = sum(counts), len(counts)
+    a = torch.randn(r, k, generator=g).bfloat16()
+    w = (torch.randn(s, n, k, generator=g) / math.sqrt(k)).bfloat16()
+    seg = _segments(counts, cuda_device)
+    status = torch.zeros(1, dtype=torch.int32, device=cuda_device)
+    out = torch.full((r + 3, n), 7.0, dtype=torch.bfloat16, device=cuda_device)  # canary rows
+    ops.grouped_gemm(a.to(cuda_device), w.to(cuda_device), seg, ops.EPI_STORE, n, status, out=out)
+    torch.cuda.synchronize()
+    ops.check_status(status)
+    want = torch.cat([a[seg[i] : seg[i + 1]].float() @ w[i].float().t() for i in range(s)])
+    torch.testing.assert_close(out[:r].cpu().float(), want, rtol=2e-2, atol=2e-2)
+    assert bool((out[r:] == 7.0).all())
+
+
+@pytest.mark.parametrize("act", ["swiglu", "gelu_tanh"])
+@pytest.mark.parametrize("counts,h,f", [([111], 32, 128), ([5, 0, 200, 51], 128, 512), ([130, 126, 257, 0, 3, 64, 64, 380], 1152, 4608)])
+def test_grouped_ffn_bf16(cuda_device, act, counts, h, f):
+    ops = _ops()
+    g = torch.Generator().manual_seed(sum(counts) + h + f)
+    r, s = sum(counts), len(counts)
+    x = torch.randn(r, h, generator=g).bfloat16()
+    mk = lambda *shape: (torch.randn(*shape, generator=g) / math.sqrt(shape[-1])).bfloat16()
+    if act == "swiglu":
+        experts = [(mk(f, h), mk(f, h), mk(h, f)) for _ in range(s)]
+        w1 = torch.stack([ops.pack_w13(e[0].to(cuda_device), e[1].to(cuda_device)) for e in experts])
+        w2 = torch.stack([e[2] for e in experts]).to(cuda_device)
+    else:
+        experts = [(mk(f, h), mk(h, f)) for _ in range(s)]
+        w1 = torch.stack([e[0] for e in experts]).to(cuda_device)
+        w2 = torch.stack([e[1] for e in experts]).to(cuda_device)
+    seg = _segments(counts, cuda_device)
+    status = torch.zeros(1, dtype=torch.int32, device=cuda_device)
+    out = ops.grouped_ffn(x.to(cuda_device), w1, w2, seg, act, f, status)
+    torch.cuda.synchronize()
+    ops.check_status(status)
+    want = torch.cat(
+        [O.run_expert(x[seg[i] : seg[i + 1]].float(), [t.float() for t in experts[i]], act) for i in range(s)]
+    )
+    err = (out.cpu().float() - want).norm() / want.norm()
+    assert err < 2e-2, f"relative error {err}"
+    torch.testing.assert_close(out.cpu().float(), want, rtol=5e-2, atol=5e-2 * want.abs().max().item())
+
+
+@pytest.mark.parametrize("act", ["swiglu", "gelu_tanh"])
+def test_grouped_ffn_fp32(cuda_device, act):
+    ops = _ops()
+    counts, h, f = [70, 0, 3, 64, 129], 96, 200
+    g = torch.Generator().manual_seed(11)
+    r, s = sum(counts), len(counts)
+    x = torch.randn(r, h, generator=g)
+    mk = lambda *shape: torch.randn(*shape, generator=g) / math.sqrt(shape[-1])
+    if act == "swiglu":
+        experts = [(mk(f, h), mk(f, h), mk(h, f)) for _ in range(s)]
+        w1 = torch.stack([ops.pack_w13(e[0].to(cuda_device), e[1].to(cuda_device)) for e in experts])
+        w2 = torch.stack([e[2] for e in experts]).to(cuda_device)
+    else:
+        experts = [(mk(f, h), mk(h, f)) for _ in range(s)]
+        w1 = torch.stack([e[0] for e in experts]).to(cuda_device)
+        w2 = torch.stack([e[1] for e in experts]).to(cuda_device)
+    seg = _segments(counts, cuda_device)
+    out = ops.grouped_ffn(x.to(cuda_device), w1, w2, seg, act, f)
+    want = torch.cat([O.run_expert(x[seg[i] : seg[i + 1]], experts[i], act) for i in range(s)])
+    torch.testing.assert_close(out.cpu(), want, rtol=1e-5, atol=1e-5)
+
+
+def test_grouped_gemm_rejects_bad_segments(cuda_device):
+    """Non-monotone segment offsets: the kernel records a status code and does
+    no work (bounded, no fault)."""
+    ops = _ops()
+    a = torch.zeros(256, 64, dtype=torch.bfloat16, device=cuda_device)
+    w = torch.zeros(2, 32, 64, dtype=torch.bfloat16, device=cuda_device)
+    seg = torch.tensor([0, 200, 100], dtype=torch.int32, device=cuda_device)
+    status = torch.zeros(1, dtype=torch.int32, device=cuda_device)
+    ops.grouped_gemm(a, w, seg, ops.EPI_STORE, 32, status)
+    with pytest.raises(RuntimeError, match="segment offsets"):
+        ops.check_status(status)
+
+
+def test_linearity_full_size_ffn_gemm(cuda_device):
+    """Size-independent property at the benchmark's shape: the store-epilogue
+    GEMM is linear in its input: f(a) + f(b) == f(a + b) up to bf16 rounding,
+    and row r of the output depends only on row r and its expert's weights."""
+    ops = _ops()
+    r, k, n, s = 32768, 1152, 1152, 8
+    g = torch.Generator(device="cuda").manual_seed(9)
+    a = torch.randn(r, k, generator=g, device=cuda_device).bfloat16()
+    w = (torch.randn(s, n, k, generator=g, device=cuda_device) / math.sqrt(k)).bfloat16()
+    counts = torch.tensor([4000, 4200, 3900, 4100, 4096, 4096, 4288, 4088])
+    seg = _segments(counts.tolist(), cuda_device)
+    status = torch.zeros(1, dtype=torch.int32, device=cuda_device)
+    out = ops.grouped_gemm(a, w, seg, ops.EPI_STORE, n, status)
+    torch.cuda.synchronize()
+    ops.check_status(status)
+    # spot-check 64 random rows against fp32 math
+    rows = torch.randint(0, r, (64,), generator=torch.Generator().manual_seed(1))
+    ends = counts.cumsum(0)
+    for row in rows.tolist():
+        e = int((ends > row).nonzero()[0])
+        want = a[row].float() @ w[e].float().t()
+        torch.testing.assert_close(out[row].float(), want, rtol=2e-2, atol=2e-2)
+    out2 = ops.grouped_gemm((a * 2).contiguous(), w, seg, ops.EPI_STORE, n, status)
+    torch.testing.assert_close(out2.float(), out.float() * 2, rtol=1e-2, atol=1e-2)
