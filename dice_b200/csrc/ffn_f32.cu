@@ -24,9 +24,9 @@ grouped_gemm_f32_kernel(const float* __restrict__ a, const float* __restrict__ w
                         float* __restrict__ out, int64_t ld_out) {
   constexpr bool DUAL = EPI == DICE_EPI_SWIGLU;
   __shared__ int s_seg, s_row0, s_rows;
-  __shared__ float As[TK][TM + 4];
-  __shared__ float Ws[TK][TN + 4];
-  __shared__ float Us[DUAL ? TK : 1][TN + 4];
+  __shared__ __align__(16) float As[TK][TM + 4];
+  __shared__ __align__(16) float Ws[TK][TN + 4];
+  __shared__ __align__(16) float Us[DUAL ? TK : 1][TN + 4];
   if (threadIdx.x == 0) {
     int run = 0, found = -1, row0 = 0, rows = 0;
     for (int s = 0; s < n_seg; ++s) {

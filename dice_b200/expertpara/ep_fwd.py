@@ -1,0 +1,343 @@
+"""Expert-parallel MoE forward: drop-in for the reference's
+``expertpara/ep_fwd.py`` (``moe_infer_ep`` :19-197 and helpers :199-354).
+
+Experts are sharded round-robin over the ranks (``etrim.py:23-24``); tokens
+stay on the rank that owns them, their (token, slot) rows travel to the expert
+owners through an uneven all-to-all (dispatch), run the expert FFN there, and
+travel back (combine).  What differs from the reference is *how*, not *what*:
+
+* the histogram, the stable expert sort, the row gather, the expert FFN and
+  the un-permute + gate-weighted pair sum are CUDA kernels reached through the
+  C ABI (``dice_b200.ops``); the zero-fill + ``index_copy_`` + ``mul_`` +
+  ``sum`` tail of the reference (:172-195) is one kernel;
+* rows are sorted by ``(owner rank, local slot)`` instead of by expert id, so
+  ONE ``all_to_all_single`` per direction and layer moves what the reference
+  moves with ``E/W`` calls (:277-291, :326-340); the receive buffer is then
+  source-major and the grouped FFN walks its ``(source, slot)`` segments;
+* per layer there is one device-to-host read (the gathered ``[W, E]`` count
+  matrix, which NCCL needs as host-side split sizes) instead of the
+  reference's per-slot ``.tolist()`` calls and tensor-valued slice bounds.
+
+The block output is identical to the reference's for every mode; the row
+order *inside* the exchanged buffers is an internal matter.
+"""
+from __future__ import annotations
+
+import contextlib
+from typing import List, Optional, Sequence, Tuple
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+from . import diep
+from .diep import ep_skip_get, ep_skip_put, global_combine_async, global_dispatch_async  # noqa: F401
+
+_use_latest_expert_weights = None
+
+
+def use_latest_expert_weights(val):
+    """ep_fwd.py:12-15: scale the (possibly stale) expert outputs by the
+    current step's gate weights (True) or by the cached ones (False)."""
+    assert val in [True, False], "val must be a boolean"
+    global _use_latest_expert_weights
+    _use_latest_expert_weights = val
+
+
+# --------------------------------------------------------------------------- #
+# device operations (CUDA kernels); replaceable only so that the host logic can
+# be exercised by CPU gloo ranks in the test-suite
+# --------------------------------------------------------------------------- #
+
+
+class CudaOps:
+    """The product's device operations: every method launches dice_b200 CUDA
+    kernels and refuses CPU tensors."""
+
+    def plan(self, keys: torch.Tensor, n_keys: int):
+        from .. import ops
+
+        pos, seg, _ = ops.permute_plan(keys, n_keys)
+        return pos, seg
+
+    def permute_rows(self, x: torch.Tensor, pos: torch.Tensor, k: int) -> torch.Tensor:
+        from .. import ops
+
+        return ops.permute_rows(x, pos, k)
+
+    def unpermute_combine(self, src0, idx0, src1, idx1, w0, w1, n_tokens, addend=None):
+        from .. import ops
+
+        return ops.unpermute_combine(src0, idx0, src1, idx1, w0, w1, n_tokens, addend=addend)
+
+    def run_packed_experts(self, rows, pack, seg_counts: Sequence[int], seg_slab: Sequence[int]):
+        return pack.run_segments(rows, seg_counts, seg_slab)
+
+
+_ops = CudaOps()
+
+
+def set_device_ops(ops_obj) -> None:
+    """Replace the device operations (used by the CPU tests of the host logic)."""
+    global _ops
+    _ops = ops_obj
+
+
+def device_ops():
+    return _ops
+
+
+def _scope(name: str):
+    """The reference wraps each phase in ``CudaProfiler.scope`` (ep_fwd.py:88,
+    108, 127, 149, 153, 172); keep the same section names when its profiler is
+    importable, else time nothing."""
+    prof = diep._profiler()
+    return prof.scope(name) if prof is not None else contextlib.nullcontext()
+
+
+# --------------------------------------------------------------------------- #
+# counts
+# --------------------------------------------------------------------------- #
+
+
+@torch.no_grad()
+def exchange_token_counts(token_counts_local: torch.Tensor) -> torch.Tensor:
+    """ep_fwd.py:214-245: all-gather the per-expert row counts (expert-id
+    order, length E) and return the ``[world_size, E/W]`` counts of rows each
+    rank sends to THIS rank's local experts."""
+    world_size, rank = dist.get_world_size(), dist.get_rank()
+    assert token_counts_local.size(0) % world_size == 0, "Number of experts must be divisible by world size"
+    gathered = [torch.zeros_like(token_counts_local) for _ in range(world_size)]
+    dist.all_gather(gathered, token_counts_local)
+    return torch.stack(gathered, dim=0)[:, rank::world_size]
+
+
+@torch.no_grad()
+def _exchange_counts_by_owner(counts_key: torch.Tensor, world_size: int, rank: int) -> Tuple[torch.Tensor, torch.Tensor]:
+    """All-gather the local counts, which are laid out ``[owner rank][slot]``,
+    and bring the ``[W, E]`` matrix to the host once.  Returns CPU int64
+    tensors ``send[W, El]`` (rows this rank sends to rank d's slot i) and
+    ``recv[W, El]`` (rows rank s sends to this rank's slot i)."""
+    n_local = counts_key.numel() // world_size
+    if world_size == 1:
+        mine = counts_key.to("cpu", torch.int64).view(1, n_local)
+        return mine, mine.clone()
+    gathered = torch.empty((world_size, counts_key.numel()), dtype=counts_key.dtype, device=counts_key.device)
+    dist.all_gather_into_tensor(gathered, counts_key.contiguous())
+    host = gathered.to("cpu", torch.int64).view(world_size, world_size, n_local)
+    return host[rank].contiguous(), host[:, rank, :].contiguous()
+
+
+# --------------------------------------------------------------------------- #
+# all-to-all
+# --------------------------------------------------------------------------- #
+
+
+@torch.no_grad()
+def _all_to_all_rows(send: torch.Tensor, in_counts: torch.Tensor, out_counts: torch.Tensor, async_op: bool):
+    """One uneven all-to-all of rows.  ``in_counts``/``out_counts`` are CPU
+    ``[W, El]`` tensors; the split towards/from a rank is the row sum."""
+    in_splits = in_counts.sum(dim=1).tolist()
+    out_splits = out_counts.sum(dim=1).tolist()
+    assert send.size(0) == sum(in_splits)
+    buf = send.new_empty((sum(out_splits), send.size(1)))
+    with _scope("global_dispatch.call_dist"):
+        handle = dist.all_to_all_single(buf, send, out_splits, in_splits, async_op=True)
+    with _scope("moe.wait"):
+        if not async_op:
+            handle.wait()
+    return buf, [handle]
+
+
+@torch.no_grad()
+def global_dispatch(grouped_dup_inp, token_counts_local, token_counts_global, async_op=False):
+    """Send owner-sorted rows to the expert owners (ep_fwd.py:247-293).
+
+    ``token_counts_local`` / ``token_counts_global`` are the CPU ``[W, E/W]``
+    send / receive counts.  Returns ``(recv_buf, handles)``; the receive
+    buffer is ordered ``[source rank][local slot]``."""
+    return _all_to_all_rows(grouped_dup_inp, token_counts_local, token_counts_global, async_op)
+
+
+@torch.no_grad()
+def global_combine(grouped_dup_outp, token_counts_local, token_counts_global, async_op=False):
+    """Return expert outputs to the token owners; the mirror image of
+    :func:`global_dispatch` (ep_fwd.py:295-342)."""
+    return _all_to_all_rows(grouped_dup_outp, token_counts_global, token_counts_local, async_op)
+
+
+# --------------------------------------------------------------------------- #
+# experts
+# --------------------------------------------------------------------------- #
+
+
+@torch.no_grad()
+def proc_experts(inp, experts, token_counts_global, num_local_experts):
+    """Run this rank's experts over the received rows (ep_fwd.py:199-211).
+
+    The buffer is ``[source][slot]``-ordered; segment ``(s, i)`` holds
+    ``token_counts_global[s, i]`` rows for local slot ``i`` (global expert
+    ``rank + i * world_size``).  Expert lists built by ``SparseMoeBlock`` carry
+    packed weights and run as one grouped-FFN launch pair; any other list of
+    row-wise modules is called segment by segment, as the reference does."""
+    world_size, rank = dist.get_world_size(), dist.get_rank()
+    counts = token_counts_global.tolist()  # CPU tensor: no device sync
+    seg_counts = [counts[s][i] for s in range(world_size) for i in range(num_local_experts)]
+    seg_slab = [i for _ in range(world_size) for i in range(num_local_experts)]
+    assert sum(seg_counts) == inp.size(0)
+    pack = getattr(experts, "_dice_pack", None)
+    if pack is not None:
+        return _ops.run_packed_experts(inp, pack, seg_counts, seg_slab)
+    outp = torch.empty_like(inp)
+    start = 0
+    for cnt, slot in zip(seg_counts, seg_slab):
+        if cnt:
+            outp[start:start + cnt] = experts[rank + slot * world_size](inp[start:start + cnt])
+        start += cnt
+    return outp
+
+
+# --------------------------------------------------------------------------- #
+# the forward
+# --------------------------------------------------------------------------- #
+
+
+def _slot_views(skip_mask: torch.Tensor, n_tokens: int, device) -> Tuple[Optional[int], torch.Tensor]:
+    """From the reference's boolean row mask (one True per token pair,
+    diep.py:72-90) derive the skipped slot: a constant for the 'high'/'low'
+    patterns, else a per-token int64 tensor on ``device``."""
+    m = skip_mask.view(n_tokens, 2)
+    assert bool((m.sum(dim=1) == 1).all()), "skip mask must mark exactly one slot per token"
+    if bool(m[:, 1].all()):
+        return 1, None
+    if bool(m[:, 0].all()):
+        return 0, None
+    return None, m[:, 1].to(device=device, dtype=torch.int64)
+
+
+_slot_cache = {}
+
+
+def _skipped_slot(skip_mask: torch.Tensor, n_tokens: int, device):
+    key = (id(skip_mask), n_tokens, str(device))
+    hit = _slot_cache.get(key)
+    if hit is None or hit[0] is not skip_mask:
+        const, per_tok = _slot_views(skip_mask.cpu() if skip_mask.is_cuda else skip_mask, n_tokens, device)
+        if len(_slot_cache) > 64:
+            _slot_cache.clear()
+        hit = (skip_mask, const, per_tok)
+        _slot_cache[key] = hit
+    return hit[1], hit[2]
+
+
+def _pick(pairs: torch.Tensor, const_slot: Optional[int], per_tok: Optional[torch.Tensor], other: bool) -> torch.Tensor:
+    """Column ``slot`` (or the other one) of an ``[N, 2]`` tensor as a 1-D view/tensor."""
+    if const_slot is not None:
+        s = 1 - const_slot if other else const_slot
+        return pairs[:, s]
+    sel = (1 - per_tok) if other else per_tok
+    return pairs.gather(1, sel.view(-1, 1)).view(-1)
+
+
+@torch.no_grad()
+def moe_infer_ep(inp: torch.Tensor, experts: nn.ModuleList, flat_expert_indices, flat_expert_weights,
+                 num_experts_per_tok, async_op, skip_mask=None, skip_now=None, cache_key=None, _addend=None):
+    """Expert-parallel replacement of ``SparseMoeBlock.moe_infer``
+    (ep_fwd.py:19-197; same arguments and result).
+
+    ``inp`` ``[N, h]``; ``experts`` the block's full expert list (only entries
+    ``rank + i*W`` are real); ``flat_expert_indices`` ``[N*k]`` int64;
+    ``flat_expert_weights`` ``[N*k, 1]``; ``async_op`` selects the displaced /
+    interweaved protocol of :mod:`diep`; ``skip_mask`` / ``skip_now`` drive
+    conditional communication; ``cache_key`` is the layer index.  ``_addend``
+    (not in the reference) is added to the result inside the combine kernel."""
+    world_size, rank = dist.get_world_size(), dist.get_rank()
+    num_total_experts = len(experts)
+    num_local_experts = num_total_experts // world_size
+    assert num_total_experts % world_size == 0, "Number of experts must be divisible by world size"
+    n_tokens, hidden = inp.shape
+    k_full = num_experts_per_tok
+
+    partial_skip = skip_mask is not None
+    const_slot = per_tok = None
+    if partial_skip:
+        assert k_full == 2, "only support num_experts_per_tok == 2"
+        const_slot, per_tok = _skipped_slot(skip_mask, n_tokens, inp.device)
+
+    # conditional communication: on a skip step only the retained slot of each token travels (:57-66)
+    if skip_now:
+        assert partial_skip, "skip is not enabled"
+        k_eff = k_full // 2
+        flat_idx = _pick(flat_expert_indices.view(n_tokens, 2), const_slot, per_tok, other=True).contiguous()
+        assert flat_idx.size(0) == n_tokens * k_eff
+    else:
+        k_eff = k_full
+        flat_idx = flat_expert_indices
+
+    # sort key = (owner rank, local slot): rows for one destination are contiguous
+    keys = (flat_idx % world_size) * num_local_experts + torch.div(flat_idx, world_size, rounding_mode="floor")
+    pos, seg_offsets = _ops.plan(keys, num_total_experts)
+    with _scope("exchange_token_counts"):
+        counts_local, counts_global = _exchange_counts_by_owner(seg_offsets[1:] - seg_offsets[:-1], world_size, rank)
+    assert int(counts_local.sum()) == n_tokens * k_eff, "expert index out of range"
+
+    with _scope("local_dispatch"):
+        grouped_dup_inp = _ops.permute_rows(inp, pos, k_eff)
+
+    latest_flat_expert_weights = flat_expert_weights
+    with _scope("global_dispatch"):
+        if not async_op:
+            mlp_inp, _ = global_dispatch(grouped_dup_inp, counts_local, counts_global)
+            experts_to_calc = experts
+        else:
+            (mlp_inp, counts_local, counts_global, pos, flat_expert_weights, experts_to_calc) = global_dispatch_async(
+                grouped_dup_inp=grouped_dup_inp, token_counts_local=counts_local, token_counts_global=counts_global,
+                grouped_idx_dup=pos, flat_expert_weights=flat_expert_weights, experts=experts, cache_key=cache_key)
+
+    with _scope("moe.mlp"):
+        mlp_outp = proc_experts(mlp_inp, experts_to_calc, counts_global, num_local_experts)
+
+    with _scope("global_combine"):
+        if not async_op:
+            grouped_dup_outp, _ = global_combine(mlp_outp, counts_local, counts_global)
+        else:
+            grouped_dup_outp, pos, flat_expert_weights = global_combine_async(
+                grouped_dup_outp=mlp_outp, token_counts_local=counts_local, token_counts_global=counts_global,
+                grouped_idx_dup=pos, flat_expert_weights=flat_expert_weights, cache_key=cache_key)
+
+    # un-permute, merge with the skip cache, scale by the gate weights and sum each token's pair (:172-195)
+    weights = latest_flat_expert_weights if _use_latest_expert_weights else flat_expert_weights
+    w_pairs = weights.reshape(n_tokens, k_full)
+    if w_pairs.dtype != torch.float32:
+        w_pairs = w_pairs.float()
+    got_rows = grouped_dup_outp.size(0)
+    with _scope("local_combine"):
+        if partial_skip and got_rows != n_tokens * k_full:
+            # the exchange that just completed carried one slot per token: the other comes from the skip cache
+            assert got_rows == n_tokens * k_full // 2
+            dropped = ep_skip_get(cache_key)
+            assert dropped is not None and dropped.shape == (n_tokens, hidden)
+            w_kept = _pick(w_pairs, const_slot, per_tok, other=True)
+            w_drop = _pick(w_pairs, const_slot, per_tok, other=False)
+            if per_tok is not None:
+                w_kept, w_drop = w_kept.contiguous(), w_drop.contiguous()
+            expert_out = _ops.unpermute_combine(grouped_dup_outp, pos, dropped, None, w_kept, w_drop, n_tokens,
+                                                addend=_addend)
+        else:
+            assert got_rows == n_tokens * k_full
+            pos_pairs = pos.view(n_tokens, k_full)
+            if partial_skip:
+                # keep the to-be-skipped slot's rows for the next skip step
+                ep_skip_put(cache_key, _ops.unpermute_combine(
+                    grouped_dup_outp, _pick(pos_pairs, const_slot, per_tok, other=False), None, None, None, None,
+                    n_tokens))
+            if k_full == 2:
+                expert_out = _ops.unpermute_combine(grouped_dup_outp, pos_pairs[:, 0], grouped_dup_outp,
+                                                    pos_pairs[:, 1], w_pairs[:, 0], w_pairs[:, 1], n_tokens,
+                                                    addend=_addend)
+            else:
+                assert k_full == 1, "num_experts_per_tok must be 1 or 2"
+                expert_out = _ops.unpermute_combine(grouped_dup_outp, pos_pairs[:, 0], None, None, w_pairs[:, 0],
+                                                    None, n_tokens, addend=_addend)
+    assert expert_out.shape == inp.shape, f"{expert_out.shape} != {inp.shape}"
+    return expert_out

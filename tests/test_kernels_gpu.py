@@ -38,8 +38,9 @@ def test_router_fp32_bit_exact_routing(cuda_device, n, h, e, renorm):
 
 @pytest.mark.parametrize("n,h,e", [(512, 1152, 8), (2048, 1792, 16), (4096, 1408, 16)])
 def test_router_bf16_against_oracle(cuda_device, n, h, e):
-    """bf16: logits may differ from the oracle's by one bf16 ulp (summation
-    order); every routing mismatch must be such a near-tie."""
+    """bf16: logits may differ from the oracle's by one bf16 ulp (plus the
+    fp32 summation-order error, which dominates for logits near zero); every
+    routing mismatch must be such a near-tie."""
     ops = _ops()
     g = torch.Generator().manual_seed(n + h + e)
     x = torch.randn(n, h, generator=g).bfloat16()
@@ -50,7 +51,7 @@ def test_router_bf16_against_oracle(cuda_device, n, h, e):
     # logits within one bf16 ulp of the oracle's
     lf, lo = logits.float(), logits_o.float()
     ulp = torch.maximum(lo.abs(), torch.tensor(2.0 ** -126)).log2().floor().exp2() * 2.0 ** -7
-    assert ((lf - lo).abs() <= ulp + 1e-12).all()
+    assert ((lf - lo).abs() <= ulp + 2e-5).all()
     # the kernel's selection is exactly the oracle's selection on the kernel's own logits
     w_sel, idx_sel = O.top2_from_scores(logits.float().softmax(-1))
     assert torch.equal(idx, idx_sel)
@@ -60,7 +61,7 @@ def test_router_bf16_against_oracle(cuda_device, n, h, e):
     for t in mism.nonzero().flatten().tolist():
         a = set(idx[t].tolist()) ^ set(idx_o[t].tolist())
         vals = lo[t, sorted(a)]
-        assert (vals.max() - vals.min()).abs() <= 2 * ulp[t].max() or set(idx[t].tolist()) == set(idx_o[t].tolist())
+        assert (vals.max() - vals.min()).abs() <= 2 * ulp[t].max() + 4e-5 or set(idx[t].tolist()) == set(idx_o[t].tolist())
     assert mism.float().mean() < 0.02
     assert int(hist.sum()) == 2 * n
 
