@@ -122,7 +122,7 @@ def _exchange_counts_by_owner(counts_key: torch.Tensor, world_size: int, rank: i
     if world_size == 1:
         mine = counts_key.to("cpu", torch.int64).view(1, n_local)
         return mine, mine.clone()
-    gathered = torch.empty((world_size, counts_key.numel()), dtype=counts_key.dtype, device=counts_key.device)
+    gathered = torch.empty((world_size * counts_key.numel(),), dtype=counts_key.dtype, device=counts_key.device)
     dist.all_gather_into_tensor(gathered, counts_key.contiguous())
     host = gathered.to("cpu", torch.int64).view(world_size, world_size, n_local)
     return host[rank].contiguous(), host[:, rank, :].contiguous()

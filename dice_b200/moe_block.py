@@ -1,0 +1,387 @@
+"""The DiT-MoE sparse MoE block on B200 kernels: drop-in for the reference's
+``models.py:159-382`` (``MoEGate``, ``MoeMLP``, ``SparseMoeBlock``) and the
+``ParaMode`` flag bundle (``models.py:34-71``).
+
+Constructor arguments, attribute names and state-dict keys are the
+reference's, so checkpoints load unchanged and ``models.py`` / ``sample_ddp.py``
+can use this class in place of their own.  In eval mode on a CUDA device the
+forward runs the hand-written kernels (fused router, permute, grouped expert
+FFN on the tensor cores, un-permute + weighted combine); there is no CPU or
+PyTorch fallback for that path.  Training (``self.training``) is outside the
+accelerated path and is expressed with ordinary differentiable torch
+operations, as the reference does (``models.py:313-320``).
+"""
+from __future__ import annotations
+
+import contextlib
+import math
+from typing import List, Optional, Sequence
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from . import ops
+from .expertpara.etrim import DummyExpert, trim_module_list
+
+
+class ParaMode:
+    """Parallelism flags handed from the launcher to every block
+    (models.py:34-71)."""
+
+    def __init__(self, ep=False, ep_async=False, sp=False, sp_async=False, num_sampling_steps=None,
+                 ep_async_warm_up=None, strided_sync=None, ep_async_cool_down=None, sp_async_warm_up=None,
+                 ep_async_mode=None):
+        if ep_async:
+            assert ep
+        if sp_async:
+            assert sp
+        self.ep, self.ep_async, self.sp, self.sp_async = ep, ep_async, sp, sp_async
+        self.dp = not ep and not sp
+        self.num_sampling_steps = num_sampling_steps
+        self.ep_async_warm_up = ep_async_warm_up
+        self.strided_sync = strided_sync
+        self.sp_async_warm_up = sp_async_warm_up
+        self.ep_async_cool_down = ep_async_cool_down
+        self.ep_async_mode = ep_async_mode
+
+    def verbose(self):
+        if self.dp:
+            return "DP"
+        name = []
+        if self.ep:
+            name.append("DiEP" if self.ep_async else "EP")
+        if self.sp:
+            name.append("DF" if self.sp_async else "SP")
+        return "+".join(name)
+
+
+def _scope(name: str):
+    from .expertpara import diep
+
+    prof = diep._profiler()
+    return prof.scope(name) if prof is not None else contextlib.nullcontext()
+
+
+def _compute_dtype(x: torch.Tensor) -> torch.dtype:
+    """bf16 for 16-bit inputs and inside an autocast region (where the
+    reference's linears run in 16 bits); fp32 inputs outside autocast take the
+    fp32 kernels."""
+    if x.dtype == torch.float32 and not torch.is_autocast_enabled():
+        return torch.float32
+    return torch.bfloat16
+
+
+def layer_is_async(para_mode, layer_idx, total_layers) -> bool:
+    """Which layers use the asynchronous exchange under each selective-sync
+    mode (models.py:328-340)."""
+    if not para_mode.ep_async:
+        return False
+    mode = para_mode.ep_async_mode
+    if mode == "shallow":
+        return layer_idx < total_layers // 2
+    if mode == "deep":
+        return layer_idx >= total_layers // 2
+    if mode == "all":
+        return True
+    if mode == "interleaved":
+        return layer_idx % 2 == 0
+    raise ValueError(f"Invalid ep_async_mode: {mode}")
+
+
+class MoEGate(nn.Module):
+    """Router parameters and (for training / standalone use) the reference's
+    gate arithmetic (models.py:159-217).  ``SparseMoeBlock`` does not call
+    ``forward`` in eval mode on CUDA; it feeds ``weight`` to the fused router
+    kernel."""
+
+    def __init__(self, embed_dim, num_experts=16, num_experts_per_tok=2, aux_loss_alpha=0.01):
+        super().__init__()
+        self.top_k = num_experts_per_tok
+        self.n_routed_experts = num_experts
+        self.scoring_func = "softmax"
+        self.alpha = aux_loss_alpha
+        self.seq_aux = False
+        self.norm_topk_prob = False
+        self.gating_dim = embed_dim
+        self.weight = nn.Parameter(torch.empty((self.n_routed_experts, self.gating_dim)))
+        self.reset_parameters()
+
+    def reset_parameters(self) -> None:
+        nn.init.kaiming_uniform_(self.weight, a=math.sqrt(5))
+
+    def forward(self, hidden_states):
+        bsz, seq_len, h = hidden_states.shape
+        x2d = hidden_states.reshape(-1, h)
+        if x2d.is_cuda and not self.training and self.top_k == 2:
+            cd = _compute_dtype(x2d)
+            idx, w, _, _ = ops.router_top2(x2d.to(cd), self.weight.to(cd), renorm=self.norm_topk_prob)
+            return idx, w, None
+        scores = F.linear(x2d, self.weight, None).softmax(dim=-1)
+        topk_weight, topk_idx = torch.topk(scores, k=self.top_k, dim=-1, sorted=False)
+        if self.top_k > 1 and self.norm_topk_prob:
+            topk_weight = topk_weight / (topk_weight.sum(dim=-1, keepdim=True) + 1e-20)
+        aux_loss = None
+        if self.training and self.alpha > 0.0:  # models.py:199-214 (token-level auxiliary loss)
+            mask_ce = F.one_hot(topk_idx.view(-1), num_classes=self.n_routed_experts)
+            ce = mask_ce.float().mean(0)
+            aux_loss = (scores.mean(0) * ce * self.n_routed_experts).sum() * self.alpha
+        return topk_idx, topk_weight, aux_loss
+
+
+class AddAuxiliaryLoss(torch.autograd.Function):
+    """Attach the auxiliary loss's gradient to the block output (models.py:220-237)."""
+
+    @staticmethod
+    def forward(ctx, x, loss):
+        assert loss.numel() == 1
+        ctx.dtype = loss.dtype
+        ctx.required_aux_loss = loss.requires_grad
+        return x
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        grad_loss = torch.ones(1, dtype=ctx.dtype, device=grad_output.device) if ctx.required_aux_loss else None
+        return grad_output, grad_loss
+
+
+class MoeMLP(nn.Module):
+    """One SwiGLU expert: ``down_proj(silu(gate_proj(x)) * up_proj(x))``, no
+    biases (models.py:240-273).  The module's own ``forward`` is plain torch
+    (used for training and by callers that run a single expert); the block runs
+    all experts together through the grouped FFN kernel."""
+
+    def __init__(self, hidden_size, intermediate_size, pretraining_tp=2):
+        super().__init__()
+        self.hidden_size = hidden_size
+        self.intermediate_size = intermediate_size
+        self.gate_proj = nn.Linear(hidden_size, intermediate_size, bias=False)
+        self.up_proj = nn.Linear(hidden_size, intermediate_size, bias=False)
+        self.down_proj = nn.Linear(intermediate_size, hidden_size, bias=False)
+        self.act_fn = nn.SiLU()
+        self.pretraining_tp = pretraining_tp
+
+    def forward(self, x):
+        # the column/row slicing of models.py:253-269 is the same sum in another order
+        return self.down_proj(self.act_fn(self.gate_proj(x)) * self.up_proj(x))
+
+
+class GeluMLP(nn.Module):
+    """Two-matrix expert ``fc2(gelu_tanh(fc1(x)))`` without biases: the expert
+    shape of the synthetic benchmark configurations; it has no counterpart in
+    the reference."""
+
+    def __init__(self, hidden_size, intermediate_size):
+        super().__init__()
+        self.hidden_size = hidden_size
+        self.intermediate_size = intermediate_size
+        self.fc1 = nn.Linear(hidden_size, intermediate_size, bias=False)
+        self.fc2 = nn.Linear(intermediate_size, hidden_size, bias=False)
+
+    def forward(self, x):
+        return self.fc2(F.gelu(self.fc1(x), approximate="tanh"))
+
+
+class ExpertPack:
+    """Kernel-side view of a list of experts: stacked first-layer weights
+    (gate/up interleaved for SwiGLU) and second-layer weights of the experts
+    this rank holds, in local-slot order, rebuilt when a parameter changes."""
+
+    def __init__(self, experts: Sequence[nn.Module]):
+        self._experts = experts
+        self._built = {}
+        self.status = None
+
+    def _local(self) -> List[nn.Module]:
+        return [e for e in self._experts if not isinstance(e, DummyExpert)]
+
+    @staticmethod
+    def _params(e: nn.Module):
+        if isinstance(e, MoeMLP):
+            return "swiglu", (e.gate_proj.weight, e.up_proj.weight, e.down_proj.weight)
+        if isinstance(e, GeluMLP):
+            return "gelu_tanh", (e.fc1.weight, e.fc2.weight)
+        raise TypeError(f"cannot pack expert of type {type(e).__name__}")
+
+    def get(self, dtype: torch.dtype):
+        local = self._local()
+        sig = tuple((p.data_ptr(), p._version) for e in local for p in self._params(e)[1])
+        hit = self._built.get(dtype)
+        if hit is not None and hit[0] == sig:
+            return hit[1]
+        act = self._params(local[0])[0]
+        dev = self._params(local[0])[1][0].device
+        if dev.type != "cuda":
+            raise RuntimeError("dice_b200 expert weights must live on a CUDA device (no CPU fallback)")
+        with torch.no_grad():
+            if act == "swiglu":
+                ffn = local[0].intermediate_size
+                w1 = torch.stack([ops.pack_w13(e.gate_proj.weight.to(dtype), e.up_proj.weight.to(dtype)) for e in local])
+                w2 = torch.stack([e.down_proj.weight.to(dtype) for e in local]).contiguous()
+            else:
+                ffn = local[0].intermediate_size
+                w1 = torch.stack([e.fc1.weight.to(dtype) for e in local]).contiguous()
+                w2 = torch.stack([e.fc2.weight.to(dtype) for e in local]).contiguous()
+            if self.status is None:
+                self.status = torch.zeros(1, dtype=torch.int32, device=dev)
+        built = (act, ffn, w1, w2)
+        self._built[dtype] = (sig, built)
+        return built
+
+    def run_offsets(self, rows: torch.Tensor, seg_offsets: torch.Tensor, seg_slab: Optional[torch.Tensor] = None):
+        act, ffn, w1, w2 = self.get(rows.dtype)
+        return ops.grouped_ffn(rows, w1, w2, seg_offsets, act, ffn, status=self.status, seg_slab=seg_slab)
+
+    def run_segments(self, rows: torch.Tensor, seg_counts: Sequence[int], seg_slab: Sequence[int]):
+        """Segments given as host-side counts (the expert-parallel receive layout)."""
+        offs = [0]
+        for c in seg_counts:
+            offs.append(offs[-1] + c)
+        seg = torch.tensor(offs, dtype=torch.int32, device=rows.device)
+        slab = torch.tensor(list(seg_slab), dtype=torch.int32, device=rows.device)
+        return self.run_offsets(rows, seg, slab)
+
+    def check(self):
+        if self.status is not None:
+            ops.check_status(self.status, "grouped expert FFN")
+
+
+class SparseMoeBlock(nn.Module):
+    """Routed experts + always-on shared expert (models.py:276-382).
+
+    Same constructor as the reference.  Two keyword-only extensions select the
+    synthetic benchmark variant: ``expert_act="gelu_tanh"`` builds two-matrix
+    GELU-tanh experts, ``shared_expert=False`` drops the shared expert;
+    ``self.gate.norm_topk_prob = True`` renormalises the top-2 weights
+    (the reference's switch, models.py:170)."""
+
+    def __init__(self, embed_dim, mlp_ratio=4, num_experts=16, num_experts_per_tok=2, pretraining_tp=2,
+                 layer_idx=None, total_layers=None, para_mode: ParaMode = None, *, expert_act="swiglu",
+                 shared_expert=True):
+        super().__init__()
+        assert para_mode is not None
+        assert expert_act in ("swiglu", "gelu_tanh")
+        self.num_experts_per_tok = num_experts_per_tok
+        self.expert_act = expert_act
+        inter = mlp_ratio * embed_dim
+
+        def make(size):
+            return MoeMLP(embed_dim, size, pretraining_tp) if expert_act == "swiglu" else GeluMLP(embed_dim, size)
+
+        self.experts = nn.ModuleList([make(inter) for _ in range(num_experts)])
+        if para_mode.ep:
+            self.experts = trim_module_list(self.experts, num_experts)  # models.py:288-290
+        self.gate = MoEGate(embed_dim=embed_dim, num_experts=num_experts, num_experts_per_tok=num_experts_per_tok)
+        self.n_shared_experts = 2 if shared_expert else None
+        if self.n_shared_experts is not None:
+            self.shared_experts = make(embed_dim * self.n_shared_experts)
+        self.layer_idx = layer_idx
+        self.total_layers = total_layers
+        self.para_mode = para_mode
+        self.num_experts = num_experts
+        self.experts._dice_pack = ExpertPack(self.experts)
+        self._shared_pack = ExpertPack([self.shared_experts]) if self.n_shared_experts is not None else None
+        self._gate_cast = {}
+        self._seg_cache = {}
+
+    # -- helpers ----------------------------------------------------------------
+    def _gate_weight(self, dtype):
+        w = self.gate.weight
+        sig = (w.data_ptr(), w._version)
+        hit = self._gate_cast.get(dtype)
+        if hit is None or hit[0] != sig:
+            hit = (sig, w.detach().to(dtype).contiguous())
+            self._gate_cast[dtype] = hit
+        return hit[1]
+
+    def _async_layer(self) -> bool:
+        return layer_is_async(self.para_mode, self.layer_idx, self.total_layers)
+
+    def _segment_all(self, n_tokens: int, device) -> torch.Tensor:
+        key = (n_tokens, str(device))
+        seg = self._seg_cache.get(key)
+        if seg is None:
+            if len(self._seg_cache) > 16:
+                self._seg_cache.clear()
+            seg = torch.tensor([0, n_tokens], dtype=torch.int32, device=device)
+            self._seg_cache[key] = seg
+        return seg
+
+    def check_status(self):
+        """Raise if a kernel of this block reported an expired wait (synchronises)."""
+        self.experts._dice_pack.check()
+        if self._shared_pack is not None:
+            self._shared_pack.check()
+
+    # -- forward ------------------------------------------------------------------
+    def forward(self, hidden_states):
+        if self.training:
+            return self._forward_train(hidden_states)
+        if not hidden_states.is_cuda:
+            raise RuntimeError("dice_b200.SparseMoeBlock runs on CUDA tensors only (no CPU fallback)")
+        return self._forward_infer(hidden_states)
+
+    @torch.no_grad()
+    def _forward_infer(self, hidden_states):
+        orig_shape, orig_dtype = hidden_states.shape, hidden_states.dtype
+        h = orig_shape[-1]
+        cd = _compute_dtype(hidden_states)
+        x = hidden_states.reshape(-1, h)
+        x = x.contiguous() if x.dtype == cd else x.to(cd)
+        n_tokens = x.shape[0]
+        assert self.num_experts_per_tok == 2, "the fused router selects exactly two experts per token"
+        with _scope("moe.gate"):
+            topk_idx, topk_weight, hist, _ = ops.router_top2(x, self._gate_weight(cd), renorm=self.gate.norm_topk_prob)
+        shared_out = None
+        if self._shared_pack is not None:
+            with _scope("moe.mlp_shared"):
+                shared_out = self._shared_pack.run_offsets(x, self._segment_all(n_tokens, x.device))
+        if not self.para_mode.ep:
+            y = self.moe_infer(x, topk_idx.view(-1), topk_weight.view(-1, 1), _addend=shared_out)
+        else:
+            from .expertpara.diep import ep_skip_enabled, ep_skip_mask, ep_skip_now
+            from .expertpara.ep_fwd import moe_infer_ep
+
+            partial_skip = ep_skip_enabled()
+            y = moe_infer_ep(
+                inp=x, experts=self.experts, flat_expert_indices=topk_idx.view(-1),
+                flat_expert_weights=topk_weight.view(-1, 1), num_experts_per_tok=self.num_experts_per_tok,
+                skip_mask=ep_skip_mask(topk_idx.numel()) if partial_skip else None,
+                skip_now=ep_skip_now(self.layer_idx) if partial_skip else None,
+                async_op=self._async_layer(), cache_key=self.layer_idx, _addend=shared_out)
+        y = y.view(*orig_shape)
+        return y if y.dtype == orig_dtype else y.to(orig_dtype)
+
+    @torch.no_grad()
+    def moe_infer(self, x, flat_expert_indices, flat_expert_weights, _addend=None):
+        """Single-device dispatch -> experts -> weighted combine
+        (models.py:361-382), as four kernel launches and no host sync."""
+        assert not self.para_mode.ep
+        n_tokens = x.shape[0]
+        k = self.num_experts_per_tok
+        pos, seg, _ = ops.permute_plan(flat_expert_indices, self.num_experts)
+        rows = ops.permute_rows(x, pos, k)
+        with _scope("moe.mlp"):
+            y_rows = self.experts._dice_pack.run_offsets(rows, seg)
+        w = flat_expert_weights.view(n_tokens, k)
+        w = w if w.dtype == torch.float32 else w.float()
+        pp = pos.view(n_tokens, k)
+        return ops.unpermute_combine(y_rows, pp[:, 0], y_rows, pp[:, 1], w[:, 0], w[:, 1], n_tokens, addend=_addend)
+
+    def _forward_train(self, hidden_states):
+        """models.py:313-320 with differentiable torch operations."""
+        identity, orig_shape = hidden_states, hidden_states.shape
+        topk_idx, topk_weight, aux_loss = self.gate(hidden_states)
+        x = hidden_states.view(-1, orig_shape[-1]).repeat_interleave(self.num_experts_per_tok, dim=0)
+        flat = topk_idx.view(-1)
+        y = torch.empty_like(x)
+        for i, expert in enumerate(self.experts):
+            sel = flat == i
+            if bool(sel.any()):
+                y[sel] = expert(x[sel]).to(y.dtype)
+        y = (y.view(*topk_weight.shape, -1) * topk_weight.unsqueeze(-1)).sum(dim=1).view(*orig_shape)
+        if aux_loss is not None:
+            y = AddAuxiliaryLoss.apply(y, aux_loss)
+        if self.n_shared_experts is not None:
+            y = y + self.shared_experts(identity)
+        return y
