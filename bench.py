@@ -1,0 +1,393 @@
+#!/usr/bin/env python
+"""Benchmark of the DiT-MoE sparse MoE block (the hot path of DICE) on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--variant gelu_tanh|swiglu] [--layers L]
+
+One *step* is one pass of a batch of tokens through the MoE blocks of all
+``L`` layers of the model (28 for DiT-XL/2), each layer with its own weights.
+``value`` is tokens per second through one MoE block, summed over all GPUs:
+``n_gpus * tokens_per_gpu * L / step_time``.
+
+* N = 1: the single-GPU DiT-XL/2 configuration (batch 32 x 2 CFG, 256 tokens
+  per image = 16384 tokens, hidden 1152, 8 experts, top-2).
+* N > 1 (under torchrun): the expert-parallel configuration (8 experts sharded
+  over the ranks, per-GPU batch 16 x 2 CFG = 8192 tokens, synchronous
+  all-to-all dispatch/combine); per-GPU work is fixed ("weak" scaling).
+
+Inputs are synthetic (seeded Gaussian activations, N(0, 0.02) weights).  The
+expert shape follows the benchmark configuration's wording by default
+(``--variant gelu_tanh``: fc1, GELU-tanh, fc2, renormalised top-2 weights, no
+shared expert); ``--variant swiglu`` measures the block exactly as the
+reference computes it (SwiGLU experts, un-normalised weights, shared expert).
+
+``--impl reference`` times the CPU restatement of the reference path (the
+oracle) on the host cores, on a bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+HIDDEN = 1152
+EXPERTS = 8
+MLP_RATIO = 4
+TOKENS_PER_IMAGE = 256
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+# dram__bytes_read.sum + dram__bytes_write.sum of one grouped-GEMM launch of this workload,
+# scaled from the ncu capture summarised under profiles/ (None until a capture exists)
+GEMM_TRAFFIC_BYTES = None
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=40)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--variant", default="gelu_tanh", choices=["gelu_tanh", "swiglu"])
+    ap.add_argument("--layers", type=int, default=28)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    return ap.parse_args()
+
+
+def workload(n_gpus: int):
+    images = 32 if n_gpus == 1 else 16
+    tokens = images * 2 * TOKENS_PER_IMAGE
+    name = ("DiT-XL/2-MoE MoE blocks, 1 GPU: batch 32 x2 CFG x 256 tokens" if n_gpus == 1 else
+            f"DiT-XL/2-MoE MoE blocks, expert parallel over {n_gpus} GPUs: per-GPU batch 16 x2 CFG x 256 tokens, sync all-to-all")
+    return tokens, name
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return json.load(f), "measured"
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+# --------------------------------------------------------------------------- #
+# clocks
+# --------------------------------------------------------------------------- #
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks / throttle reasons of one GPU while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.lines, self.proc, self.thread = index, [], None, None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=lambda: [self.lines.append(l) for l in self.proc.stdout], daemon=True)
+        self.thread.start()
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# --------------------------------------------------------------------------- #
+# model construction
+# --------------------------------------------------------------------------- #
+
+
+def build_blocks(layers, variant, para_mode, device, seed=0):
+    from dice_b200.moe_block import SparseMoeBlock
+
+    blocks = []
+    gen = torch.Generator(device=device).manual_seed(seed)
+    for layer in range(layers):
+        with torch.device(device):
+            blk = SparseMoeBlock(HIDDEN, MLP_RATIO, EXPERTS, 2, pretraining_tp=1, layer_idx=layer, total_layers=layers,
+                                 para_mode=para_mode, expert_act=variant, shared_expert=(variant == "swiglu"))
+        blk = blk.to(torch.bfloat16).eval()
+        for p in blk.parameters():
+            p.data.normal_(0.0, 0.02, generator=gen)
+        blk.gate.norm_topk_prob = variant == "gelu_tanh"
+        blocks.append(blk)
+    return blocks
+
+
+def kernels_per_block(variant, ep):
+    # router, 3 plan kernels, row gather, 2 grouped GEMMs, combine (+ 2 GEMMs of the shared expert)
+    n = 1 + 3 + 1 + 2 + 1
+    if variant == "swiglu":
+        n += 2
+    return n
+
+
+def ffn_flops(tokens, variant):
+    """Algorithmic FLOPs of one grouped-GEMM launch pair (routed experts only): 2 rows per token."""
+    rows = 2 * tokens
+    per_row = (6 if variant == "swiglu" else 4) * HIDDEN * MLP_RATIO * HIDDEN
+    return rows * per_row
+
+
+# --------------------------------------------------------------------------- #
+# our arm
+# --------------------------------------------------------------------------- #
+
+
+def run_ours(args):
+    import torch.distributed as dist
+
+    from dice_b200.moe_block import ExpertPack, ParaMode
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.gpus > 1 and world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} needs torchrun with {args.gpus} ranks (WORLD_SIZE={world})")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    ep = world > 1
+    if ep:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=device)
+    tokens, wl_name = workload(world)
+    para_mode = ParaMode(ep=ep)
+    blocks = build_blocks(args.layers, args.variant, para_mode, device)
+    gen = torch.Generator(device=device).manual_seed(1000 + rank)
+    # one distinct input per layer: together with >150 MB of expert weights per layer the working set
+    # between two uses of any buffer is far larger than the 126 MB L2
+    xs = [torch.randn(tokens // TOKENS_PER_IMAGE, TOKENS_PER_IMAGE, HIDDEN, generator=gen, device=device).bfloat16()
+          for _ in range(args.layers)]
+    host_in = torch.randn(tokens // TOKENS_PER_IMAGE, TOKENS_PER_IMAGE, HIDDEN).bfloat16().pin_memory()
+    host_out = torch.empty_like(host_in).pin_memory()
+    dev_in = torch.empty_like(xs[0])
+
+    def step_device():
+        y = None
+        for blk, x in zip(blocks, xs):
+            y = blk(x)
+        return y
+
+    def step_e2e():
+        dev_in.copy_(host_in, non_blocking=True)
+        y = None
+        for blk in blocks:
+            y = blk(dev_in)
+        host_out.copy_(y, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    def barrier():
+        if ep:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps, sampler=None):
+        barrier()
+        if sampler is not None:
+            sampler.start()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        barrier()
+        clocks = sampler.stop() if sampler is not None else None
+        ms = torch.tensor([e0.elapsed_time(e1)], device=device)
+        if ep:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item()), clocks
+
+    for _ in range(max(args.warmup, 3)):
+        step_device()
+    # FFN launch durations, measured on the launching stream inside the timed region
+    ExpertPack.timing = []
+    total_ms, clocks = timed(step_device, args.steps, ClockSampler(local_rank))
+    ffn_events = ExpertPack.timing
+    ExpertPack.timing = None
+    torch.cuda.synchronize()
+    routed = [s.elapsed_time(e) for tag, s, e in ffn_events if tag == "routed"]
+    for blk in blocks:
+        blk.check_status()
+
+    for _ in range(2):
+        step_e2e()
+    e2e_ms, _ = timed(step_e2e, args.steps)
+
+    ms_per_step = total_ms / args.steps
+    value = world * tokens * args.layers / (ms_per_step * 1e-3)
+    e2e_value = world * tokens * args.layers / (e2e_ms / args.steps * 1e-3)
+
+    pk, pk_src = peaks()
+    peak_tf = pk.get("bf16_tflops_sustained", FALLBACK_PEAKS["bf16_tflops_sustained"])
+    # one FFN call = 2 grouped-GEMM launches; rows per rank = 2 * tokens under uniform routing
+    gemm_launches = 2 * len(routed)
+    gemm_ms = sum(routed) / max(gemm_launches, 1)
+    flops_per_launch = ffn_flops(tokens, args.variant) / 2
+    achieved = flops_per_launch / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else 0.0
+    roofline = {"kernel": "grouped_gemm_kernel (tcgen05, fc1+fc2 of the routed experts)", "bound": "tensor",
+                "achieved": round(achieved, 1), "peak": peak_tf, "unit": "TFLOP/s", "frac": round(achieved / peak_tf, 4),
+                "peak_source": f"bf16_tflops_sustained of {pk_src}", "avg_launch_ms": round(gemm_ms, 4),
+                "launches_timed": gemm_launches, "flops_per_launch": flops_per_launch, "traffic": GEMM_TRAFFIC_BYTES}
+
+    line = {
+        "metric": "moe_block_tokens_per_s", "value": round(value, 1), "unit": "tokens/s", "n_gpus": world,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(ms_per_step, 4),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": wl_name, "variant": args.variant, "layers_per_step": args.layers, "tokens_per_gpu": tokens,
+                   "hidden": HIDDEN, "experts": EXPERTS, "top_k": 2, "ffn": MLP_RATIO * HIDDEN,
+                   "parallelism": "ep%d" % world if ep else "single",
+                   "l2": "per-layer inputs and weights (>150 MB per layer) exceed the 126 MB L2; no explicit flush"},
+        "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "ms_per_step": round(e2e_ms / args.steps, 4),
+                "h2d_bytes_per_step": host_in.numel() * 2, "d2h_bytes_per_step": host_out.numel() * 2},
+        "gpu_launches": kernels_per_block(args.variant, ep) * args.layers * args.steps,
+        "clocks": clocks, "roofline": roofline,
+        "tokens_per_s_per_gpu": round(value / world, 1),
+    }
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        line["cpu_baseline"] = cpu_baseline(blocks, xs, args.variant, budget_s=12.0)
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if ep:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+# --------------------------------------------------------------------------- #
+# CPU baseline / reference arm (the oracle, timed; never the product path)
+# --------------------------------------------------------------------------- #
+
+
+def _oracle_weights(blk, variant):
+    sd = {k: v.detach().float().cpu() for k, v in blk.state_dict().items()}
+    if variant == "swiglu":
+        ex = [tuple(sd[f"experts.{i}.{p}.weight"] for p in ("gate_proj", "up_proj", "down_proj")) for i in range(EXPERTS)]
+        sh = tuple(sd[f"shared_experts.{p}.weight"] for p in ("gate_proj", "up_proj", "down_proj"))
+    else:
+        ex = [tuple(sd[f"experts.{i}.{p}.weight"] for p in ("fc1", "fc2")) for i in range(EXPERTS)]
+        sh = None
+    return sd["gate.weight"], ex, sh
+
+
+def _oracle_block(x, weights, variant):
+    from oracle import moe_oracle as O
+
+    wg, ex, sh = weights
+    return O.moe_block_forward(x, wg, ex, sh, act=variant, renorm=(variant == "gelu_tanh"))["out"]
+
+
+def cpu_baseline(blocks, xs, variant, budget_s):
+    """The oracle (fp32, all host threads) on whole blocks of the same workload until ~budget_s elapsed."""
+    threads = torch.get_num_threads()
+    weights = _oracle_weights(blocks[0], variant)
+    x = xs[0].float().cpu()
+    with torch.no_grad():
+        _oracle_block(x[:2], weights, variant)  # warm-up on a slice
+        t0 = time.perf_counter()
+        n = 0
+        while True:
+            _oracle_block(x, weights, variant)
+            n += 1
+            if time.perf_counter() - t0 > budget_s or n >= 8:
+                break
+        dt = time.perf_counter() - t0
+    tokens = x.shape[0] * x.shape[1]
+    return {"value": round(tokens * n / dt, 1), "unit": "tokens/s", "cores": threads, "kind": "port",
+            "sample": f"{n} full MoE block(s) of layer 0 ({tokens} tokens, fp32, torch CPU, {threads} threads, "
+                      f"os.cpu_count()={os.cpu_count()})"}
+
+
+def run_reference(args):
+    """The reference arm: the CPU restatement of the reference path, on the host cores."""
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if rank != 0:
+        return
+    tokens, wl_name = workload(world)
+    threads = torch.get_num_threads()
+    g = torch.Generator().manual_seed(0)
+    f = MLP_RATIO * HIDDEN
+    rn = lambda *s: torch.randn(*s, generator=g) * 0.02
+    wg = rn(EXPERTS, HIDDEN)
+    if args.variant == "swiglu":
+        ex = [(rn(f, HIDDEN), rn(f, HIDDEN), rn(HIDDEN, f)) for _ in range(EXPERTS)]
+        sh = (rn(2 * HIDDEN, HIDDEN), rn(2 * HIDDEN, HIDDEN), rn(HIDDEN, 2 * HIDDEN))
+    else:
+        ex = [(rn(f, HIDDEN), rn(HIDDEN, f)) for _ in range(EXPERTS)]
+        sh = None
+    x = torch.randn(tokens // TOKENS_PER_IMAGE, TOKENS_PER_IMAGE, HIDDEN, generator=g)
+    # bounded sample: one step = ONE block (not all layers) over the full token batch
+    with torch.no_grad():
+        for _ in range(min(args.warmup, 2)):
+            _oracle_block(x, (wg, ex, sh), args.variant)
+        steps = min(args.steps, 10)
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            _oracle_block(x, (wg, ex, sh), args.variant)
+        dt = time.perf_counter() - t0
+    value = tokens * steps / dt
+    sample = (f"{steps} timed block passes of {tokens} tokens (1 layer per step instead of {args.layers}); fp32 torch CPU, "
+              f"{threads} threads, os.cpu_count()={os.cpu_count()}")
+    line = {
+        "impl": "reference", "metric": "moe_block_tokens_per_s", "value": round(value, 1), "unit": "tokens/s",
+        "n_gpus": world, "steps": steps, "warmup": min(args.warmup, 2), "ms_per_step": round(dt / steps * 1e3, 3),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": wl_name, "variant": args.variant, "layers_per_step": 1, "tokens_per_gpu": tokens,
+                   "hidden": HIDDEN, "experts": EXPERTS, "top_k": 2, "ffn": f},
+        "cpu_baseline": {"value": round(value, 1), "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": round(value, 1), "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        if not torch.cuda.is_available():
+            raise SystemExit("bench.py measures the CUDA path and needs a GPU (there is no CPU fallback); "
+                             "use --impl reference for the CPU baseline")
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -187,10 +187,15 @@ class ExpertPack:
     (gate/up interleaved for SwiGLU) and second-layer weights of the experts
     this rank holds, in local-slot order, rebuilt when a parameter changes."""
 
-    def __init__(self, experts: Sequence[nn.Module]):
+    # when set to a list, every FFN call appends (tag, start_event, end_event) recorded on the
+    # launching stream (used by the benchmark to time the grouped-GEMM launches in place)
+    timing = None
+
+    def __init__(self, experts: Sequence[nn.Module], tag: str = "routed"):
         self._experts = experts
         self._built = {}
         self.status = None
+        self.tag = tag
 
     def _local(self) -> List[nn.Module]:
         return [e for e in self._experts if not isinstance(e, DummyExpert)]
@@ -230,7 +235,14 @@ class ExpertPack:
 
     def run_offsets(self, rows: torch.Tensor, seg_offsets: torch.Tensor, seg_slab: Optional[torch.Tensor] = None):
         act, ffn, w1, w2 = self.get(rows.dtype)
-        return ops.grouped_ffn(rows, w1, w2, seg_offsets, act, ffn, status=self.status, seg_slab=seg_slab)
+        if ExpertPack.timing is None:
+            return ops.grouped_ffn(rows, w1, w2, seg_offsets, act, ffn, status=self.status, seg_slab=seg_slab)
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        out = ops.grouped_ffn(rows, w1, w2, seg_offsets, act, ffn, status=self.status, seg_slab=seg_slab)
+        end.record()
+        ExpertPack.timing.append((self.tag, start, end))
+        return out
 
     def run_segments(self, rows: torch.Tensor, seg_counts: Sequence[int], seg_slab: Sequence[int]):
         """Segments given as host-side counts (the expert-parallel receive layout)."""
@@ -280,7 +292,7 @@ class SparseMoeBlock(nn.Module):
         self.para_mode = para_mode
         self.num_experts = num_experts
         self.experts._dice_pack = ExpertPack(self.experts)
-        self._shared_pack = ExpertPack([self.shared_experts]) if self.n_shared_experts is not None else None
+        self._shared_pack = ExpertPack([self.shared_experts], tag="shared") if self.n_shared_experts is not None else None
         self._gate_cast = {}
         self._seg_cache = {}
 
