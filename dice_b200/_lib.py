@@ -26,6 +26,7 @@ SIGNATURES = {
         c_int,
         [c_void_p, c_int64, c_int, c_void_p, c_size_t, c_void_p, c_void_p, c_void_p, c_void_p],
     ),
+    "dice_permute_plan_static": (c_int, [c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
     "dice_permute_rows": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_void_p, c_void_p]),
     "dice_unpermute_combine": (
         c_int,

@@ -5,7 +5,14 @@
 // The plan works on 4-byte indices only (a few hundred KB); the two row movers
 // read and write every activation byte exactly once and are bounded by HBM
 // bandwidth.
+#include <mutex>
+
 #include "common.cuh"
+
+// Scratch of dice_permute_plan_static: lives in the library image, so every GPU that loads the
+// library holds these 256 KB until the process exits.  Host code may only use this name to ask
+// for the array's device address (cudaGetSymbolAddress); it is not itself a device pointer.
+static __device__ __align__(256) int g_plan_static_scratch[DICE_PLAN_STATIC_MAX_INTS];
 
 namespace {
 
@@ -223,6 +230,46 @@ extern "C" int dice_permute_plan(const int64_t* flat_idx, int64_t n_rows, int n_
   plan_count_kernel<<<chunks, kChunkRows, 0, s>>>(flat_idx, n_rows, n_experts, chunk_hist);
   plan_scan_kernel<<<1, 2 * kMaxExperts, 0, s>>>(chunk_hist, chunks, n_experts, out_seg_offsets);
   plan_rank_kernel<<<chunks, kChunkRows, 0, s>>>(flat_idx, n_rows, n_experts, chunk_hist, out_pos, out_order);
+  return cudaGetLastError() == cudaSuccess ? DICE_OK : DICE_ERR_CUDA;
+}
+
+// Device address of g_plan_static_scratch on the current device, looked up once per device.
+static int static_plan_scratch(int** out) {
+  constexpr int kMaxDevices = 64;
+  static std::mutex mu;
+  static int* addr[kMaxDevices] = {nullptr};
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return DICE_ERR_CUDA;
+  std::lock_guard<std::mutex> lock(mu);
+  if (addr[dev] == nullptr) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_plan_static_scratch) != cudaSuccess || p == nullptr) return DICE_ERR_CUDA;
+    addr[dev] = static_cast<int*>(p);
+  }
+  *out = addr[dev];
+  return DICE_OK;
+}
+
+extern "C" int dice_permute_plan_static(const int64_t* flat_idx, int64_t n_rows, int n_experts, int32_t* out_pos,
+                                        int32_t* out_order, int32_t* out_seg_offsets, void* stream) {
+  DICE_CHECK_ARG(n_rows >= 0 && out_seg_offsets != nullptr, DICE_ERR_ARG);
+  DICE_CHECK_ARG(n_experts >= 1 && n_experts <= kMaxExperts, DICE_ERR_SHAPE);
+  const int64_t chunks = (n_rows + kChunkRows - 1) / kChunkRows;
+  DICE_CHECK_ARG(chunks * n_experts <= DICE_PLAN_STATIC_MAX_INTS, DICE_ERR_LIMIT);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (n_rows == 0) {
+    DICE_CUDA_OK(cudaMemsetAsync(out_seg_offsets, 0, sizeof(int32_t) * (n_experts + 1), s));
+    return DICE_OK;
+  }
+  DICE_CHECK_ARG(flat_idx && out_pos, DICE_ERR_ARG);
+  int* chunk_hist = nullptr;
+  const int rc = static_plan_scratch(&chunk_hist);
+  if (rc != DICE_OK) return rc;
+  // pass 1 overwrites every cell the later passes read, so nothing has to be cleared between calls
+  plan_count_kernel<<<static_cast<int>(chunks), kChunkRows, 0, s>>>(flat_idx, n_rows, n_experts, chunk_hist);
+  plan_scan_kernel<<<1, 2 * kMaxExperts, 0, s>>>(chunk_hist, static_cast<int>(chunks), n_experts, out_seg_offsets);
+  plan_rank_kernel<<<static_cast<int>(chunks), kChunkRows, 0, s>>>(flat_idx, n_rows, n_experts, chunk_hist, out_pos,
+                                                                    out_order);
   return cudaGetLastError() == cudaSuccess ? DICE_OK : DICE_ERR_CUDA;
 }
 

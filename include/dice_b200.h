@@ -112,6 +112,32 @@ DICE_API int dice_permute_plan(const int64_t* flat_idx, int64_t n_rows, int n_ex
                       size_t scratch_bytes, int32_t* out_pos, int32_t* out_order,
                       int32_t* out_seg_offsets, void* stream);
 
+/* Allocation-free variant of dice_permute_plan; it has no counterpart in the
+ * reference.  It is for hosts that must not allocate device memory while they
+ * run: a serving loop whose memory pool was sized and frozen at start-up, a
+ * plug-in that is handed its caller's buffers and nothing else, or an
+ * embedding application that enforces a fixed memory budget and treats any
+ * cudaMalloc on the request path as an error.  Such a caller still passes the
+ * input and the three outputs, but no scratch: the per-chunk histograms live
+ * in a fixed 256 KB array inside the library (present on every GPU that loads
+ * it, until the process exits).
+ *   limit: ceil(n_rows / 256) * n_experts <= DICE_PLAN_STATIC_MAX_INTS
+ *          (2 M rows at 8 experts, 262144 rows at 64); larger requests return
+ *          DICE_ERR_LIMIT and enqueue nothing.
+ *   The first call on a device looks up the array's address (once per device,
+ *   with that device current); that first call should come before any stream
+ *   capture.  The call never calls cudaMalloc, cudaFree or an allocating
+ *   library routine.
+ *   All calls share the one array, which keeps the previous call's contents;
+ *   every cell that is read is rewritten first by the same call, so nothing
+ *   needs clearing, but two calls that overlap on the GPU (different streams,
+ *   or host threads without ordering between them) race on it: serialise them.
+ * Outputs are identical to dice_permute_plan's. */
+#define DICE_PLAN_STATIC_MAX_INTS 65536
+DICE_API int dice_permute_plan_static(const int64_t* flat_idx, int64_t n_rows, int n_experts,
+                             int32_t* out_pos, int32_t* out_order, int32_t* out_seg_offsets,
+                             void* stream);
+
 /* Row gather into expert-sorted order (ep_fwd.py:107-111, :344-347;
  * models.py:374): out_rows[pos[t*k + s]] = x[t] for s < k.  Negative
  * positions are skipped. */
