@@ -342,6 +342,8 @@ def run_reference(args):
     if rank != 0:
         return
     tokens, wl_name = workload(world)
+    # torchrun exports OMP_NUM_THREADS=1; the reference arm may use every host core
+    torch.set_num_threads(max(1, os.cpu_count() or 1))
     threads = torch.get_num_threads()
     g = torch.Generator().manual_seed(0)
     f = MLP_RATIO * HIDDEN

@@ -51,3 +51,8 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
 }
+
+// internal (not exported): bf16 router on the tensor cores, defined next to the grouped GEMM kernel
+int dice_internal_router_tc(const void* x, const void* w_gate, int64_t n_tokens, int hidden, int n_experts, int renorm,
+                            int64_t* out_idx, float* out_w, int32_t* out_hist, void* out_logits,
+                            cudaStream_t stream);

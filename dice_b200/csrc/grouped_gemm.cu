@@ -26,6 +26,7 @@
 #include <cuda.h>
 
 #include "common.cuh"
+#include "select.cuh"
 
 namespace {
 
@@ -33,7 +34,8 @@ constexpr int BM = 128;          // rows per tile (tensor-memory lanes)
 constexpr int BN = 256;          // weight rows per tile (accumulator columns)
 constexpr int BK = 64;           // reduction elements per ring slot (128 bytes of bf16)
 constexpr int UMMA_K = 16;       // reduction elements per tcgen05.mma
-constexpr int kStages = 4;
+constexpr int kStages = 4;      // ring slots when the weight box is full-size (48 KB per slot)
+constexpr int kMaxStages = 10;  // ring slots when the weight box is small (router: 18 KB per slot)
 constexpr int kAccStages = 2;
 constexpr int kTileABytes = BM * BK * 2;
 constexpr int kTileBBytes = BN * BK * 2;
@@ -59,7 +61,18 @@ struct GemmParams {
   __nv_bfloat16* out;
   int64_t ld_out;
   uint32_t* status;
+  int b_box_rows;  // rows of the weight box one TMA load brings (<= BN)
+  int n_stages;    // ring depth: as many slots as fit, between kStages and kMaxStages
+  // router epilogue only
+  int n_experts;
+  int renorm;
+  int64_t* out_idx;
+  float* out_w;
+  int* hist;
+  __nv_bfloat16* logits_out;
 };
+
+constexpr int kEpiRouter = 100;  // internal epilogue: logits -> top-2 (see launch_router_tc)
 
 // ---- PTX wrappers ---------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
@@ -211,22 +224,30 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* aux = smem + kStages * kStageBytes;
+  // a narrow weight box leaves room for a deeper ring in the same shared memory
+  const uint32_t stage_bytes = kTileABytes + ((static_cast<uint32_t>(p.b_box_rows) * (BK * 2) + 1023u) & ~1023u);
+  const int n_stages = p.n_stages;
   uint64_t* bars = reinterpret_cast<uint64_t*>(aux);
-  const uint32_t full_bar = smem_u32(bars);                       // [kStages]
-  const uint32_t empty_bar = smem_u32(bars + kStages);            // [kStages]
-  const uint32_t acc_full_bar = smem_u32(bars + 2 * kStages);     // [kAccStages]
-  const uint32_t acc_empty_bar = smem_u32(bars + 2 * kStages + kAccStages);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 2 * kAccStages);
+  const uint32_t full_bar = smem_u32(bars);                       // [kMaxStages]
+  const uint32_t empty_bar = smem_u32(bars + kMaxStages);         // [kMaxStages]
+  const uint32_t acc_full_bar = smem_u32(bars + 2 * kMaxStages);  // [kAccStages]
+  const uint32_t acc_empty_bar = smem_u32(bars + 2 * kMaxStages + kAccStages);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kMaxStages + 2 * kAccStages);
   volatile uint32_t* abort_flag = tmem_slot + 1;
   int* s_seg_off = reinterpret_cast<int*>(tmem_slot + 4);         // [n_seg + 1]
   int* s_mprefix = s_seg_off + (kMaxSeg + 1);                     // [n_seg + 1] m-blocks before segment s
   const uint32_t tiles_smem = smem_u32(smem);
+  const uint32_t stage_tx_bytes = kTileABytes + static_cast<uint32_t>(p.b_box_rows) * (BK * 2);
+  int* s_hist = s_mprefix + (kMaxSeg + 1);                        // [64] router histogram
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-  for (int i = threadIdx.x; i <= p.n_seg; i += kThreads) s_seg_off[i] = p.seg_offsets[i];
+  // a null offset table means one segment covering all rows
+  for (int i = threadIdx.x; i <= p.n_seg; i += kThreads)
+    s_seg_off[i] = p.seg_offsets != nullptr ? p.seg_offsets[i] : (i == 0 ? 0 : p.n_rows);
+  if (threadIdx.x < 64) s_hist[threadIdx.x] = 0;
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kStages; ++s) {
+    for (int s = 0; s < n_stages; ++s) {
       mbar_init(full_bar + 8 * s, 1);
       mbar_init(empty_bar + 8 * s, 1);
     }
@@ -266,27 +287,33 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   if (warp == 0) {
     // ---------------- loader ----------------
     if (lane == 0) {
-      int stage = 0, seg = 0;
+      // (tile, k-block) cursor over this CTA's share of the tile list
+      struct Cursor { int64_t t; int kb, seg, row0, wrow0; bool valid; };
+      auto decode = [&](Cursor& c) {
+        c.valid = c.t < total_tiles;
+        if (!c.valid) return;
+        const int mb = static_cast<int>(c.t / p.n_nblk);
+        const int nb = static_cast<int>(c.t - static_cast<int64_t>(mb) * p.n_nblk);
+        while (mb >= s_mprefix[c.seg + 1]) ++c.seg;
+        c.row0 = s_seg_off[c.seg] + (mb - s_mprefix[c.seg]) * BM;
+        const int slab = p.seg_slab != nullptr ? p.seg_slab[c.seg] : c.seg;
+        c.wrow0 = slab * p.w_rows + nb * BN;
+      };
+      auto advance = [&](Cursor& c) {
+        if (++c.kb == p.n_kblk) { c.kb = 0; c.t += gridDim.x; decode(c); }
+      };
+      Cursor cur{static_cast<int64_t>(blockIdx.x), 0, 0, 0, 0, false};
+      decode(cur);
+      int stage = 0;
       uint32_t phase = 0;
-      bool alive = true;
-      for (int64_t t = blockIdx.x; alive && t < total_tiles; t += gridDim.x) {
-        const int mb = static_cast<int>(t / p.n_nblk);
-        const int nb = static_cast<int>(t - static_cast<int64_t>(mb) * p.n_nblk);
-        while (mb >= s_mprefix[seg + 1]) ++seg;
-        const int row0 = s_seg_off[seg] + (mb - s_mprefix[seg]) * BM;
-        const int slab = p.seg_slab != nullptr ? p.seg_slab[seg] : seg;
-        const int wrow0 = slab * p.w_rows + nb * BN;
-        for (int kb = 0; kb < p.n_kblk; ++kb) {
-          if (!mbar_wait(empty_bar + 8 * stage, phase ^ 1u, abort_flag, p.status, DICE_STATUS_WAIT_SMEM_EMPTY)) {
-            alive = false;
-            break;
-          }
-          const uint32_t a_dst = tiles_smem + stage * kStageBytes;
-          mbar_expect_tx(full_bar + 8 * stage, kStageBytes);
-          tma_load_2d(a_dst, &tm_a, kb * BK, row0, full_bar + 8 * stage);
-          tma_load_2d(a_dst + kTileABytes, &tm_b, kb * BK, wrow0, full_bar + 8 * stage);
-          if (++stage == kStages) { stage = 0; phase ^= 1u; }
-        }
+      while (cur.valid) {
+        if (!mbar_wait(empty_bar + 8 * stage, phase ^ 1u, abort_flag, p.status, DICE_STATUS_WAIT_SMEM_EMPTY)) break;
+        const uint32_t a_dst = tiles_smem + stage * stage_bytes;
+        mbar_expect_tx(full_bar + 8 * stage, stage_tx_bytes);
+        tma_load_2d(a_dst, &tm_a, cur.kb * BK, cur.row0, full_bar + 8 * stage);
+        tma_load_2d(a_dst + kTileABytes, &tm_b, cur.kb * BK, cur.wrow0, full_bar + 8 * stage);
+        if (++stage == n_stages) { stage = 0; phase ^= 1u; }
+        advance(cur);
       }
     }
   } else if (warp == 1) {
@@ -309,7 +336,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             break;
           }
           tc_fence_after_sync();
-          const uint32_t a_addr = tiles_smem + stage * kStageBytes;
+          const uint32_t a_addr = tiles_smem + stage * stage_bytes;
           const uint64_t a_desc = make_operand_desc(a_addr);
           const uint64_t b_desc = make_operand_desc(a_addr + kTileABytes);
 #pragma unroll
@@ -319,7 +346,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                       static_cast<uint32_t>((kb | kk) != 0));
           }
           umma_commit(empty_bar + 8 * stage);  // slot reusable once these MMAs have read it
-          if (++stage == kStages) { stage = 0; phase ^= 1u; }
+          if (++stage == n_stages) { stage = 0; phase ^= 1u; }
         }
         if (!alive) break;
         umma_commit(acc_full_bar + 8 * acc);   // accumulator complete
@@ -343,7 +370,52 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       const bool row_ok = r < rows_valid;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + static_cast<uint32_t>(acc * BN);
       __nv_bfloat16* out_row = p.out + static_cast<int64_t>(row0 + r) * p.ld_out;
-      if (p.epilogue == DICE_EPI_SWIGLU) {
+      if (p.epilogue == kEpiRouter) {
+        // one thread = one token: its logits are the first n_experts accumulator columns of its lane
+        const int64_t tok = row0 + r;
+        int i0 = 0, i1 = 1;
+        float p0 = 0.f, p1 = 0.f;
+        if (p.n_experts <= 32) {
+          uint32_t a[32];
+          tmem_ld32(taddr, a);
+          tmem_ld_wait();
+          float l[32];
+#pragma unroll
+          for (int e = 0; e < 32; ++e) l[e] = __bfloat162float(__float2bfloat16_rn(__uint_as_float(a[e])));
+          if (row_ok && p.logits_out != nullptr) {
+#pragma unroll
+            for (int e = 0; e < 32; ++e)
+              if (e < p.n_experts) p.logits_out[tok * p.n_experts + e] = __float2bfloat16_rn(l[e]);
+          }
+          if (p.n_experts <= 8) select_top2<8>(reinterpret_cast<const float(&)[8]>(l), p.n_experts, p.renorm, i0, i1, p0, p1);
+          else if (p.n_experts <= 16) select_top2<16>(reinterpret_cast<const float(&)[16]>(l), p.n_experts, p.renorm, i0, i1, p0, p1);
+          else select_top2<32>(l, p.n_experts, p.renorm, i0, i1, p0, p1);
+        } else {
+          uint32_t a[32], b[32];
+          tmem_ld32(taddr, a);
+          tmem_ld32(taddr + 32, b);
+          tmem_ld_wait();
+          float l[64];
+#pragma unroll
+          for (int e = 0; e < 32; ++e) {
+            l[e] = __bfloat162float(__float2bfloat16_rn(__uint_as_float(a[e])));
+            l[32 + e] = __bfloat162float(__float2bfloat16_rn(__uint_as_float(b[e])));
+          }
+          if (row_ok && p.logits_out != nullptr) {
+#pragma unroll
+            for (int e = 0; e < 64; ++e)
+              if (e < p.n_experts) p.logits_out[tok * p.n_experts + e] = __float2bfloat16_rn(l[e]);
+          }
+          select_top2<64>(l, p.n_experts, p.renorm, i0, i1, p0, p1);
+        }
+        if (row_ok) {
+          longlong2 iv; iv.x = i0; iv.y = i1;
+          *reinterpret_cast<longlong2*>(p.out_idx + 2 * tok) = iv;
+          *reinterpret_cast<float2*>(p.out_w + 2 * tok) = make_float2(p0, p1);
+          atomicAdd(&s_hist[i0], 1);
+          atomicAdd(&s_hist[i1], 1);
+        }
+      } else if (p.epilogue == DICE_EPI_SWIGLU) {
         const int col0 = nb * (BN / 2);
         int n_valid = p.n_out - col0;
         if (n_valid > BN / 2) n_valid = BN / 2;
@@ -385,6 +457,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   // ---------------- teardown ----------------
   tc_fence_before_sync();
   __syncthreads();
+  if (p.epilogue == kEpiRouter && threadIdx.x < p.n_experts && s_hist[threadIdx.x] != 0)
+    atomicAdd(&p.hist[threadIdx.x], s_hist[threadIdx.x]);
   if (*abort_flag != 0) {
     // a wait expired: give copies and MMAs still in flight time to land before the CTA's
     // shared and tensor memory are released
@@ -431,6 +505,12 @@ int encode_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols,
   return r == CUDA_SUCCESS ? DICE_OK : DICE_ERR_CUDA;
 }
 
+int ring_depth(int b_box_rows) {
+  const int stage_bytes = kTileABytes + ((b_box_rows * BK * 2 + 1023) & ~1023);
+  const int n = (kStages * kStageBytes) / stage_bytes;
+  return n > kMaxStages ? kMaxStages : n;
+}
+
 int sm_count() {
   static int cached[64] = {0};
   int dev = 0;
@@ -470,8 +550,9 @@ extern "C" int dice_grouped_gemm(const void* a, int64_t n_rows, int k_dim, const
   CUtensorMap tm_a, tm_b;
   int rc = encode_map(&tm_a, a, static_cast<uint64_t>(n_rows), static_cast<uint64_t>(k_dim), BM);
   if (rc != DICE_OK) return rc;
+  const int b_box_rows = w_rows >= BN ? BN : static_cast<int>((w_rows + 15) / 16 * 16);
   rc = encode_map(&tm_b, w, static_cast<uint64_t>(n_slabs) * static_cast<uint64_t>(w_rows),
-                  static_cast<uint64_t>(k_dim), BN);
+                  static_cast<uint64_t>(k_dim), static_cast<uint32_t>(b_box_rows));
   if (rc != DICE_OK) return rc;
 
   GemmParams p;
@@ -487,10 +568,60 @@ extern "C" int dice_grouped_gemm(const void* a, int64_t n_rows, int k_dim, const
   p.out = static_cast<__nv_bfloat16*>(out);
   p.ld_out = ld_out;
   p.status = status;
+  p.b_box_rows = b_box_rows;
+  p.n_stages = ring_depth(b_box_rows);
+  p.n_experts = 0;
+  p.renorm = 0;
+  p.out_idx = nullptr;
+  p.out_w = nullptr;
+  p.hist = nullptr;
+  p.logits_out = nullptr;
 
   const int64_t max_tiles = ((n_rows + BM - 1) / BM + n_seg) * p.n_nblk;
   const int grid = static_cast<int>(max_tiles < sms ? max_tiles : sms);
   grouped_gemm_kernel<<<grid, kThreads, kSmemBytes, static_cast<cudaStream_t>(stream)>>>(tm_a, tm_b, p);
+  return cudaGetLastError() == cudaSuccess ? DICE_OK : DICE_ERR_CUDA;
+}
+
+// Router on the tensor cores (bf16): logits = x * w_gate^T as one 128 x 16..64 accumulator tile per 128
+// tokens, then every epilogue thread selects the top-2 of its own token.
+int dice_internal_router_tc(const void* x, const void* w_gate, int64_t n_tokens, int hidden, int n_experts, int renorm,
+                            int64_t* out_idx, float* out_w, int32_t* out_hist, void* out_logits,
+                            cudaStream_t stream) {
+  const int sms = sm_count();
+  if (sms <= 0) return DICE_ERR_CUDA;
+  if (n_tokens >= 0x7fffff00LL) return DICE_ERR_LIMIT;
+  CUtensorMap tm_a, tm_b;
+  const int b_box_rows = (n_experts + 15) / 16 * 16;
+  int rc = encode_map(&tm_a, x, static_cast<uint64_t>(n_tokens), static_cast<uint64_t>(hidden), BM);
+  if (rc != DICE_OK) return rc;
+  rc = encode_map(&tm_b, w_gate, static_cast<uint64_t>(n_experts), static_cast<uint64_t>(hidden),
+                  static_cast<uint32_t>(b_box_rows));
+  if (rc != DICE_OK) return rc;
+  GemmParams p;
+  p.seg_offsets = nullptr;
+  p.seg_slab = nullptr;
+  p.n_seg = 1;
+  p.n_rows = static_cast<int>(n_tokens);
+  p.n_kblk = (hidden + BK - 1) / BK;
+  p.n_nblk = 1;
+  p.w_rows = n_experts;
+  p.n_out = n_experts;
+  p.epilogue = kEpiRouter;
+  p.out = nullptr;
+  p.ld_out = 0;
+  p.status = nullptr;
+  p.b_box_rows = b_box_rows;
+  p.n_stages = ring_depth(b_box_rows);
+  p.n_experts = n_experts;
+  p.renorm = renorm;
+  p.out_idx = out_idx;
+  p.out_w = out_w;
+  p.hist = out_hist;
+  p.logits_out = static_cast<__nv_bfloat16*>(out_logits);
+  const int64_t tiles = (n_tokens + BM - 1) / BM;
+  const int grid = static_cast<int>(tiles < sms ? tiles : sms);
+  grouped_gemm_kernel<<<grid, kThreads, kSmemBytes, stream>>>(tm_a, tm_b, p);
   return cudaGetLastError() == cudaSuccess ? DICE_OK : DICE_ERR_CUDA;
 }
 

@@ -36,20 +36,20 @@ plan_count_kernel(const int64_t* __restrict__ flat_idx, int64_t n_rows, int n_ex
 
 // ---- plan, pass 2: exclusive scan over chunks (per expert) and experts -------
 // chunk_hist[c][e] becomes the first sorted position of chunk c's rows of
-// expert e; seg_offsets[e] the first position of expert e.
-__global__ void __launch_bounds__(2 * kMaxExperts)
+// expert e; seg_offsets[e] the first position of expert e.  One warp per expert:
+// lanes take 32 chunks at a time and scan them with shuffles.
+constexpr int kScanThreads = 1024;
+__global__ void __launch_bounds__(kScanThreads)
 plan_scan_kernel(int* __restrict__ chunk_hist, int n_chunks, int n_experts, int* __restrict__ seg_offsets) {
   __shared__ int s_total[kMaxExperts];
   __shared__ int s_base[kMaxExperts + 1];
-  const int e = threadIdx.x;
-  if (e < n_experts) {
-    int run = 0;
-    for (int c = 0; c < n_chunks; ++c) {
-      const int v = chunk_hist[static_cast<int64_t>(c) * n_experts + e];
-      chunk_hist[static_cast<int64_t>(c) * n_experts + e] = run;
-      run += v;
-    }
-    s_total[e] = run;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int e = warp; e < n_experts; e += kScanThreads / 32) {
+    int sum = 0;
+    for (int c = lane; c < n_chunks; c += 32) sum += chunk_hist[static_cast<int64_t>(c) * n_experts + e];
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+    if (lane == 0) s_total[e] = sum;
   }
   __syncthreads();
   if (threadIdx.x == 0) {
@@ -58,10 +58,21 @@ plan_scan_kernel(int* __restrict__ chunk_hist, int n_chunks, int n_experts, int*
     s_base[n_experts] = run;
   }
   __syncthreads();
-  if (e <= n_experts) seg_offsets[e] = s_base[e];
-  if (e < n_experts) {
-    const int base = s_base[e];
-    for (int c = 0; c < n_chunks; ++c) chunk_hist[static_cast<int64_t>(c) * n_experts + e] += base;
+  if (threadIdx.x <= n_experts) seg_offsets[threadIdx.x] = s_base[threadIdx.x];
+  for (int e = warp; e < n_experts; e += kScanThreads / 32) {
+    int carry = s_base[e];
+    for (int c0 = 0; c0 < n_chunks; c0 += 32) {
+      const int c = c0 + lane;
+      const int v = c < n_chunks ? chunk_hist[static_cast<int64_t>(c) * n_experts + e] : 0;
+      int incl = v;
+#pragma unroll
+      for (int off = 1; off < 32; off <<= 1) {
+        const int up = __shfl_up_sync(0xffffffffu, incl, off);
+        if (lane >= off) incl += up;
+      }
+      if (c < n_chunks) chunk_hist[static_cast<int64_t>(c) * n_experts + e] = carry + incl - v;
+      carry += __shfl_sync(0xffffffffu, incl, 31);
+    }
   }
 }
 
@@ -228,7 +239,7 @@ extern "C" int dice_permute_plan(const int64_t* flat_idx, int64_t n_rows, int n_
   const int chunks = static_cast<int>((n_rows + kChunkRows - 1) / kChunkRows);
   int* chunk_hist = static_cast<int*>(scratch);
   plan_count_kernel<<<chunks, kChunkRows, 0, s>>>(flat_idx, n_rows, n_experts, chunk_hist);
-  plan_scan_kernel<<<1, 2 * kMaxExperts, 0, s>>>(chunk_hist, chunks, n_experts, out_seg_offsets);
+  plan_scan_kernel<<<1, kScanThreads, 0, s>>>(chunk_hist, chunks, n_experts, out_seg_offsets);
   plan_rank_kernel<<<chunks, kChunkRows, 0, s>>>(flat_idx, n_rows, n_experts, chunk_hist, out_pos, out_order);
   return cudaGetLastError() == cudaSuccess ? DICE_OK : DICE_ERR_CUDA;
 }
@@ -267,7 +278,7 @@ extern "C" int dice_permute_plan_static(const int64_t* flat_idx, int64_t n_rows,
   if (rc != DICE_OK) return rc;
   // pass 1 overwrites every cell the later passes read, so nothing has to be cleared between calls
   plan_count_kernel<<<static_cast<int>(chunks), kChunkRows, 0, s>>>(flat_idx, n_rows, n_experts, chunk_hist);
-  plan_scan_kernel<<<1, 2 * kMaxExperts, 0, s>>>(chunk_hist, static_cast<int>(chunks), n_experts, out_seg_offsets);
+  plan_scan_kernel<<<1, kScanThreads, 0, s>>>(chunk_hist, static_cast<int>(chunks), n_experts, out_seg_offsets);
   plan_rank_kernel<<<static_cast<int>(chunks), kChunkRows, 0, s>>>(flat_idx, n_rows, n_experts, chunk_hist, out_pos,
                                                                     out_order);
   return cudaGetLastError() == cudaSuccess ? DICE_OK : DICE_ERR_CUDA;

@@ -1,0 +1,85 @@
+"""Worker of tests/test_ep_gpu_multi.py: one NCCL rank per GPU (run under torchrun).
+
+Checks the expert-parallel block against the single-device block on the same
+seeded inputs: synchronous exchange (same step), displaced (two steps stale),
+interweaved over two layers (one step stale), and displaced with conditional
+communication (runs, finite, right shapes)."""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+
+def main():
+    from dice_b200.expertpara import diep, ep_fwd
+    from dice_b200.moe_block import ParaMode, SparseMoeBlock
+
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    h, e, layers, steps, n_tok = 256, 8, 2, 6, 1000 + 37 * rank  # ragged: ranks hold different token counts
+
+    def make(pm, layer):
+        torch.manual_seed(100 + layer)
+        full = SparseMoeBlock(h, 4, e, 2, 1, layer, layers, ParaMode(), shared_expert=False)
+        sd = {k: v.clone() for k, v in full.state_dict().items()}
+        if pm.ep:
+            blk = SparseMoeBlock(h, 4, e, 2, 1, layer, layers, pm, shared_expert=False)
+            mine = {k: v for k, v in sd.items() if ".experts." not in "." + k or int(k.split(".")[1]) % world == rank}
+            blk.load_state_dict(mine)
+        else:
+            blk = full
+        return blk.to(device=dev, dtype=torch.bfloat16).eval()
+
+    g = torch.Generator(device=dev).manual_seed(7 + rank)
+    xs = [[torch.randn(1, n_tok, h, generator=g, device=dev).bfloat16() for _ in range(layers)] for _ in range(steps)]
+    ref_blocks = [make(ParaMode(), l) for l in range(layers)]
+    want = [[ref_blocks[l](xs[t][l]).float() for l in range(layers)] for t in range(steps)]
+
+    def close(a, b, what):
+        err = ((a.float() - b).norm() / b.norm()).item()
+        assert err < 2e-2, f"rank {rank} {what}: rel err {err}"
+
+    def run(pm, cache_kwargs, check):
+        blocks = [make(pm, l) for l in range(layers)]
+        diep.ep_cache_init(layers, **cache_kwargs)
+        ep_fwd.use_latest_expert_weights(False)
+        for t in range(steps):
+            diep.ep_set_step(steps - t)
+            forced = pm.ep_async and t == 0
+            if forced:
+                diep.diep_force_sync()
+                diep.ep_cache_clear()
+            for l in range(layers):
+                y = blocks[l](xs[t][l])
+                assert y.shape == xs[t][l].shape and bool(torch.isfinite(y.float()).all())
+                check(t, l, y)
+            if forced:
+                diep.diep_cancel_sync()
+        for b in blocks:
+            b.check_status()
+
+    run(ParaMode(ep=True), {}, lambda t, l, y: close(y, want[t][l], f"sync t={t} l={l}"))
+    a = dict(ep=True, ep_async=True, ep_async_mode="all", ep_async_warm_up=0, strided_sync=0, ep_async_cool_down=0)
+    run(ParaMode(**a), dict(async_pipeline=False, selective_async_strategy="all"),
+        lambda t, l, y: close(y, want[max(0, t - 2)][l], f"displaced t={t} l={l}"))
+    run(ParaMode(**a), dict(async_pipeline=True, selective_async_strategy="all", auto_gc=True),
+        lambda t, l, y: close(y, want[max(0, t - 1) if t != 1 else 0][l], f"interweaved t={t} l={l}"))
+    run(ParaMode(**a), dict(async_pipeline=False, selective_async_strategy="all", noskip_step=2, skip_mode="low"),
+        lambda t, l, y: None)
+    mem = diep.ep_cached_tensors_size()
+    assert mem > 0 and diep.ep_get_max_mem() >= 0
+    dist.barrier()
+    if rank == 0:
+        print("EP_GPU_WORKER_OK", flush=True)
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
