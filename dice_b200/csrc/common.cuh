@@ -56,3 +56,8 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
 int dice_internal_router_tc(const void* x, const void* w_gate, int64_t n_tokens, int hidden, int n_experts, int renorm,
                             int64_t* out_idx, float* out_w, int32_t* out_hist, void* out_logits,
                             cudaStream_t stream);
+
+// internal (not exported): grouped GEMM on CTA pairs (cta_group::2); arguments as dice_grouped_gemm, validated by it
+int dice_internal_gemm_pair(const void* a, int64_t n_rows, int k_dim, const void* w, int n_slabs, int64_t w_rows,
+                            const int32_t* seg_offsets, const int32_t* seg_slab, int n_seg, int epilogue, void* out,
+                            int64_t ld_out, int n_out, uint32_t* status, cudaStream_t stream);

@@ -1,0 +1,365 @@
+// Grouped GEMM with CTA pairs (tcgen05 cta_group::2).
+//
+// Same contract as grouped_gemm.cu, different tiling: two CTAs of a cluster
+// share one 256 x 256 tile.  CTA r of the pair loads its own 128 rows of A and
+// HALF of the weight tile (128 of the 256 weight rows); one thread of the
+// leader CTA issues tcgen05.mma.cta_group::2 (M = 256), which reads A from
+// both CTAs' shared memory and stitches the two weight halves together, and
+// leaves rows [128 r, 128 r + 128) of the result in CTA r's tensor memory.
+// Per SM and k-block that is 32 KB of operands instead of 48 KB, so shared
+// memory carries a third less traffic and the same 192 KB ring holds six
+// slots instead of four.
+//
+// Synchronisation across the pair:
+//   * both loaders' TMA copies complete on the LEADER's "full" mbarrier (the
+//     leader arms it with the pair's byte count);
+//   * the leader's MMA thread commits to the "empty" and "accumulator full"
+//     mbarriers of BOTH CTAs;
+//   * the epilogue warps of both CTAs arrive on the LEADER's "accumulator
+//     empty" mbarrier;
+//   * a cluster barrier before the exit keeps either CTA alive until its peer
+//     can no longer signal it.
+// Every wait is bounded as in the single-CTA kernel.
+#include <cuda.h>
+#include <stdlib.h>
+
+#include "umma.cuh"
+
+using namespace dice_umma;
+
+namespace {
+
+constexpr int PM = 256;                    // rows per tile pair
+constexpr int kPairStages = 6;
+constexpr int kPairTileBBytes = 128 * BK * 2;
+constexpr int kPairStageBytes = kTileABytes + kPairTileBBytes;  // 32 KB
+constexpr int kPairSmemBytes = kPairStages * kPairStageBytes + kAuxBytes + 1024;
+
+__device__ __forceinline__ uint32_t cluster_cta_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// shared::cluster address of `addr` (a shared::cta address of this CTA) in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_barrier() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// TMA tile load of this CTA whose completion is counted on the leader's mbarrier
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int c0, int c1,
+                                                 uint32_t leader_bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(leader_bar)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t slot_smem_addr, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot_smem_addr), "r"(cols) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void umma_bf16_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                               uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// arrive (once all MMAs issued so far have completed) on the mbarrier at this offset in both CTAs of the pair
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
+  const uint16_t both = 3;
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar),
+               "h"(both)
+               : "memory");
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+                         const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* aux = smem + kPairStages * kPairStageBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(aux);
+  const uint32_t full_bar = smem_u32(bars);                          // [kPairStages] used in the leader
+  const uint32_t empty_bar = smem_u32(bars + kPairStages);           // [kPairStages] in both CTAs
+  const uint32_t acc_full_bar = smem_u32(bars + 2 * kPairStages);    // [kAccStages] in both CTAs
+  const uint32_t acc_empty_bar = smem_u32(bars + 2 * kPairStages + kAccStages);  // used in the leader
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kPairStages + 2 * kAccStages);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+  int* s_seg_off = reinterpret_cast<int*>(tmem_slot + 4);
+  int* s_mprefix = s_seg_off + (kMaxSeg + 1);
+  const uint32_t tiles_smem = smem_u32(smem);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t cta_rank = cluster_cta_rank();  // 0 = leader
+  const bool leader = cta_rank == 0;
+  const int64_t pair_id = blockIdx.x >> 1;
+  const int64_t n_pairs = gridDim.x >> 1;
+
+  for (int i = threadIdx.x; i <= p.n_seg; i += kThreads)
+    s_seg_off[i] = p.seg_offsets != nullptr ? p.seg_offsets[i] : (i == 0 ? 0 : p.n_rows);
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kPairStages; ++s) {
+      mbar_init(full_bar + 8 * s, 1);
+      mbar_init(empty_bar + 8 * s, 1);
+    }
+    for (int a = 0; a < kAccStages; ++a) {
+      mbar_init(acc_full_bar + 8 * a, 1);
+      mbar_init(acc_empty_bar + 8 * a, 2 * kEpilogueWarps);  // the epilogue warps of both CTAs
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int run = 0;
+    bool ok = s_seg_off[0] >= 0;
+    for (int s = 0; s < p.n_seg; ++s) {
+      const int cnt = s_seg_off[s + 1] - s_seg_off[s];
+      ok = ok && cnt >= 0;
+      s_mprefix[s] = run;
+      run += cnt > 0 ? (cnt + PM - 1) / PM : 0;
+    }
+    ok = ok && s_seg_off[p.n_seg] <= p.n_rows;
+    if (!ok) {
+      run = 0;
+      if (p.status != nullptr) atomicCAS(p.status, 0u, DICE_STATUS_BAD_SEGMENTS);
+    }
+    s_mprefix[p.n_seg] = run;
+  }
+  if (warp == 1) tmem_alloc_pair(smem_u32(tmem_slot), kTmemCols);
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_barrier();  // the peer's mbarriers are initialised before anything signals them
+  tc_fence_after_sync();
+
+  const uint32_t tmem_base = *tmem_slot;
+  const int64_t total_tiles = static_cast<int64_t>(s_mprefix[p.n_seg]) * p.n_nblk;
+
+  if (warp == 0) {
+    // ---------------- loader (both CTAs) ----------------
+    if (lane == 0) {
+      int stage = 0, seg = 0;
+      uint32_t phase = 0;
+      bool alive = true;
+      for (int64_t t = pair_id; alive && t < total_tiles; t += n_pairs) {
+        const int mb = static_cast<int>(t / p.n_nblk);
+        const int nb = static_cast<int>(t - static_cast<int64_t>(mb) * p.n_nblk);
+        while (mb >= s_mprefix[seg + 1]) ++seg;
+        const int row0 = s_seg_off[seg] + (mb - s_mprefix[seg]) * PM + static_cast<int>(cta_rank) * BM;
+        const int slab = p.seg_slab != nullptr ? p.seg_slab[seg] : seg;
+        int n_valid = p.w_rows - nb * BN;
+        if (n_valid > BN) n_valid = BN;
+        const int n_mma = (n_valid + 15) & ~15;
+        // the MMA takes the first n_mma/2 weight rows of the tile from the leader and the rest from the peer
+        const int wrow0 = slab * p.w_rows + nb * BN + static_cast<int>(cta_rank) * (n_mma / 2);
+        for (int kb = 0; kb < p.n_kblk; ++kb) {
+          if (!mbar_wait(empty_bar + 8 * stage, phase ^ 1u, abort_flag, p.status, DICE_STATUS_WAIT_SMEM_EMPTY)) {
+            alive = false;
+            break;
+          }
+          const uint32_t a_dst = tiles_smem + stage * kPairStageBytes;
+          const uint32_t leader_full = map_to_cta(full_bar + 8 * stage, 0);
+          if (leader) mbar_expect_tx(full_bar + 8 * stage, 2 * kPairStageBytes);
+          tma_load_2d_pair(a_dst, &tm_a, kb * BK, row0, leader_full);
+          tma_load_2d_pair(a_dst + kTileABytes, &tm_b, kb * BK, wrow0, leader_full);
+          if (++stage == kPairStages) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- tensor-core issue (leader only) ----------------
+    if (leader && lane == 0) {
+      int stage = 0, acc = 0;
+      uint32_t phase = 0, acc_phase = 0;
+      bool alive = true;
+      for (int64_t t = pair_id; alive && t < total_tiles; t += n_pairs) {
+        const int nb = static_cast<int>(t % p.n_nblk);
+        int n_valid = p.w_rows - nb * BN;
+        if (n_valid > BN) n_valid = BN;
+        const uint32_t idesc = make_instr_desc(PM, (n_valid + 15) & ~15);
+        if (!mbar_wait(acc_empty_bar + 8 * acc, acc_phase ^ 1u, abort_flag, p.status, DICE_STATUS_WAIT_ACC_EMPTY)) break;
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
+        for (int kb = 0; kb < p.n_kblk; ++kb) {
+          if (!mbar_wait(full_bar + 8 * stage, phase, abort_flag, p.status, DICE_STATUS_WAIT_SMEM_FULL)) {
+            alive = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t a_addr = tiles_smem + stage * kPairStageBytes;
+          const uint64_t a_desc = make_operand_desc(a_addr);
+          const uint64_t b_desc = make_operand_desc(a_addr + kTileABytes);
+#pragma unroll
+          for (int kk = 0; kk < BK / UMMA_K; ++kk)
+            umma_bf16_pair(d_tmem, a_desc + static_cast<uint64_t>(kk * 2), b_desc + static_cast<uint64_t>(kk * 2), idesc,
+                           static_cast<uint32_t>((kb | kk) != 0));
+          umma_commit_pair(empty_bar + 8 * stage);
+          if (++stage == kPairStages) { stage = 0; phase ^= 1u; }
+        }
+        if (!alive) break;
+        umma_commit_pair(acc_full_bar + 8 * acc);
+        if (++acc == kAccStages) { acc = 0; acc_phase ^= 1u; }
+      }
+    }
+  } else {
+    // ---------------- epilogue (both CTAs, each over its own 128 rows) ----------------
+    const int quad = warp & 3;            // tensor-memory lanes [32*quad, 32*quad+32) belong to this warp
+    const int half = (warp - 2) >> 2;     // which of the quadrant's two warps: even or odd 32-column chunks
+    int acc = 0, seg = 0;
+    uint32_t acc_phase = 0;
+    for (int64_t t = pair_id; t < total_tiles; t += n_pairs) {
+      const int mb = static_cast<int>(t / p.n_nblk);
+      const int nb = static_cast<int>(t - static_cast<int64_t>(mb) * p.n_nblk);
+      while (mb >= s_mprefix[seg + 1]) ++seg;
+      const int row0 = s_seg_off[seg] + (mb - s_mprefix[seg]) * PM + static_cast<int>(cta_rank) * BM;
+      const int rows_valid = s_seg_off[seg + 1] - row0;  // <= 0 when this CTA's half lies past the segment
+      if (!mbar_wait(acc_full_bar + 8 * acc, acc_phase, abort_flag, p.status, DICE_STATUS_WAIT_ACC_FULL)) break;
+      tc_fence_after_sync();
+      const int r = quad * 32 + lane;
+      const bool row_ok = r < rows_valid;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + static_cast<uint32_t>(acc * BN);
+      __nv_bfloat16* out_row = p.out + static_cast<int64_t>(row0 + r) * p.ld_out;
+      if (p.epilogue == DICE_EPI_SWIGLU) {
+        const int col0 = nb * (BN / 2);
+        int n_valid = p.n_out - col0;
+        if (n_valid > BN / 2) n_valid = BN / 2;
+        for (int c = half * 32; c < n_valid; c += 64) {
+          uint32_t g[32], u[32];
+          tmem_ld32(taddr + c, g);
+          tmem_ld32(taddr + BN / 2 + c, u);
+          tmem_ld_wait();
+          float v[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = silu_f(__uint_as_float(g[j])) * __uint_as_float(u[j]);
+          store_row_chunk(out_row + col0 + c, v, n_valid - c, row_ok);
+        }
+      } else {
+        const int col0 = nb * BN;
+        int n_valid = p.n_out - col0;
+        if (n_valid > BN) n_valid = BN;
+        const bool gelu = p.epilogue == DICE_EPI_GELU_TANH;
+        for (int c = half * 32; c < n_valid; c += 64) {
+          uint32_t a[32];
+          tmem_ld32(taddr + c, a);
+          tmem_ld_wait();
+          float v[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const float f = __uint_as_float(a[j]);
+            v[j] = gelu ? gelu_tanh_f(f) : f;
+          }
+          store_row_chunk(out_row + col0 + c, v, n_valid - c, row_ok);
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(acc_empty_bar + 8 * acc, 0));
+      if (++acc == kAccStages) { acc = 0; acc_phase ^= 1u; }
+    }
+  }
+
+  // ---------------- teardown ----------------
+  tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag != 0) {
+    const uint64_t t0 = global_timer_ns();
+    while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  cluster_barrier();  // neither CTA leaves while the other may still signal its mbarriers or read its operands
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after_sync();
+    tmem_dealloc_pair(tmem_base, kTmemCols);
+  }
+}
+
+// number of CTA pairs that can be resident at once (cached per device); 0 on error
+int resident_pairs() {
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+  if (cached[dev] == 0) {
+    if (cudaFuncSetAttribute(grouped_gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmemBytes) !=
+        cudaSuccess)
+      return 0;
+    const int sms = sm_count_cached();
+    if (sms <= 0) return 0;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(sms & ~1), 1, 1);
+    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.dynamicSmemBytes = kPairSmemBytes;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, grouped_gemm_pair_kernel, &cfg) != cudaSuccess || n <= 0) return 0;
+    cached[dev] = n < sms / 2 ? n : sms / 2;
+  }
+  return cached[dev];
+}
+
+}  // namespace
+
+// Internal entry used by dice_grouped_gemm: same arguments, already validated.
+int dice_internal_gemm_pair(const void* a, int64_t n_rows, int k_dim, const void* w, int n_slabs, int64_t w_rows,
+                            const int32_t* seg_offsets, const int32_t* seg_slab, int n_seg, int epilogue, void* out,
+                            int64_t ld_out, int n_out, uint32_t* status, cudaStream_t stream) {
+  const int pairs = resident_pairs();
+  if (pairs <= 0) return DICE_ERR_CUDA;
+  CUtensorMap tm_a, tm_b;
+  int rc = encode_map(&tm_a, a, static_cast<uint64_t>(n_rows), static_cast<uint64_t>(k_dim), BM);
+  if (rc != DICE_OK) return rc;
+  rc = encode_map(&tm_b, w, static_cast<uint64_t>(n_slabs) * static_cast<uint64_t>(w_rows), static_cast<uint64_t>(k_dim),
+                  128);
+  if (rc != DICE_OK) return rc;
+  GemmParams p = {};
+  p.seg_offsets = seg_offsets;
+  p.seg_slab = seg_slab;
+  p.n_seg = n_seg;
+  p.n_rows = static_cast<int>(n_rows);
+  p.n_kblk = (k_dim + BK - 1) / BK;
+  p.n_nblk = static_cast<int>((w_rows + BN - 1) / BN);
+  p.w_rows = static_cast<int>(w_rows);
+  p.n_out = n_out;
+  p.epilogue = epilogue;
+  p.out = static_cast<__nv_bfloat16*>(out);
+  p.ld_out = ld_out;
+  p.status = status;
+  p.b_box_rows = 128;
+  p.n_stages = kPairStages;
+
+  const int64_t max_tiles = ((n_rows + PM - 1) / PM + n_seg) * p.n_nblk;
+  const int use_pairs = static_cast<int>(max_tiles < pairs ? max_tiles : pairs);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(2 * use_pairs), 1, 1);
+  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.dynamicSmemBytes = kPairSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (cudaLaunchKernelEx(&cfg, grouped_gemm_pair_kernel, tm_a, tm_b, p) != cudaSuccess) return DICE_ERR_CUDA;
+  return DICE_OK;
+}
