@@ -48,7 +48,7 @@ TOKENS_PER_IMAGE = 256
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 # dram__bytes_read.sum + dram__bytes_write.sum of one grouped-GEMM launch of this workload,
 # scaled from the ncu capture summarised under profiles/ (None until a capture exists)
-GEMM_TRAFFIC_BYTES = None
+GEMM_TRAFFIC_BYTES = 440.5e6  # mean of fc1 (409.7 MB) and fc2 (471.3 MB), profiles/grouped_gemm_dit_xl2_moe_block.md
 
 
 def parse_args():
@@ -263,10 +263,10 @@ def run_ours(args):
     gemm_ms = sum(routed) / max(gemm_launches, 1)
     flops_per_launch = ffn_flops(tokens, args.variant) / 2
     achieved = flops_per_launch / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else 0.0
-    roofline = {"kernel": "grouped_gemm_kernel (tcgen05, fc1+fc2 of the routed experts)", "bound": "tensor",
+    roofline = {"kernel": "grouped_gemm_pair_kernel (tcgen05 cta_group::2, fc1+fc2 of the routed experts)", "bound": "tensor",
                 "achieved": round(achieved, 1), "peak": peak_tf, "unit": "TFLOP/s", "frac": round(achieved / peak_tf, 4),
                 "peak_source": f"bf16_tflops_sustained of {pk_src}", "avg_launch_ms": round(gemm_ms, 4),
-                "launches_timed": gemm_launches, "flops_per_launch": flops_per_launch, "traffic": GEMM_TRAFFIC_BYTES}
+                "launches_timed": gemm_launches, "flops_per_launch": flops_per_launch, "traffic": GEMM_TRAFFIC_BYTES if (world == 1 and args.variant == "gelu_tanh") else None}
 
     line = {
         "metric": "moe_block_tokens_per_s", "value": round(value, 1), "unit": "tokens/s", "n_gpus": world,

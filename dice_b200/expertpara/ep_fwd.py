@@ -70,7 +70,11 @@ class CudaOps:
 
         return ops.unpermute_combine(src0, idx0, src1, idx1, w0, w1, n_tokens, addend=addend)
 
-    def run_packed_experts(self, rows, pack, seg_counts: Sequence[int], seg_slab: Sequence[int]):
+    def run_packed_experts(self, rows, pack, seg_counts: Sequence[int], seg_slab: Sequence[int], seg_offsets_dev=None):
+        if seg_offsets_dev is not None:
+            # segment offsets were derived on the device from the gathered counts: no host-to-device copy,
+            # and therefore no stream synchronisation, between the dispatch and the expert FFN
+            return pack.run_offsets(rows, seg_offsets_dev, pack.slab_table(seg_slab, rows.device))
         return pack.run_segments(rows, seg_counts, seg_slab)
 
 
@@ -120,12 +124,20 @@ def _exchange_counts_by_owner(counts_key: torch.Tensor, world_size: int, rank: i
     ``recv[W, El]`` (rows rank s sends to this rank's slot i)."""
     n_local = counts_key.numel() // world_size
     if world_size == 1:
-        mine = counts_key.to("cpu", torch.int64).view(1, n_local)
-        return mine, mine.clone()
-    gathered = torch.empty((world_size * counts_key.numel(),), dtype=counts_key.dtype, device=counts_key.device)
-    dist.all_gather_into_tensor(gathered, counts_key.contiguous())
+        gathered = counts_key.contiguous()
+    else:
+        gathered = torch.empty((world_size * counts_key.numel(),), dtype=counts_key.dtype, device=counts_key.device)
+        dist.all_gather_into_tensor(gathered, counts_key.contiguous())
+    seg_dev = None
+    if gathered.is_cuda:
+        # offsets of the [source][slot] segments of the receive buffer, kept on the device for the grouped FFN
+        mine = gathered.view(world_size, world_size, n_local)[:, rank, :].reshape(-1)
+        seg_dev = torch.zeros(mine.numel() + 1, dtype=torch.int32, device=gathered.device)
+        torch.cumsum(mine, 0, out=seg_dev[1:])
     host = gathered.to("cpu", torch.int64).view(world_size, world_size, n_local)
-    return host[rank].contiguous(), host[:, rank, :].contiguous()
+    send, recv = host[rank].contiguous(), host[:, rank, :].contiguous()
+    recv._dice_seg_offsets = seg_dev
+    return send, recv
 
 
 # --------------------------------------------------------------------------- #
@@ -187,6 +199,9 @@ def proc_experts(inp, experts, token_counts_global, num_local_experts):
     assert sum(seg_counts) == inp.size(0)
     pack = getattr(experts, "_dice_pack", None)
     if pack is not None:
+        seg_dev = getattr(token_counts_global, "_dice_seg_offsets", None)
+        if seg_dev is not None:
+            return _ops.run_packed_experts(inp, pack, seg_counts, seg_slab, seg_dev)
         return _ops.run_packed_experts(inp, pack, seg_counts, seg_slab)
     outp = torch.empty_like(inp)
     start = 0

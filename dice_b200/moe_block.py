@@ -196,6 +196,7 @@ class ExpertPack:
         self._built = {}
         self.status = None
         self.tag = tag
+        self._slab_tables = {}
 
     def _local(self) -> List[nn.Module]:
         return [e for e in self._experts if not isinstance(e, DummyExpert)]
@@ -244,14 +245,22 @@ class ExpertPack:
         ExpertPack.timing.append((self.tag, start, end))
         return out
 
+    def slab_table(self, seg_slab: Sequence[int], device) -> torch.Tensor:
+        """Device copy of a segment -> weight-slab table (cached: it only depends on world size and slots)."""
+        key = (tuple(seg_slab), str(device))
+        hit = self._slab_tables.get(key)
+        if hit is None:
+            hit = torch.tensor(list(seg_slab), dtype=torch.int32, device=device)
+            self._slab_tables[key] = hit
+        return hit
+
     def run_segments(self, rows: torch.Tensor, seg_counts: Sequence[int], seg_slab: Sequence[int]):
         """Segments given as host-side counts (the expert-parallel receive layout)."""
         offs = [0]
         for c in seg_counts:
             offs.append(offs[-1] + c)
         seg = torch.tensor(offs, dtype=torch.int32, device=rows.device)
-        slab = torch.tensor(list(seg_slab), dtype=torch.int32, device=rows.device)
-        return self.run_offsets(rows, seg, slab)
+        return self.run_offsets(rows, seg, self.slab_table(seg_slab, rows.device))
 
     def check(self):
         if self.status is not None:
