@@ -60,10 +60,32 @@ def parse_args():
     ap.add_argument("--variant", default="gelu_tanh", choices=["gelu_tanh", "swiglu"])
     ap.add_argument("--layers", type=int, default=28)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    # beyond the default configurations (manual runs; the JSON line names what was run)
+    ap.add_argument("--shape", default="xl", choices=["xl", "g1792", "g1408"],
+                    help="xl: DiT-XL/2 (h=1152, 8 experts, 256 tokens/image); g1792 / g1408: DiT-G/2-like "
+                         "(16 experts, 1024 tokens/image, 8 x2 images per GPU, 40 layers)")
+    ap.add_argument("--ep-mode", default="sync", choices=["sync", "displaced", "interweaved"])
+    ap.add_argument("--ep-async-mode", default="all", choices=["all", "shallow", "deep", "interleaved"])
+    ap.add_argument("--auto-gc", action="store_true", help="drop send buffers of completed exchanges (ep_cache_init auto_gc)")
+    ap.add_argument("--skip", action="store_true", help="conditional communication: noskip step 2, 'low' strategy")
     return ap.parse_args()
 
 
-def workload(n_gpus: int):
+def apply_shape(args):
+    global HIDDEN, EXPERTS, TOKENS_PER_IMAGE
+    if args.shape != "xl":
+        HIDDEN = 1792 if args.shape == "g1792" else 1408
+        EXPERTS = 16
+        TOKENS_PER_IMAGE = 1024
+        if args.layers == 28:
+            args.layers = 40
+
+
+def workload(n_gpus: int, shape: str = "xl"):
+    if shape != "xl":
+        tokens = 8 * 2 * TOKENS_PER_IMAGE
+        return tokens, (f"DiT-G/2-MoE-like MoE blocks (hidden {HIDDEN}, 16 experts), {n_gpus} GPU(s): per-GPU batch 8 x2 CFG x "
+                        f"1024 tokens")
     images = 32 if n_gpus == 1 else 16
     tokens = images * 2 * TOKENS_PER_IMAGE
     name = ("DiT-XL/2-MoE MoE blocks, 1 GPU: batch 32 x2 CFG x 256 tokens" if n_gpus == 1 else
@@ -189,9 +211,21 @@ def run_ours(args):
     if ep:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=device)
-    tokens, wl_name = workload(world)
-    para_mode = ParaMode(ep=ep)
+    tokens, wl_name = workload(world, args.shape)
+    is_async = ep and args.ep_mode != "sync"
+    para_mode = ParaMode(ep=ep, ep_async=is_async, ep_async_mode=args.ep_async_mode if is_async else None,
+                         ep_async_warm_up=0, strided_sync=0, ep_async_cool_down=0)
     blocks = build_blocks(args.layers, args.variant, para_mode, device)
+    step_counter = [10 ** 6]
+    if ep:
+        from dice_b200.expertpara import diep, ep_fwd
+
+        diep.ep_cache_init(args.layers, auto_gc=args.auto_gc, noskip_step=2 if args.skip else 1,
+                           skip_mode="low" if args.skip else None, async_pipeline=args.ep_mode == "interweaved",
+                           selective_async_strategy=args.ep_async_mode if is_async else None)
+        ep_fwd.use_latest_expert_weights(True)
+        wl_name += f", {args.ep_mode} exchange" + (f" ({args.ep_async_mode} layers async)" if is_async else "") + (
+            ", conditional communication" if args.skip else "")
     gen = torch.Generator(device=device).manual_seed(1000 + rank)
     # one distinct input per layer: together with >150 MB of expert weights per layer the working set
     # between two uses of any buffer is far larger than the 126 MB L2
@@ -201,13 +235,25 @@ def run_ours(args):
     host_out = torch.empty_like(host_in).pin_memory()
     dev_in = torch.empty_like(xs[0])
 
+    def begin_step(forced=False):
+        # what the sampler does around each model call (rectified_flow.py:91-114)
+        if not ep:
+            return
+        step_counter[0] -= 1
+        diep.ep_set_step(step_counter[0])
+        if forced:
+            diep.diep_force_sync()
+            diep.ep_cache_clear()
+
     def step_device():
+        begin_step()
         y = None
         for blk, x in zip(blocks, xs):
             y = blk(x)
         return y
 
     def step_e2e():
+        begin_step()
         dev_in.copy_(host_in, non_blocking=True)
         y = None
         for blk in blocks:
@@ -236,6 +282,11 @@ def run_ours(args):
             dist.all_reduce(ms, op=dist.ReduceOp.MAX)
         return float(ms.item()), clocks
 
+    if is_async:  # the first step of a sampling run is always synchronous and fills the caches
+        begin_step(forced=True)
+        for blk, x in zip(blocks, xs):
+            blk(x)
+        diep.diep_cancel_sync()
     for _ in range(max(args.warmup, 3)):
         step_device()
     # FFN launch durations, measured on the launching stream inside the timed region
@@ -341,7 +392,7 @@ def run_reference(args):
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if rank != 0:
         return
-    tokens, wl_name = workload(world)
+    tokens, wl_name = workload(world, args.shape)
     # torchrun exports OMP_NUM_THREADS=1; the reference arm may use every host core
     torch.set_num_threads(max(1, os.cpu_count() or 1))
     threads = torch.get_num_threads()
@@ -382,6 +433,7 @@ def run_reference(args):
 
 def main():
     args = parse_args()
+    apply_shape(args)
     if args.impl == "reference":
         run_reference(args)
     else:

@@ -200,7 +200,6 @@ def ep_skip_put(key, tensor):
 # ---- the two protocols (diep.py:178-310) ------------------------------------------
 
 
-@torch.no_grad()
 def _wait(handles):
     if handles is not None:
         for handle in handles:

@@ -116,7 +116,6 @@ def exchange_token_counts(token_counts_local: torch.Tensor) -> torch.Tensor:
     return torch.stack(gathered, dim=0)[:, rank::world_size]
 
 
-@torch.no_grad()
 def _exchange_counts_by_owner(counts_key: torch.Tensor, world_size: int, rank: int) -> Tuple[torch.Tensor, torch.Tensor]:
     """All-gather the local counts, which are laid out ``[owner rank][slot]``,
     and bring the ``[W, E]`` matrix to the host once.  Returns CPU int64
@@ -145,7 +144,6 @@ def _exchange_counts_by_owner(counts_key: torch.Tensor, world_size: int, rank: i
 # --------------------------------------------------------------------------- #
 
 
-@torch.no_grad()
 def _all_to_all_rows(send: torch.Tensor, in_counts: torch.Tensor, out_counts: torch.Tensor, async_op: bool):
     """One uneven all-to-all of rows.  ``in_counts``/``out_counts`` are CPU
     ``[W, El]`` tensors; the split towards/from a rank is the row sum."""

@@ -41,7 +41,8 @@ def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
 
 
 def _stream() -> int:
-    return torch.cuda.current_stream().cuda_stream
+    # the raw handle of torch's current stream on the current device (the Stream object is slow to build)
+    return torch._C._cuda_getCurrentRawStream(torch.cuda.current_device())
 
 
 def check_status(status: torch.Tensor, what: str = "dice_b200 kernel") -> None:
