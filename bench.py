@@ -66,6 +66,8 @@ def parse_args():
                          "(16 experts, 1024 tokens/image, 8 x2 images per GPU, 40 layers)")
     ap.add_argument("--ep-mode", default="sync", choices=["sync", "displaced", "interweaved"])
     ap.add_argument("--ep-async-mode", default="all", choices=["all", "shallow", "deep", "interleaved"])
+    ap.add_argument("--nccl-exchange", action="store_true",
+                    help="synchronous expert parallelism through NCCL all-to-all instead of the NVLink peer-memory exchange")
     ap.add_argument("--auto-gc", action="store_true", help="drop send buffers of completed exchanges (ep_cache_init auto_gc)")
     ap.add_argument("--skip", action="store_true", help="conditional communication: noskip step 2, 'low' strategy")
     return ap.parse_args()
@@ -180,6 +182,9 @@ def kernels_per_block(variant, ep):
     n = 1 + 3 + 1 + 2 + 1
     if variant == "swiglu":
         n += 2
+    if ep:
+        # peer-memory exchange: counts, dispatch (replaces the row gather), 2 flag waits, return
+        n += 4
     return n
 
 
@@ -224,6 +229,9 @@ def run_ours(args):
                            skip_mode="low" if args.skip else None, async_pipeline=args.ep_mode == "interweaved",
                            selective_async_strategy=args.ep_async_mode if is_async else None)
         ep_fwd.use_latest_expert_weights(True)
+        from dice_b200.expertpara import p2p
+
+        p2p.enable(not args.nccl_exchange)
         wl_name += f", {args.ep_mode} exchange" + (f" ({args.ep_async_mode} layers async)" if is_async else "") + (
             ", conditional communication" if args.skip else "")
     gen = torch.Generator(device=device).manual_seed(1000 + rank)
@@ -298,6 +306,11 @@ def run_ours(args):
     routed = [s.elapsed_time(e) for tag, s, e in ffn_events if tag == "routed"]
     for blk in blocks:
         blk.check_status()
+    exchange = "nccl"
+    if ep:
+        if p2p._exchange is not None:
+            p2p._exchange.check()
+            exchange = "nvlink peer memory (own kernels)" if not is_async else "nccl"
 
     for _ in range(2):
         step_e2e()
@@ -325,7 +338,7 @@ def run_ours(args):
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": wl_name, "variant": args.variant, "layers_per_step": args.layers, "tokens_per_gpu": tokens,
                    "hidden": HIDDEN, "experts": EXPERTS, "top_k": 2, "ffn": MLP_RATIO * HIDDEN,
-                   "parallelism": "ep%d" % world if ep else "single",
+                   "parallelism": "ep%d" % world if ep else "single", "exchange": exchange if ep else None,
                    "l2": "per-layer inputs and weights (>150 MB per layer) exceed the 126 MB L2; no explicit flush"},
         "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "ms_per_step": round(e2e_ms / args.steps, 4),
                 "h2d_bytes_per_step": host_in.numel() * 2, "d2h_bytes_per_step": host_out.numel() * 2},

@@ -50,6 +50,21 @@ SIGNATURES = {
         [c_void_p, c_int64, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p,
          c_void_p, c_void_p],
     ),
+    "dice_ep_meta_ints": (c_int, [c_int, c_int]),
+    "dice_ep_exchange_counts": (
+        c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_uint32, c_void_p, c_void_p]),
+    "dice_ep_dispatch_rows": (
+        c_int,
+        [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int,
+         c_int, c_int, c_uint32, c_void_p, c_void_p]),
+    "dice_ep_wait_flags": (c_int, [c_void_p, c_int, c_uint32, c_int, c_void_p, c_void_p]),
+    "dice_ep_return_rows": (
+        c_int,
+        [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_uint32, c_void_p,
+         c_void_p]),
+    "dice_ipc_export": (c_int, [c_void_p, c_void_p, c_void_p]),
+    "dice_ipc_import": (c_int, [c_void_p, ctypes.c_uint64, c_void_p]),
+    "dice_ipc_close": (c_int, [c_void_p, ctypes.c_uint64]),
 }
 
 ABI_VERSION = 1

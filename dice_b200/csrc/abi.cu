@@ -25,6 +25,10 @@ extern "C" const char* dice_status_message(uint32_t status) {
     case DICE_STATUS_WAIT_ACC_FULL: return "timed out waiting for an accumulator to complete";
     case DICE_STATUS_WAIT_ACC_EMPTY: return "timed out waiting for an accumulator to be drained";
     case DICE_STATUS_BAD_SEGMENTS: return "segment offsets are not monotone or exceed the row count";
+    case DICE_STATUS_WAIT_PEER_COUNTS: return "timed out waiting for a peer rank's row counts";
+    case DICE_STATUS_WAIT_PEER_DISPATCH: return "timed out waiting for a peer rank's dispatched rows";
+    case DICE_STATUS_WAIT_PEER_COMBINE: return "timed out waiting for a peer rank's expert outputs";
+    case DICE_STATUS_EXCHANGE_OVERFLOW: return "a rank received more rows than its exchange buffer holds";
     default: return "unknown device status";
   }
 }

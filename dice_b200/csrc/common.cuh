@@ -23,6 +23,10 @@
 #define DICE_STATUS_WAIT_ACC_FULL 3u    // epilogue warps: accumulator never completed
 #define DICE_STATUS_WAIT_ACC_EMPTY 4u   // tensor-core warp: accumulator never drained
 #define DICE_STATUS_BAD_SEGMENTS 5u     // segment offsets not monotone / beyond n_rows
+#define DICE_STATUS_WAIT_PEER_COUNTS 6u    // exchange: a peer's row counts never arrived
+#define DICE_STATUS_WAIT_PEER_DISPATCH 7u  // exchange: a peer's dispatched rows never arrived
+#define DICE_STATUS_WAIT_PEER_COMBINE 8u   // exchange: a peer's expert outputs never arrived
+#define DICE_STATUS_EXCHANGE_OVERFLOW 9u   // exchange: more rows than the receive buffer holds
 
 static inline bool dice_aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 

@@ -30,7 +30,7 @@ import torch
 import torch.distributed as dist
 import torch.nn as nn
 
-from . import diep
+from . import diep, p2p
 from .diep import ep_skip_get, ep_skip_put, global_combine_async, global_dispatch_async  # noqa: F401
 
 _use_latest_expert_weights = None
@@ -215,6 +215,53 @@ def proc_experts(inp, experts, token_counts_global, num_local_experts):
 # --------------------------------------------------------------------------- #
 
 
+def _exchange_p2p(xchg, inp, pos, seg_offsets, k_eff, experts, num_local_experts):
+    """Counts -> dispatch -> expert FFN -> return, all on the current stream and
+    all device-side: rows are written straight into the expert owners' receive
+    buffers over NVLink and come back the same way (csrc/p2p_exchange.cu)."""
+    from .. import _lib
+    from ..ops import _dtype_code, _stream
+
+    lib = xchg.lib
+    slot, seq, tab = xchg.begin()
+    stream = _stream()
+    status = xchg.status.data_ptr()
+    meta = xchg.meta[slot]
+    n_tokens, hidden = inp.shape
+    inp = inp.contiguous()
+    with _scope("exchange_token_counts"):
+        _lib.check(lib.dice_ep_exchange_counts(seg_offsets.data_ptr(), tab["matrix"], tab["f_cnt"], meta.data_ptr(),
+                                               xchg.rank, xchg.world, xchg.n_experts, xchg.capacity_rows, seq, status,
+                                               stream), "dice_ep_exchange_counts")
+    with _scope("global_dispatch"):
+        _lib.check(lib.dice_ep_dispatch_rows(inp.data_ptr(), pos.data_ptr(), seg_offsets.data_ptr(), meta.data_ptr(),
+                                             tab["recv"], tab["f_disp"], xchg.done[2 * slot:].data_ptr(), n_tokens, k_eff,
+                                             hidden, _dtype_code(inp), xchg.rank, xchg.world, xchg.n_experts,
+                                             xchg.min_peer_cap, seq, status, stream), "dice_ep_dispatch_rows")
+        _lib.check(lib.dice_ep_wait_flags(xchg.my_flags_ptr(slot, 1), xchg.world, seq, 0, status, stream),
+                   "dice_ep_wait_flags")
+    recv = xchg.recv[slot]
+    with _scope("moe.mlp"):
+        pack = getattr(experts, "_dice_pack", None)
+        seg_slab = [i for _ in range(xchg.world) for i in range(num_local_experts)]
+        if pack is not None:
+            mlp_outp = pack.run_offsets(recv, xchg.seg_offsets(slot), pack.slab_table(seg_slab, recv.device))
+        else:  # arbitrary row-wise expert modules: segment bounds are needed on the host
+            offs = xchg.seg_offsets(slot).tolist()
+            mlp_outp = torch.empty_like(recv)
+            for j, slot_i in enumerate(seg_slab):
+                if offs[j + 1] > offs[j]:
+                    mlp_outp[offs[j]:offs[j + 1]] = experts[xchg.rank + slot_i * xchg.world](recv[offs[j]:offs[j + 1]])
+    with _scope("global_combine"):
+        _lib.check(lib.dice_ep_return_rows(mlp_outp.data_ptr(), meta.data_ptr(), tab["back"], tab["f_back"],
+                                           xchg.done[2 * slot + 1:].data_ptr(), hidden, _dtype_code(inp), xchg.rank,
+                                           xchg.world, min(xchg.peer_max_rows), xchg.capacity_rows, seq, status, stream),
+                   "dice_ep_return_rows")
+        _lib.check(lib.dice_ep_wait_flags(xchg.my_flags_ptr(slot, 2), xchg.world, seq, 1, status, stream),
+                   "dice_ep_wait_flags")
+    return xchg.back[slot][: n_tokens * k_eff]
+
+
 def _slot_views(skip_mask: torch.Tensor, n_tokens: int, device) -> Tuple[Optional[int], torch.Tensor]:
     """From the reference's boolean row mask (one True per token pair,
     diep.py:72-90) derive the skipped slot: a constant for the 'high'/'low'
@@ -290,6 +337,15 @@ def moe_infer_ep(inp: torch.Tensor, experts: nn.ModuleList, flat_expert_indices,
     # sort key = (owner rank, local slot): rows for one destination are contiguous
     keys = (flat_idx % world_size) * num_local_experts + torch.div(flat_idx, world_size, rounding_mode="floor")
     pos, seg_offsets = _ops.plan(keys, num_total_experts)
+
+    # synchronous exchange over NVLink peer memory: counts, dispatch and combine without NCCL or host sync
+    if not async_op and inp.is_cuda and p2p.enabled():
+        xchg = p2p.get_exchange(num_total_experts, hidden, inp.dtype, n_tokens * k_full)
+        if xchg is not None:
+            grouped_dup_outp = _exchange_p2p(xchg, inp, pos, seg_offsets, k_eff, experts, num_local_experts)
+            return _finish(grouped_dup_outp, pos, flat_expert_weights, flat_expert_weights, n_tokens, hidden, k_full,
+                           partial_skip, const_slot, per_tok, cache_key, _addend, inp)
+
     with _scope("exchange_token_counts"):
         counts_local, counts_global = _exchange_counts_by_owner(seg_offsets[1:] - seg_offsets[:-1], world_size, rank)
     assert int(counts_local.sum()) == n_tokens * k_eff, "expert index out of range"
@@ -318,7 +374,14 @@ def moe_infer_ep(inp: torch.Tensor, experts: nn.ModuleList, flat_expert_indices,
                 grouped_dup_outp=mlp_outp, token_counts_local=counts_local, token_counts_global=counts_global,
                 grouped_idx_dup=pos, flat_expert_weights=flat_expert_weights, cache_key=cache_key)
 
-    # un-permute, merge with the skip cache, scale by the gate weights and sum each token's pair (:172-195)
+    return _finish(grouped_dup_outp, pos, latest_flat_expert_weights, flat_expert_weights, n_tokens, hidden, k_full,
+                   partial_skip, const_slot, per_tok, cache_key, _addend, inp)
+
+
+def _finish(grouped_dup_outp, pos, latest_flat_expert_weights, flat_expert_weights, n_tokens, hidden, k_full,
+            partial_skip, const_slot, per_tok, cache_key, _addend, inp):
+    """Un-permute, merge with the skip cache, scale by the gate weights and sum
+    each token's pair (ep_fwd.py:172-195) in one kernel."""
     weights = latest_flat_expert_weights if _use_latest_expert_weights else flat_expert_weights
     w_pairs = weights.reshape(n_tokens, k_full)
     if w_pairs.dtype != torch.float32:

@@ -212,6 +212,53 @@ DICE_API int dice_grouped_ffn_f32(const void* rows_in, int64_t n_rows, int hidde
                          const int32_t* seg_slab, int n_seg, void* inter, void* rows_out,
                          void* stream);
 
+/* ---------------------------------------------------------------------------
+ * Expert-parallel exchange over NVLink peer memory (one process per GPU, one
+ * box).  Replaces, for the synchronous exchange, exchange_token_counts
+ * (ep_fwd.py:214-245), global_dispatch (:247-293) and global_combine (:295-342)
+ * together with the host synchronisations they need for split sizes.
+ * Peers' buffers are mapped with dice_ipc_export / dice_ipc_import at set-up;
+ * `peer_*` arguments are HOST arrays of `world` device pointers (entry `rank`
+ * is this rank's own buffer).  A rank only writes into peer memory and raises
+ * flags there; waits are bounded and report through `status`.
+ *   keys are (owner rank, local slot) = owner * (n_experts / world) + slot, so
+ *   seg_offsets [n_experts+1] (from dice_permute_plan on those keys) lists this
+ *   rank's rows per destination;
+ *   meta: int32 [dice_ep_meta_ints(world, n_experts/world)], written by
+ *   dice_ep_exchange_counts: send_base[W] | back_base[W] | src_off[W+1] |
+ *   seg_off[W*El+1] (segments of the receive buffer in (source, slot) order,
+ *   ready for dice_grouped_ffn with seg_slab[s*El+i] = i) | total, overflow;
+ *   seq: a number that grows with every use of the same buffers;
+ *   done_counter: device uint32, zero before first use, one per call site.
+ */
+DICE_API int dice_ep_meta_ints(int world, int n_local_experts);
+DICE_API int dice_ep_exchange_counts(const int32_t* seg_offsets, const void* const* peer_matrices,
+                            const void* const* peer_flags, int32_t* meta, int rank, int world,
+                            int n_experts, int capacity_rows, uint32_t seq, uint32_t* status,
+                            void* stream);
+/* permutation gather fused with the dispatch: row (t, s) goes straight into its
+ * expert owner's receive buffer (ep_fwd.py:107-111 + :277-291) */
+DICE_API int dice_ep_dispatch_rows(const void* x, const int32_t* pos, const int32_t* seg_offsets,
+                          const int32_t* meta, const void* const* peer_recv,
+                          const void* const* peer_flags, uint32_t* done_counter, int64_t n_tokens,
+                          int k, int hidden, int dtype, int rank, int world, int n_experts,
+                          int capacity_rows, uint32_t seq, uint32_t* status, void* stream);
+/* wait (bounded) until every source raised flag >= seq; what: 0 dispatch, 1 combine */
+DICE_API int dice_ep_wait_flags(const uint32_t* my_flags, int world, uint32_t seq, int what,
+                       uint32_t* status, void* stream);
+/* expert outputs back to the token owners, in the order the rows were sent
+ * (ep_fwd.py:326-340); max_rows bounds the rows received (grid sizing only) */
+DICE_API int dice_ep_return_rows(const void* rows, const int32_t* meta, const void* const* peer_back,
+                        const void* const* peer_flags, uint32_t* done_counter, int hidden, int dtype,
+                        int rank, int world, int back_capacity_rows, int max_rows, uint32_t seq,
+                        uint32_t* status, void* stream);
+/* CUDA IPC plumbing for the above (set-up time): export the allocation that
+ * holds `ptr` (64-byte handle + offset of ptr inside it); import maps a peer's
+ * allocation into this process and enables peer access. */
+DICE_API int dice_ipc_export(const void* ptr, uint8_t* out_handle64, uint64_t* out_offset);
+DICE_API int dice_ipc_import(const uint8_t* handle64, uint64_t offset, void** out_ptr);
+DICE_API int dice_ipc_close(void* imported_ptr, uint64_t offset);
+
 #ifdef __cplusplus
 }
 #endif

@@ -46,7 +46,7 @@ def main():
         err = ((a.float() - b).norm() / b.norm()).item()
         assert err < 2e-2, f"rank {rank} {what}: rel err {err}"
 
-    def run(pm, cache_kwargs, check):
+    def run(pm, cache_kwargs, check, collect=None):
         blocks = [make(pm, l) for l in range(layers)]
         diep.ep_cache_init(layers, **cache_kwargs)
         ep_fwd.use_latest_expert_weights(False)
@@ -60,12 +60,28 @@ def main():
                 y = blocks[l](xs[t][l])
                 assert y.shape == xs[t][l].shape and bool(torch.isfinite(y.float()).all())
                 check(t, l, y)
+                if collect is not None:
+                    collect.append(y.clone())
             if forced:
                 diep.diep_cancel_sync()
         for b in blocks:
             b.check_status()
 
-    run(ParaMode(ep=True), {}, lambda t, l, y: close(y, want[t][l], f"sync t={t} l={l}"))
+    from dice_b200.expertpara import p2p
+
+    nccl_sync, nccl_skip = [], []
+    run(ParaMode(ep=True), {}, lambda t, l, y: close(y, want[t][l], f"sync t={t} l={l}"), nccl_sync)
+    run(ParaMode(ep=True), dict(noskip_step=2, skip_mode="low"), lambda t, l, y: None, nccl_skip)
+    # the same two runs over NVLink peer memory (no NCCL, no host sync): same kernels, same order -> same bits
+    p2p.enable(True)
+    peer_sync, peer_skip = [], []
+    run(ParaMode(ep=True), {}, lambda t, l, y: close(y, want[t][l], f"peer sync t={t} l={l}"), peer_sync)
+    run(ParaMode(ep=True), dict(noskip_step=2, skip_mode="low"), lambda t, l, y: None, peer_skip)
+    assert p2p.enabled() and p2p._exchange is not None, "peer-memory exchange was not used"
+    p2p._exchange.check()
+    for a_, b_ in zip(nccl_sync + nccl_skip, peer_sync + peer_skip):
+        assert torch.equal(a_, b_), f"rank {rank}: peer-memory exchange differs from the NCCL exchange"
+    p2p.enable(False)
     a = dict(ep=True, ep_async=True, ep_async_mode="all", ep_async_warm_up=0, strided_sync=0, ep_async_cool_down=0)
     run(ParaMode(**a), dict(async_pipeline=False, selective_async_strategy="all"),
         lambda t, l, y: close(y, want[max(0, t - 2)][l], f"displaced t={t} l={l}"))

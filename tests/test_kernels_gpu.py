@@ -295,3 +295,79 @@ def test_linearity_full_size_ffn_gemm(cuda_device):
         torch.testing.assert_close(out[row].float(), want, rtol=2e-2, atol=2e-2)
     out2 = ops.grouped_gemm((a * 2).contiguous(), w, seg, ops.EPI_STORE, n, status)
     torch.testing.assert_close(out2.float(), out.float() * 2, rtol=1e-2, atol=1e-2)
+
+
+def test_exchange_wait_runs_out_and_reports(cuda_device):
+    """Failure detection without a fault: a flag that nothing raises makes the
+    bounded wait expire; the kernel returns, the status word names the reason
+    and the context stays usable."""
+    import time
+
+    from dice_b200 import _lib
+
+    ops = _ops()
+    lib = _lib.load()
+    flags = torch.zeros(8, dtype=torch.int32, device=cuda_device)
+    status = torch.zeros(1, dtype=torch.int32, device=cuda_device)
+    t0 = time.time()
+    rc = lib.dice_ep_wait_flags(flags.data_ptr(), 2, 1, 0, status.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert 1.0 < time.time() - t0 < 10.0
+    with pytest.raises(RuntimeError, match="dispatched rows"):
+        ops.check_status(status)
+    # a raised flag passes at once, and the device still works
+    flags.fill_(5)
+    rc = lib.dice_ep_wait_flags(flags.data_ptr(), 2, 5, 1, status.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    ops.check_status(status)
+    assert int((flags + 1).sum()) == 48
+
+
+def test_exchange_world_of_one(cuda_device):
+    """The four exchange kernels on one GPU (world of one rank: every 'peer' is
+    the rank itself): dispatch + return reproduce the plain permutation."""
+    import ctypes
+
+    from dice_b200 import _lib
+
+    ops = _ops()
+    lib = _lib.load()
+    n, h, e = 777, 256, 8
+    g = torch.Generator().manual_seed(4)
+    x = torch.randn(n, h, generator=g).bfloat16().to(cuda_device)
+    flat = torch.randint(0, e, (2 * n,), generator=g).to(cuda_device)
+    pos, seg, _ = ops.permute_plan(flat, e)
+    cap = 2 * n + 5
+    ctrl = torch.zeros(e + 3 * 64, dtype=torch.int32, device=cuda_device)
+    recv = torch.full((cap, h), 3.0, dtype=torch.bfloat16, device=cuda_device)
+    back = torch.zeros((2 * n, h), dtype=torch.bfloat16, device=cuda_device)
+    meta = torch.zeros(lib.dice_ep_meta_ints(1, e), dtype=torch.int32, device=cuda_device)
+    done = torch.zeros(2, dtype=torch.int32, device=cuda_device)
+    status = torch.zeros(1, dtype=torch.int32, device=cuda_device)
+    st = torch.cuda.current_stream().cuda_stream
+    tab = lambda p: (ctypes.c_void_p * 1)(p)
+    f = lambda i: ctrl.data_ptr() + (e + 64 * i) * 4
+    for seq in (1, 2):  # twice: the done counters and flags must be reusable
+        assert lib.dice_ep_exchange_counts(seg.data_ptr(), tab(ctrl.data_ptr()), tab(f(0)), meta.data_ptr(), 0, 1, e, cap,
+                                           seq, status.data_ptr(), st) == 0
+        assert lib.dice_ep_dispatch_rows(x.data_ptr(), pos.data_ptr(), seg.data_ptr(), meta.data_ptr(), tab(recv.data_ptr()),
+                                         tab(f(1)), done.data_ptr(), n, 2, h, 0, 0, 1, e, cap, seq, status.data_ptr(), st) == 0
+        assert lib.dice_ep_wait_flags(f(1), 1, seq, 0, status.data_ptr(), st) == 0
+        assert lib.dice_ep_return_rows(recv.data_ptr(), meta.data_ptr(), tab(back.data_ptr()), tab(f(2)), done[1:].data_ptr(),
+                                       h, 0, 0, 1, 2 * n, cap, seq, status.data_ptr(), st) == 0
+        assert lib.dice_ep_wait_flags(f(2), 1, seq, 1, status.data_ptr(), st) == 0
+        torch.cuda.synchronize()
+        ops.check_status(status)
+        want = ops.permute_rows(x, pos, 2)
+        assert torch.equal(recv[: 2 * n], want) and torch.equal(back, want)
+        assert bool((recv[2 * n:] == 3.0).all())
+        m = meta.cpu().tolist()
+        assert m[0] == 0 and m[1] == 0 and m[2:4] == [0, 2 * n]           # send_base, back_base, src_off
+        assert m[4:4 + e + 1] == seg.cpu().tolist() and m[4 + e + 1] == 2 * n and m[4 + e + 2] == 0
+    # a receive buffer that is too small is reported, not overrun
+    assert lib.dice_ep_exchange_counts(seg.data_ptr(), tab(ctrl.data_ptr()), tab(f(0)), meta.data_ptr(), 0, 1, e, 100, 3,
+                                       status.data_ptr(), st) == 0
+    torch.cuda.synchronize()
+    with pytest.raises(RuntimeError, match="more rows"):
+        ops.check_status(status)
