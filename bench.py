@@ -310,7 +310,7 @@ def run_ours(args):
     if ep:
         if p2p._exchange is not None:
             p2p._exchange.check()
-            exchange = "nvlink peer memory (own kernels)" if not is_async else "nccl"
+            exchange = "nvlink peer memory (own kernels)"
 
     for _ in range(2):
         step_e2e()

@@ -248,8 +248,11 @@ def global_dispatch_async(grouped_dup_inp, token_counts_local, token_counts_glob
     _wait(prev_handles)
     _diep_cache_dispatch.manual_gc_recv_buf()
     buf, handles = global_dispatch(grouped_dup_inp, token_counts_local, token_counts_global, async_op=True)
+    # the send side stays alive until the exchange completes: the gathered rows, or (peer-memory exchange,
+    # where the gather is part of the dispatch kernel) the layer input itself
+    send_buf = getattr(grouped_dup_inp, "keepalive", grouped_dup_inp)
     _diep_cache_dispatch.put(cache_key, (handles, buf, token_counts_local, token_counts_global, grouped_idx_dup,
-                                         flat_expert_weights, experts, grouped_dup_inp))
+                                         flat_expert_weights, experts, send_buf))
     global max_mem
     max_mem = max(max_mem, ep_cached_tensors_size())
     return prev_buf, prev_counts_local, prev_counts_global, prev_pos, prev_weights, prev_experts

@@ -38,6 +38,7 @@ class All2AllCache:
         self.gc_recv_buf = gc_recv_buf
         self.cl_name = cl_name
         self.cache: List[Optional[Tuple]] = [None] * capacity
+        self._bytes: List[int] = [0] * capacity  # tensor bytes per slot, kept current by put / release / clear
 
     # -- completion ---------------------------------------------------------
     def wait(self) -> None:
@@ -49,6 +50,7 @@ class All2AllCache:
 
     def clear(self) -> None:
         self.cache = [None] * self.capacity
+        self._bytes = [0] * self.capacity
 
     # -- access ---------------------------------------------------------------
     def put(self, key: int, value: Tuple) -> None:
@@ -60,6 +62,7 @@ class All2AllCache:
         if self.gc_send_buf:
             self._release(SEND_BUF_IDX, clear_handles=True)
         self.cache[key] = value
+        self._bytes[key] = sum(_tensor_bytes(x) for x in value)
 
     def get(self, key: int) -> Tuple:
         """Return the tuple under ``key`` without removing it (ep_cache.py:114-124)."""
@@ -78,6 +81,7 @@ class All2AllCache:
                 item = list(entry)
                 if clear_handles:
                     item[HANDLES_IDX] = None
+                self._bytes[i] -= _tensor_bytes(item[field])
                 item[field] = None
                 self.cache[i] = tuple(item)
 
@@ -91,7 +95,7 @@ class All2AllCache:
 
     def tensors_size(self) -> int:
         """Bytes of all tensors held (ep_cache.py:169-186)."""
-        return sum(sum(_tensor_bytes(x) for x in entry) for entry in self.cache if entry is not None)
+        return sum(self._bytes)
 
 
 class EPSkipCache:

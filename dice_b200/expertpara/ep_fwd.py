@@ -165,15 +165,62 @@ def global_dispatch(grouped_dup_inp, token_counts_local, token_counts_global, as
 
     ``token_counts_local`` / ``token_counts_global`` are the CPU ``[W, E/W]``
     send / receive counts.  Returns ``(recv_buf, handles)``; the receive
-    buffer is ordered ``[source rank][local slot]``."""
+    buffer is ordered ``[source rank][local slot]``.
+
+    With the peer-memory exchange the first argument is a
+    :class:`p2p.PendingRows`: the row gather and the dispatch are one kernel
+    that writes every row into its owner's receive buffer over NVLink, on the
+    current stream, or on the exchange's side stream when ``async_op``."""
+    if isinstance(grouped_dup_inp, p2p.PendingRows):
+        return _peer_push(grouped_dup_inp.info, async_op, dispatch=grouped_dup_inp)
     return _all_to_all_rows(grouped_dup_inp, token_counts_local, token_counts_global, async_op)
 
 
 @torch.no_grad()
 def global_combine(grouped_dup_outp, token_counts_local, token_counts_global, async_op=False):
     """Return expert outputs to the token owners; the mirror image of
-    :func:`global_dispatch` (ep_fwd.py:295-342)."""
+    :func:`global_dispatch` (ep_fwd.py:295-342).  With the peer-memory exchange
+    ``token_counts_global`` is the :class:`p2p.SegInfo` of the dispatch being
+    answered and the rows are written into the token owners' buffers."""
+    if isinstance(token_counts_global, p2p.SegInfo):
+        return _peer_push(token_counts_global, async_op, rows_back=grouped_dup_outp)
     return _all_to_all_rows(grouped_dup_outp, token_counts_global, token_counts_local, async_op)
+
+
+def _peer_push(info, async_op, dispatch=None, rows_back=None):
+    """Launch one push of the peer-memory exchange (csrc/p2p_exchange.cu) and
+    return ``(buffer the peers fill for this rank, [handle])``."""
+    from .. import _lib
+    from ..ops import _dtype_code, _stream
+
+    x = info.xchg
+    lib, tab, slot = x.lib, info.tab, info.slot
+    if async_op:
+        stream = x.fork_to_comm()  # the push runs on the side stream, after what the current stream has produced
+        # the caching allocator must not hand these to someone else before the side stream has read them
+        for t in ((dispatch.inp, dispatch.pos, dispatch.seg_offsets) if dispatch is not None else (rows_back,)):
+            t.record_stream(x._comm)
+    else:
+        stream = _stream()
+    if dispatch is not None:
+        inp = dispatch.inp
+        _lib.check(lib.dice_ep_dispatch_rows(
+            inp.data_ptr(), dispatch.pos.data_ptr(), dispatch.seg_offsets.data_ptr(), x._meta_ptrs[slot], tab["recv"],
+            tab["f_disp"], x._done_ptrs[2 * slot], inp.shape[0], dispatch.k_eff, inp.shape[1], _dtype_code(inp), x.rank,
+            x.world, x.n_experts, x.min_peer_cap, info.seq, x.status_ptr, stream), "dice_ep_dispatch_rows")
+        out, which = x._recv_views[slot], 0
+    else:
+        _lib.check(lib.dice_ep_return_rows(
+            rows_back.data_ptr(), x._meta_ptrs[slot], tab["back"], tab["f_back"], x._done_ptrs[2 * slot + 1], x.hidden,
+            _dtype_code(rows_back), x.rank, x.world, x.min_peer_rows, x.capacity_rows, info.seq, x.status_ptr, stream),
+            "dice_ep_return_rows")
+        out, which = x.back[slot][: info.rows_sent], 1
+    event = None
+    handle = p2p.PeerHandle(info, which, event)
+    with _scope("moe.wait"):
+        if not async_op:
+            handle.wait()
+    return out, [handle]
 
 
 # --------------------------------------------------------------------------- #
@@ -191,6 +238,17 @@ def proc_experts(inp, experts, token_counts_global, num_local_experts):
     packed weights and run as one grouped-FFN launch pair; any other list of
     row-wise modules is called segment by segment, as the reference does."""
     world_size, rank = dist.get_world_size(), dist.get_rank()
+    if isinstance(token_counts_global, p2p.SegInfo):
+        seg_slab = [i for _ in range(world_size) for i in range(num_local_experts)]
+        pack = getattr(experts, "_dice_pack", None)
+        if pack is not None:
+            return pack.run_offsets(inp, token_counts_global.seg_dev, token_counts_global.xchg.seg_slab_dev)
+        offs = token_counts_global.seg_dev.tolist()  # arbitrary expert modules need the bounds on the host
+        outp = torch.empty_like(inp)
+        for j, slot in enumerate(seg_slab):
+            if offs[j + 1] > offs[j]:
+                outp[offs[j]:offs[j + 1]] = experts[rank + slot * world_size](inp[offs[j]:offs[j + 1]])
+        return outp
     counts = token_counts_global.tolist()  # CPU tensor: no device sync
     seg_counts = [counts[s][i] for s in range(world_size) for i in range(num_local_experts)]
     seg_slab = [i for _ in range(world_size) for i in range(num_local_experts)]
@@ -213,53 +271,6 @@ def proc_experts(inp, experts, token_counts_global, num_local_experts):
 # --------------------------------------------------------------------------- #
 # the forward
 # --------------------------------------------------------------------------- #
-
-
-def _exchange_p2p(xchg, inp, pos, seg_offsets, k_eff, experts, num_local_experts):
-    """Counts -> dispatch -> expert FFN -> return, all on the current stream and
-    all device-side: rows are written straight into the expert owners' receive
-    buffers over NVLink and come back the same way (csrc/p2p_exchange.cu)."""
-    from .. import _lib
-    from ..ops import _dtype_code, _stream
-
-    lib = xchg.lib
-    slot, seq, tab = xchg.begin()
-    stream = _stream()
-    status = xchg.status.data_ptr()
-    meta = xchg.meta[slot]
-    n_tokens, hidden = inp.shape
-    inp = inp.contiguous()
-    with _scope("exchange_token_counts"):
-        _lib.check(lib.dice_ep_exchange_counts(seg_offsets.data_ptr(), tab["matrix"], tab["f_cnt"], meta.data_ptr(),
-                                               xchg.rank, xchg.world, xchg.n_experts, xchg.capacity_rows, seq, status,
-                                               stream), "dice_ep_exchange_counts")
-    with _scope("global_dispatch"):
-        _lib.check(lib.dice_ep_dispatch_rows(inp.data_ptr(), pos.data_ptr(), seg_offsets.data_ptr(), meta.data_ptr(),
-                                             tab["recv"], tab["f_disp"], xchg.done[2 * slot:].data_ptr(), n_tokens, k_eff,
-                                             hidden, _dtype_code(inp), xchg.rank, xchg.world, xchg.n_experts,
-                                             xchg.min_peer_cap, seq, status, stream), "dice_ep_dispatch_rows")
-        _lib.check(lib.dice_ep_wait_flags(xchg.my_flags_ptr(slot, 1), xchg.world, seq, 0, status, stream),
-                   "dice_ep_wait_flags")
-    recv = xchg.recv[slot]
-    with _scope("moe.mlp"):
-        pack = getattr(experts, "_dice_pack", None)
-        seg_slab = [i for _ in range(xchg.world) for i in range(num_local_experts)]
-        if pack is not None:
-            mlp_outp = pack.run_offsets(recv, xchg.seg_offsets(slot), pack.slab_table(seg_slab, recv.device))
-        else:  # arbitrary row-wise expert modules: segment bounds are needed on the host
-            offs = xchg.seg_offsets(slot).tolist()
-            mlp_outp = torch.empty_like(recv)
-            for j, slot_i in enumerate(seg_slab):
-                if offs[j + 1] > offs[j]:
-                    mlp_outp[offs[j]:offs[j + 1]] = experts[xchg.rank + slot_i * xchg.world](recv[offs[j]:offs[j + 1]])
-    with _scope("global_combine"):
-        _lib.check(lib.dice_ep_return_rows(mlp_outp.data_ptr(), meta.data_ptr(), tab["back"], tab["f_back"],
-                                           xchg.done[2 * slot + 1:].data_ptr(), hidden, _dtype_code(inp), xchg.rank,
-                                           xchg.world, min(xchg.peer_max_rows), xchg.capacity_rows, seq, status, stream),
-                   "dice_ep_return_rows")
-        _lib.check(lib.dice_ep_wait_flags(xchg.my_flags_ptr(slot, 2), xchg.world, seq, 1, status, stream),
-                   "dice_ep_wait_flags")
-    return xchg.back[slot][: n_tokens * k_eff]
 
 
 def _slot_views(skip_mask: torch.Tensor, n_tokens: int, device) -> Tuple[Optional[int], torch.Tensor]:
@@ -338,20 +349,30 @@ def moe_infer_ep(inp: torch.Tensor, experts: nn.ModuleList, flat_expert_indices,
     keys = (flat_idx % world_size) * num_local_experts + torch.div(flat_idx, world_size, rounding_mode="floor")
     pos, seg_offsets = _ops.plan(keys, num_total_experts)
 
-    # synchronous exchange over NVLink peer memory: counts, dispatch and combine without NCCL or host sync
-    if not async_op and inp.is_cuda and p2p.enabled():
-        xchg = p2p.get_exchange(num_total_experts, hidden, inp.dtype, n_tokens * k_full)
-        if xchg is not None:
-            grouped_dup_outp = _exchange_p2p(xchg, inp, pos, seg_offsets, k_eff, experts, num_local_experts)
-            return _finish(grouped_dup_outp, pos, flat_expert_weights, flat_expert_weights, n_tokens, hidden, k_full,
-                           partial_skip, const_slot, per_tok, cache_key, _addend, inp)
+    xchg = None
+    if inp.is_cuda and p2p.enabled():
+        # exchange over NVLink peer memory: counts, dispatch and combine are own kernels, no NCCL, no host sync
+        cached_layers = diep._diep_cache_dispatch.capacity if diep._diep_cache_dispatch is not None else 0
+        xchg = p2p.get_exchange(num_total_experts, hidden, inp.dtype, n_tokens * k_full, max(1, cached_layers))
+    if xchg is not None:
+        from .. import _lib
+        from ..ops import _stream
 
-    with _scope("exchange_token_counts"):
-        counts_local, counts_global = _exchange_counts_by_owner(seg_offsets[1:] - seg_offsets[:-1], world_size, rank)
-    assert int(counts_local.sum()) == n_tokens * k_eff, "expert index out of range"
-
-    with _scope("local_dispatch"):
-        grouped_dup_inp = _ops.permute_rows(inp, pos, k_eff)
+        inp = inp.contiguous()
+        slot, seq, tab = xchg.begin(cache_key or 0)
+        with _scope("exchange_token_counts"):
+            _lib.check(xchg.lib.dice_ep_exchange_counts(
+                seg_offsets.data_ptr(), tab["matrix"], tab["f_cnt"], xchg._meta_ptrs[slot], xchg.rank, xchg.world,
+                xchg.n_experts, xchg.capacity_rows, seq, xchg.status_ptr, _stream()), "dice_ep_exchange_counts")
+        counts_local = None
+        counts_global = p2p.SegInfo(xchg, slot, seq, tab, n_tokens * k_eff)
+        grouped_dup_inp = p2p.PendingRows(inp, pos, seg_offsets, k_eff, counts_global)
+    else:
+        with _scope("exchange_token_counts"):
+            counts_local, counts_global = _exchange_counts_by_owner(seg_offsets[1:] - seg_offsets[:-1], world_size, rank)
+        assert int(counts_local.sum()) == n_tokens * k_eff, "expert index out of range"
+        with _scope("local_dispatch"):
+            grouped_dup_inp = _ops.permute_rows(inp, pos, k_eff)
 
     latest_flat_expert_weights = flat_expert_weights
     with _scope("global_dispatch"):

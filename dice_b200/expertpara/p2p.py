@@ -8,8 +8,11 @@ the reference's ``exchange_token_counts`` / ``global_dispatch`` /
 ``global_combine`` (``expertpara/ep_fwd.py:214-342``): no NCCL call and no
 host synchronisation remain on the per-layer path.
 
-Buffers per rank (``n_slots`` copies, used round-robin so that a peer that is one
-call ahead never writes what this rank still reads):
+Buffers per rank, one set per *slot*.  A layer owns ``n_par`` slots and uses them
+in turn, so an exchange launched at one step can still be in flight, or waiting
+to be consumed, while the same layer launches the next ones (the displaced
+protocol consumes a dispatch one step and its results two steps after launch;
+peers are never more than a step ahead, so three slots per layer suffice):
 
 * ``ctrl``  int32: count matrix ``[W][E]`` + three flag arrays ``[W]``
 * ``recv``  rows received for this rank's experts, ``capacity_rows x hidden``
@@ -32,7 +35,10 @@ _FLAG_PAD = 64  # ints; keeps the three flag arrays on separate 256-byte lines
 
 class PeerExchange:
     def __init__(self, n_experts: int, hidden: int, dtype: torch.dtype, max_rows: int, capacity_factor: float = 2.0,
-                 n_slots: int = 2, group=None):
+                 n_layers: int = 1, n_par: int = 3, group=None):
+        n_slots = n_layers * n_par
+        self.n_layers, self.n_par = n_layers, n_par
+        self.uses = [0] * n_layers
         self.group = group
         self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
         assert n_experts % self.world == 0
@@ -43,6 +49,7 @@ class PeerExchange:
         self.lib = _lib.load()
         self.max_rows = int(max_rows)
         self.calls = 0
+        self._comm = None
 
         # every rank sizes its receive buffer from the largest sender
         sizes = [None] * self.world
@@ -112,6 +119,18 @@ class PeerExchange:
             self._tables.append(t)
         # the smallest receive / return capacity among the peers bounds what this rank may write
         self.min_peer_cap = min(self.peer_cap)
+        self.min_peer_rows = min(self.peer_max_rows)
+        a = 3 * self.world + 1
+        self._seg_views = [self.meta[s, a:a + self.world * self.el + 1] for s in range(n_slots)]
+        self._meta_ptrs = [self.meta[s].data_ptr() for s in range(n_slots)]
+        self._done_ptrs = [self.done.data_ptr() + 4 * i for i in range(2 * n_slots)]
+        self._recv_views = [self.recv[s] for s in range(n_slots)]
+        self.status_ptr = self.status.data_ptr()
+        self.seg_slab = [i for _ in range(self.world) for i in range(self.el)]
+        self.seg_slab_dev = torch.tensor(self.seg_slab, dtype=torch.int32, device=self.device)
+        self._fork = torch.cuda.Event()
+        self._comm = torch.cuda.Stream(device=self.device)
+        self.comm_raw = self._comm.cuda_stream
         dist.barrier(group=group)
 
     # -- IPC ---------------------------------------------------------------------
@@ -132,20 +151,29 @@ class PeerExchange:
         return (ctypes.c_void_p * self.world)(*ptrs)
 
     # -- per call -------------------------------------------------------------------
-    def begin(self):
-        """Next (slot, sequence number, tables)."""
-        slot = self.calls % self.n_slots
+    def begin(self, layer: int = 0):
+        """Next (slot, sequence number, tables) of ``layer``."""
+        layer %= self.n_layers
+        slot = layer * self.n_par + self.uses[layer] % self.n_par
+        self.uses[layer] += 1
         self.calls += 1
         self.seq[slot] += 1
         return slot, self.seq[slot], self._tables[slot]
+
+    def fork_to_comm(self) -> int:
+        """Order the side stream (on which asynchronous pushes run next to the
+        expert FFN) after everything enqueued so far on the current stream;
+        returns its raw handle."""
+        self._fork.record()
+        self._comm.wait_event(self._fork)
+        return self.comm_raw
 
     def my_flags_ptr(self, slot: int, which: int) -> int:
         return self.ctrl.data_ptr() + (slot * self.ctrl_stride + self.flag_base + which * _FLAG_PAD) * 4
 
     def seg_offsets(self, slot: int) -> torch.Tensor:
         """Segments of the receive buffer, (source, slot) order: int32 [W*El + 1]."""
-        a = 3 * self.world + 1
-        return self.meta[slot, a:a + self.world * self.el + 1]
+        return self._seg_views[slot]
 
     def check(self):
         from .. import ops
@@ -169,21 +197,27 @@ def enabled() -> bool:
     return _enabled and not _failed
 
 
-def get_exchange(n_experts: int, hidden: int, dtype: torch.dtype, rows: int) -> Optional[PeerExchange]:
+def get_exchange(n_experts: int, hidden: int, dtype: torch.dtype, rows: int, n_layers: int = 1) -> Optional[PeerExchange]:
     """The process-wide exchange, created on first use (a collective call: every
-    rank reaches it in the same layer call)."""
+    rank reaches it in the same layer call).  ``n_layers`` is the number of
+    layers that keep exchanges in flight (the capacity given to
+    ``ep_cache_init``), 1 when nothing is cached."""
     global _exchange, _failed
     if not enabled():
         return None
     x = _exchange
     if x is not None:
-        if (x.n_experts, x.hidden, x.dtype) != (n_experts, hidden, dtype) or rows > x.max_rows:
+        if (x.n_experts, x.hidden, x.dtype) != (n_experts, hidden, dtype) or rows > x.max_rows or n_layers > x.n_layers:
             raise RuntimeError("peer-memory exchange was sized for another shape "
-                               f"(experts {x.n_experts}, hidden {x.hidden}, {x.dtype}, {x.max_rows} rows)")
+                               f"(experts {x.n_experts}, hidden {x.hidden}, {x.dtype}, {x.max_rows} rows, "
+                               f"{x.n_layers} layers); call ep_cache_init before the first forward and "
+                               "p2p.reset() to change shapes")
         return x
     try:
         factor = float(os.environ.get("DICE_EP_P2P_CAPACITY", "2.0"))
-        _exchange = PeerExchange(n_experts, hidden, dtype, max_rows=int(rows * 1.25) + 256, capacity_factor=factor)
+        n_par = int(os.environ.get("DICE_EP_P2P_SLOTS", "3"))
+        _exchange = PeerExchange(n_experts, hidden, dtype, max_rows=int(rows * 1.25) + 256, capacity_factor=factor,
+                                 n_layers=max(1, n_layers), n_par=n_par)
     except Exception as exc:  # IPC not permitted in this environment: stay on NCCL, say so once
         _failed = True
         if dist.get_rank() == 0:
@@ -196,3 +230,51 @@ def reset() -> None:
     global _exchange, _failed
     _exchange = None
     _failed = False
+
+
+# ---- stand-ins that travel through the exchange protocol of ep_fwd / diep -------------------
+
+
+class SegInfo:
+    """Plays the part of ``token_counts_global`` for one exchange: which slot and
+    sequence number it uses, how many rows this rank sent, and (on the device)
+    how the rows it receives are segmented."""
+
+    def __init__(self, xchg: PeerExchange, slot: int, seq: int, tab, rows_sent: int):
+        self.xchg, self.slot, self.seq, self.tab, self.rows_sent = xchg, slot, seq, tab, rows_sent
+
+    @property
+    def seg_dev(self) -> torch.Tensor:
+        return self.xchg.seg_offsets(self.slot)
+
+
+class PendingRows:
+    """Plays the part of ``grouped_dup_inp``: the rows are not gathered into a
+    send buffer; the dispatch kernel reads ``inp`` through ``pos`` and writes
+    each row into its expert owner's receive buffer."""
+
+    def __init__(self, inp: torch.Tensor, pos: torch.Tensor, seg_offsets: torch.Tensor, k_eff: int, info: SegInfo):
+        self.inp, self.pos, self.seg_offsets, self.k_eff, self.info = inp, pos, seg_offsets, k_eff, info
+
+    @property
+    def keepalive(self) -> torch.Tensor:
+        return self.inp
+
+
+class PeerHandle:
+    """Work handle of one push: ``wait`` makes the current stream wait (bounded,
+    on the device) until every source raised this exchange's flag;
+    ``is_completed`` tells whether this rank's own push has left its buffers."""
+
+    def __init__(self, info: SegInfo, which: int, event: Optional[torch.cuda.Event]):
+        self.info, self.which, self.event = info, which, event
+
+    def wait(self) -> None:
+        from ..ops import _stream
+
+        x = self.info.xchg
+        _lib.check(x.lib.dice_ep_wait_flags(x.my_flags_ptr(self.info.slot, 1 + self.which), x.world, self.info.seq,
+                                            self.which, x.status.data_ptr(), _stream()), "dice_ep_wait_flags")
+
+    def is_completed(self) -> bool:
+        return self.event is None or self.event.query()

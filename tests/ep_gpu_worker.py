@@ -83,12 +83,29 @@ def main():
         assert torch.equal(a_, b_), f"rank {rank}: peer-memory exchange differs from the NCCL exchange"
     p2p.enable(False)
     a = dict(ep=True, ep_async=True, ep_async_mode="all", ep_async_warm_up=0, strided_sync=0, ep_async_cool_down=0)
-    run(ParaMode(**a), dict(async_pipeline=False, selective_async_strategy="all"),
-        lambda t, l, y: close(y, want[max(0, t - 2)][l], f"displaced t={t} l={l}"))
-    run(ParaMode(**a), dict(async_pipeline=True, selective_async_strategy="all", auto_gc=True),
-        lambda t, l, y: close(y, want[max(0, t - 1) if t != 1 else 0][l], f"interweaved t={t} l={l}"))
-    run(ParaMode(**a), dict(async_pipeline=False, selective_async_strategy="all", noskip_step=2, skip_mode="low"),
-        lambda t, l, y: None)
+    sel = dict(a, ep_async_mode="interleaved")
+    async_runs = [
+        (a, dict(async_pipeline=False, selective_async_strategy="all"),
+         lambda t, l, y: close(y, want[max(0, t - 2)][l], f"displaced t={t} l={l}")),
+        (a, dict(async_pipeline=True, selective_async_strategy="all", auto_gc=True),
+         lambda t, l, y: close(y, want[max(0, t - 1) if t != 1 else 0][l], f"interweaved t={t} l={l}")),
+        (a, dict(async_pipeline=False, selective_async_strategy="all", noskip_step=2, skip_mode="low"), lambda t, l, y: None),
+        (a, dict(async_pipeline=True, selective_async_strategy="all", noskip_step=2, skip_mode="low"), lambda t, l, y: None),
+        (sel, dict(async_pipeline=False, selective_async_strategy="interleaved"), lambda t, l, y: None),
+    ]
+    nccl_async = []
+    for kw, cache_kw, check in async_runs:
+        run(ParaMode(**kw), cache_kw, check, nccl_async)
+    # the asynchronous protocols over peer memory (pushes on a side stream) must give the very same bits
+    p2p.enable(True)
+    peer_async = []
+    for kw, cache_kw, check in async_runs:
+        run(ParaMode(**kw), cache_kw, check, peer_async)
+    p2p._exchange.check()
+    assert len(nccl_async) == len(peer_async) == len(async_runs) * steps * layers
+    for i, (a_, b_) in enumerate(zip(nccl_async, peer_async)):
+        assert torch.equal(a_, b_), f"rank {rank}: asynchronous peer-memory exchange differs from NCCL at output {i}"
+    p2p.enable(False)
     mem = diep.ep_cached_tensors_size()
     assert mem > 0 and diep.ep_get_max_mem() >= 0
     dist.barrier()
