@@ -62,6 +62,10 @@ SIGNATURES = {
         c_int,
         [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_uint32, c_void_p,
          c_void_p]),
+    "dice_grouped_ffn_return": (
+        c_int,
+        [c_void_p, c_int64, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+         c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_uint32, c_void_p, c_void_p]),
     "dice_ipc_export": (c_int, [c_void_p, c_void_p, c_void_p]),
     "dice_ipc_import": (c_int, [c_void_p, ctypes.c_uint64, c_void_p]),
     "dice_ipc_close": (c_int, [c_void_p, ctypes.c_uint64]),

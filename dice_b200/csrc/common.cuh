@@ -62,6 +62,16 @@ int dice_internal_router_tc(const void* x, const void* w_gate, int64_t n_tokens,
                             cudaStream_t stream);
 
 // internal (not exported): grouped GEMM on CTA pairs (cta_group::2); arguments as dice_grouped_gemm, validated by it
+// where the output rows of a grouped GEMM go when they leave the GPU (see GemmParams::ret_*)
+struct DiceReturnSpec {
+  int world, rank, capacity_rows;
+  const int32_t* meta;
+  const void* const* bufs;   // host array [world]
+  const void* const* flags;  // host array [world]
+  uint32_t* done_counter;
+  uint32_t seq;
+};
 int dice_internal_gemm_pair(const void* a, int64_t n_rows, int k_dim, const void* w, int n_slabs, int64_t w_rows,
                             const int32_t* seg_offsets, const int32_t* seg_slab, int n_seg, int epilogue, void* out,
-                            int64_t ld_out, int n_out, uint32_t* status, cudaStream_t stream);
+                            int64_t ld_out, int n_out, uint32_t* status, cudaStream_t stream,
+                            const DiceReturnSpec* ret = nullptr);

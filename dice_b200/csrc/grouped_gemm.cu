@@ -491,3 +491,43 @@ extern "C" int dice_grouped_ffn(const void* rows_in, int64_t n_rows, int hidden,
   return dice_grouped_gemm(inter, n_rows, ffn, w2, n_slabs, hidden, seg_offsets, seg_slab, n_seg, DICE_EPI_STORE,
                            rows_out, hidden, hidden, status, stream);
 }
+
+// The expert FFN whose second GEMM writes its rows straight into the token owners' combine buffers
+// (peer memory) and raises their flags when the whole grid is done: FFN + return of the exchange in
+// one launch pair.  `out` rows are not stored locally.
+extern "C" int dice_grouped_ffn_return(const void* rows_in, int64_t n_rows, int hidden, int ffn, int act,
+                                       const void* w1, const void* w2, int n_slabs, const int32_t* seg_offsets,
+                                       const int32_t* seg_slab, int n_seg, void* inter, const int32_t* meta,
+                                       const void* const* peer_back, const void* const* peer_flags,
+                                       uint32_t* done_counter, int rank, int world, int back_capacity_rows,
+                                       uint32_t seq, uint32_t* status, void* stream) {
+  DICE_CHECK_ARG(act == DICE_ACT_SWIGLU || act == DICE_ACT_GELU_TANH, DICE_ERR_ARG);
+  DICE_CHECK_ARG(n_rows > 0 && n_seg > 0 && hidden > 0 && ffn > 0 && n_slabs > 0, DICE_ERR_ARG);
+  DICE_CHECK_ARG(rows_in && w1 && w2 && seg_offsets && inter && meta && peer_back && peer_flags && done_counter,
+                 DICE_ERR_ARG);
+  DICE_CHECK_ARG(n_seg <= kMaxSeg && world >= 1 && world <= kMaxPeerRanks && rank >= 0 && rank < world, DICE_ERR_LIMIT);
+  DICE_CHECK_ARG(hidden % 8 == 0 && ffn % 8 == 0, DICE_ERR_SHAPE);
+  DICE_CHECK_ARG(dice_aligned16(rows_in) && dice_aligned16(w1) && dice_aligned16(w2) && dice_aligned16(inter),
+                 DICE_ERR_ALIGN);
+  int rc;
+  if (act == DICE_ACT_SWIGLU)
+    rc = dice_grouped_gemm(rows_in, n_rows, hidden, w1, n_slabs, dice_w13_rows(ffn), seg_offsets, seg_slab, n_seg,
+                           DICE_EPI_SWIGLU, inter, ffn, ffn, status, stream);
+  else
+    rc = dice_grouped_gemm(rows_in, n_rows, hidden, w1, n_slabs, ffn, seg_offsets, seg_slab, n_seg, DICE_EPI_GELU_TANH,
+                           inter, ffn, ffn, status, stream);
+  if (rc != DICE_OK) return rc;
+  DiceReturnSpec ret;
+  ret.world = world;
+  ret.rank = rank;
+  ret.capacity_rows = back_capacity_rows;
+  ret.meta = meta;
+  ret.bufs = peer_back;
+  ret.flags = peer_flags;
+  ret.done_counter = done_counter;
+  ret.seq = seq;
+  // `out` is only a base for pointer arithmetic that the return mapping replaces
+  return dice_internal_gemm_pair(inter, n_rows, ffn, w2, n_slabs, hidden, seg_offsets, seg_slab, n_seg, DICE_EPI_STORE,
+                                 const_cast<void*>(peer_back[rank]), hidden, hidden, status,
+                                 static_cast<cudaStream_t>(stream), &ret);
+}

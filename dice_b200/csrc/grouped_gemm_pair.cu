@@ -100,10 +100,16 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
   volatile uint32_t* abort_flag = tmem_slot + 1;
   int* s_seg_off = reinterpret_cast<int*>(tmem_slot + 4);
   int* s_mprefix = s_seg_off + (kMaxSeg + 1);
+  int* s_ret_src = s_mprefix + (kMaxSeg + 1);   // [W + 1] first received row of each source rank
+  int* s_ret_base = s_ret_src + (kMaxPeerRanks + 1);  // [W] first row of this rank's block in each source's buffer
   const uint32_t tiles_smem = smem_u32(smem);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t cta_rank = cluster_cta_rank();  // 0 = leader
+  if (p.ret_world > 0) {
+    if (threadIdx.x <= p.ret_world) s_ret_src[threadIdx.x] = p.ret_meta[2 * p.ret_world + threadIdx.x];
+    if (threadIdx.x < p.ret_world) s_ret_base[threadIdx.x] = p.ret_meta[p.ret_world + threadIdx.x];
+  }
   const bool leader = cta_rank == 0;
   const int64_t pair_id = blockIdx.x >> 1;
   const int64_t n_pairs = gridDim.x >> 1;
@@ -232,6 +238,19 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
       const bool row_ok = r < rows_valid;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + static_cast<uint32_t>(acc * BN);
       __nv_bfloat16* out_row = p.out + static_cast<int64_t>(row0 + r) * p.ld_out;
+      bool row_ok_store = row_ok;
+      if (p.ret_world > 0) {
+        // the row goes straight into the buffer of the rank whose token it is, over NVLink
+        const int gr = row0 + r;
+        int src = 0;
+        while (src + 1 < p.ret_world && gr >= s_ret_src[src + 1]) ++src;
+        const int dst_row = s_ret_base[src] + (gr - s_ret_src[src]);
+        if (row_ok && dst_row >= p.ret_capacity_rows) {
+          row_ok_store = false;
+          if (p.status != nullptr) atomicCAS(p.status, 0u, DICE_STATUS_EXCHANGE_OVERFLOW);
+        }
+        out_row = static_cast<__nv_bfloat16*>(p.ret_bufs[src]) + static_cast<int64_t>(dst_row) * p.ld_out;
+      }
       if (p.epilogue == DICE_EPI_SWIGLU) {
         const int col0 = nb * (BN / 2);
         int n_valid = p.n_out - col0;
@@ -244,7 +263,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
           float v[32];
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] = silu_f(__uint_as_float(g[j])) * __uint_as_float(u[j]);
-          store_row_chunk(out_row + col0 + c, v, n_valid - c, row_ok);
+          store_row_chunk(out_row + col0 + c, v, n_valid - c, row_ok_store);
         }
       } else {
         const int col0 = nb * BN;
@@ -261,7 +280,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
             const float f = __uint_as_float(a[j]);
             v[j] = gelu ? gelu_tanh_f(f) : f;
           }
-          store_row_chunk(out_row + col0 + c, v, n_valid - c, row_ok);
+          store_row_chunk(out_row + col0 + c, v, n_valid - c, row_ok_store);
         }
       }
       tc_fence_before_sync();
@@ -278,6 +297,21 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
     const uint64_t t0 = global_timer_ns();
     while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
     __syncthreads();
+  }
+  if (p.ret_world > 0) {
+    // every CTA's stores are out; the last CTA of the grid tells the token owners that their rows have arrived
+    __threadfence_system();
+    __syncthreads();
+    __shared__ int s_last;
+    if (threadIdx.x == 0) s_last = atomicAdd(p.ret_done_counter, 1u) == gridDim.x - 1;
+    __syncthreads();
+    if (s_last) {
+      __threadfence_system();
+      if (threadIdx.x < p.ret_world)
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.ret_flags[threadIdx.x] + p.ret_rank), "r"(p.ret_seq)
+                     : "memory");
+      if (threadIdx.x == 0) *p.ret_done_counter = 0;
+    }
   }
   cluster_barrier();  // neither CTA leaves while the other may still signal its mbarriers or read its operands
   if (warp == 1) {
@@ -321,7 +355,8 @@ int resident_pairs() {
 // Internal entry used by dice_grouped_gemm: same arguments, already validated.
 int dice_internal_gemm_pair(const void* a, int64_t n_rows, int k_dim, const void* w, int n_slabs, int64_t w_rows,
                             const int32_t* seg_offsets, const int32_t* seg_slab, int n_seg, int epilogue, void* out,
-                            int64_t ld_out, int n_out, uint32_t* status, cudaStream_t stream) {
+                            int64_t ld_out, int n_out, uint32_t* status, cudaStream_t stream,
+                            const DiceReturnSpec* ret) {
   const int pairs = resident_pairs();
   if (pairs <= 0) return DICE_ERR_CUDA;
   CUtensorMap tm_a, tm_b;
@@ -345,6 +380,20 @@ int dice_internal_gemm_pair(const void* a, int64_t n_rows, int k_dim, const void
   p.status = status;
   p.b_box_rows = 128;
   p.n_stages = kPairStages;
+  if (ret != nullptr) {
+    if (ret->world < 1 || ret->world > kMaxPeerRanks || epilogue != DICE_EPI_STORE) return DICE_ERR_ARG;
+    p.ret_world = ret->world;
+    p.ret_rank = ret->rank;
+    p.ret_capacity_rows = ret->capacity_rows;
+    p.ret_meta = ret->meta;
+    p.ret_done_counter = ret->done_counter;
+    p.ret_seq = ret->seq;
+    for (int i = 0; i < ret->world; ++i) {
+      if (ret->bufs[i] == nullptr || ret->flags[i] == nullptr) return DICE_ERR_ARG;
+      p.ret_bufs[i] = const_cast<void*>(ret->bufs[i]);
+      p.ret_flags[i] = static_cast<uint32_t*>(const_cast<void*>(ret->flags[i]));
+    }
+  }
 
   const int64_t max_tiles = ((n_rows + PM - 1) / PM + n_seg) * p.n_nblk;
   const int use_pairs = static_cast<int>(max_tiles < pairs ? max_tiles : pairs);

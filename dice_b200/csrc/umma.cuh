@@ -25,6 +25,8 @@ constexpr uint64_t kWaitLimitNs = 1000ull * 1000ull * 1000ull;  // 1 s per wait
 constexpr int kAuxBytes = 4096;  // barriers, flags and the segment tables
 constexpr int kSmemBytes = kStages * kStageBytes + kAuxBytes + 1024;  // +1024: manual alignment
 
+constexpr int kMaxPeerRanks = 16;
+
 struct GemmParams {
   const int* seg_offsets;
   const int* seg_slab;
@@ -47,6 +49,17 @@ struct GemmParams {
   float* out_w;
   int* hist;
   __nv_bfloat16* logits_out;
+  // output rows leave the GPU (CTA-pair kernel only): row r of the receive order belongs to source rank s
+  // with ret_src_off[s] <= r < ret_src_off[s+1] and is stored in that rank's buffer at row
+  // ret_back_base[s] + r - ret_src_off[s]; ret_world == 0 means a plain local store to `out`
+  int ret_world;
+  int ret_rank;
+  int ret_capacity_rows;
+  const int* ret_meta;            // meta block of the exchange (p2p_exchange.cu)
+  void* ret_bufs[kMaxPeerRanks];  // peers' combine buffers
+  uint32_t* ret_flags[kMaxPeerRanks];
+  unsigned int* ret_done_counter;
+  uint32_t ret_seq;
 };
 
 constexpr int kEpiRouter = 100;  // internal epilogue: logits -> top-2 (see launch_router_tc)

@@ -281,5 +281,6 @@ def global_combine_async(grouped_dup_outp, token_counts_local, token_counts_glob
     prev_handles, prev_buf, prev_pos, prev_weights, _prev_send = _diep_cache_combine.get(cache_key)
     _wait(prev_handles)
     buf, handles = global_combine(grouped_dup_outp, token_counts_local, token_counts_global, async_op=True)
-    _diep_cache_combine.put(key_to_put, (handles, buf, grouped_idx_dup, flat_expert_weights, grouped_dup_outp))
+    _diep_cache_combine.put(key_to_put, (handles, buf, grouped_idx_dup, flat_expert_weights,
+                                         getattr(grouped_dup_outp, "keepalive", grouped_dup_outp)))
     return prev_buf, prev_pos, prev_weights

@@ -183,6 +183,12 @@ def global_combine(grouped_dup_outp, token_counts_local, token_counts_global, as
     ``token_counts_global`` is the :class:`p2p.SegInfo` of the dispatch being
     answered and the rows are written into the token owners' buffers."""
     if isinstance(token_counts_global, p2p.SegInfo):
+        if isinstance(grouped_dup_outp, p2p.ReturnedRows):  # the FFN kernel already returned the rows
+            info = token_counts_global
+            handle = p2p.PeerHandle(info, 1, None)
+            if not async_op:
+                handle.wait()
+            return info.xchg.back[info.slot][: info.rows_sent], [handle]
         return _peer_push(token_counts_global, async_op, rows_back=grouped_dup_outp)
     return _all_to_all_rows(grouped_dup_outp, token_counts_global, token_counts_local, async_op)
 
@@ -242,6 +248,9 @@ def proc_experts(inp, experts, token_counts_global, num_local_experts):
         seg_slab = [i for _ in range(world_size) for i in range(num_local_experts)]
         pack = getattr(experts, "_dice_pack", None)
         if pack is not None:
+            if inp.dtype == torch.bfloat16 and p2p.fused_return():
+                pack.run_offsets_return(inp, token_counts_global)
+                return p2p.ReturnedRows(token_counts_global)
             return pack.run_offsets(inp, token_counts_global.seg_dev, token_counts_global.xchg.seg_slab_dev)
         offs = token_counts_global.seg_dev.tolist()  # arbitrary expert modules need the bounds on the host
         outp = torch.empty_like(inp)

@@ -197,6 +197,22 @@ def enabled() -> bool:
     return _enabled and not _failed
 
 
+_fused_return = os.environ.get("DICE_EP_P2P_FUSED_RETURN", "0") == "1"
+
+
+def set_fused_return(flag: bool) -> None:
+    global _fused_return
+    _fused_return = flag
+
+
+def fused_return() -> bool:
+    """Whether the second expert GEMM writes its rows straight into the token
+    owners' buffers instead of a separate return kernel.  Off by default: the
+    epilogue's 64-byte row pieces use NVLink poorly and stall the accumulator
+    hand-over (measured: the GEMM loses more than the return kernel costs)."""
+    return _fused_return
+
+
 def get_exchange(n_experts: int, hidden: int, dtype: torch.dtype, rows: int, n_layers: int = 1) -> Optional[PeerExchange]:
     """The process-wide exchange, created on first use (a collective call: every
     rank reaches it in the same layer call).  ``n_layers`` is the number of
@@ -259,6 +275,17 @@ class PendingRows:
     @property
     def keepalive(self) -> torch.Tensor:
         return self.inp
+
+
+class ReturnedRows:
+    """Plays the part of the expert outputs (``grouped_dup_outp``) when the FFN
+    kernel has already written them into the token owners' buffers: the combine
+    that follows has nothing left to send."""
+
+    keepalive = None
+
+    def __init__(self, info: SegInfo):
+        self.info = info
 
 
 class PeerHandle:

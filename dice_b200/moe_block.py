@@ -245,6 +245,29 @@ class ExpertPack:
         ExpertPack.timing.append((self.tag, start, end))
         return out
 
+    def run_offsets_return(self, rows: torch.Tensor, info):
+        """FFN over the receive buffer of a peer-memory exchange with the
+        return fused into the second GEMM (bf16 only): the outputs land in the
+        token owners' buffers, nothing is stored locally."""
+        from . import _lib
+
+        act, ffn, w1, w2 = self.get(rows.dtype)
+        x = info.xchg
+        n_rows, h = rows.shape
+        inter = torch.empty((n_rows, ffn), dtype=rows.dtype, device=rows.device)
+        timing = ExpertPack.timing
+        if timing is not None:
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+        _lib.check(x.lib.dice_grouped_ffn_return(
+            rows.data_ptr(), n_rows, h, ffn, ops.ACT_CODES[act], w1.data_ptr(), w2.data_ptr(), w1.shape[0],
+            info.seg_dev.data_ptr(), x.seg_slab_dev.data_ptr(), x.world * x.el, inter.data_ptr(), x._meta_ptrs[info.slot],
+            info.tab["back"], info.tab["f_back"], x._done_ptrs[2 * info.slot + 1], x.rank, x.world, x.min_peer_rows,
+            info.seq, self.status.data_ptr(), ops._stream()), "dice_grouped_ffn_return")
+        if timing is not None:
+            end.record()
+            timing.append((self.tag, start, end))
+
     def slab_table(self, seg_slab: Sequence[int], device) -> torch.Tensor:
         """Device copy of a segment -> weight-slab table (cached: it only depends on world size and slots)."""
         key = (tuple(seg_slab), str(device))

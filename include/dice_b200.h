@@ -252,6 +252,18 @@ DICE_API int dice_ep_return_rows(const void* rows, const int32_t* meta, const vo
                         const void* const* peer_flags, uint32_t* done_counter, int hidden, int dtype,
                         int rank, int world, int back_capacity_rows, int max_rows, uint32_t seq,
                         uint32_t* status, void* stream);
+/* The expert FFN fused with the return: same as dice_grouped_ffn over the
+ * receive buffer, but the second GEMM's epilogue stores every output row
+ * straight into the combine buffer of the rank that owns the token (NVLink
+ * peer stores) and the last CTA raises the peers' flags: proc_experts
+ * (ep_fwd.py:199-211) + global_combine (:295-342) in one launch pair.  `meta`,
+ * `peer_back`, `peer_flags`, `done_counter`, `seq` as for dice_ep_return_rows. */
+DICE_API int dice_grouped_ffn_return(const void* rows_in, int64_t n_rows, int hidden, int ffn, int act,
+                            const void* w1, const void* w2, int n_slabs, const int32_t* seg_offsets,
+                            const int32_t* seg_slab, int n_seg, void* inter, const int32_t* meta,
+                            const void* const* peer_back, const void* const* peer_flags,
+                            uint32_t* done_counter, int rank, int world, int back_capacity_rows,
+                            uint32_t seq, uint32_t* status, void* stream);
 /* CUDA IPC plumbing for the above (set-up time): export the allocation that
  * holds `ptr` (64-byte handle + offset of ptr inside it); import maps a peer's
  * allocation into this process and enables peer access. */

@@ -78,8 +78,13 @@ def main():
     run(ParaMode(ep=True), {}, lambda t, l, y: close(y, want[t][l], f"peer sync t={t} l={l}"), peer_sync)
     run(ParaMode(ep=True), dict(noskip_step=2, skip_mode="low"), lambda t, l, y: None, peer_skip)
     assert p2p.enabled() and p2p._exchange is not None, "peer-memory exchange was not used"
+    # once more with the return fused into the second expert GEMM
+    p2p.set_fused_return(True)
+    fused_sync = []
+    run(ParaMode(ep=True), {}, lambda t, l, y: close(y, want[t][l], f"fused return t={t} l={l}"), fused_sync)
+    p2p.set_fused_return(False)
     p2p._exchange.check()
-    for a_, b_ in zip(nccl_sync + nccl_skip, peer_sync + peer_skip):
+    for a_, b_ in zip(nccl_sync + nccl_skip + nccl_sync, peer_sync + peer_skip + fused_sync):
         assert torch.equal(a_, b_), f"rank {rank}: peer-memory exchange differs from the NCCL exchange"
     p2p.enable(False)
     a = dict(ep=True, ep_async=True, ep_async_mode="all", ep_async_warm_up=0, strided_sync=0, ep_async_cool_down=0)

@@ -371,3 +371,49 @@ def test_exchange_world_of_one(cuda_device):
     torch.cuda.synchronize()
     with pytest.raises(RuntimeError, match="more rows"):
         ops.check_status(status)
+
+
+def test_ffn_with_fused_return_world_of_one(cuda_device):
+    """dice_grouped_ffn_return on one GPU: the rows the second GEMM sends "home"
+    land where the separate return kernel would put them and equal the plain
+    FFN's output bit for bit; the flag is raised by the last CTA."""
+    import ctypes
+
+    from dice_b200 import _lib
+
+    ops = _ops()
+    lib = _lib.load()
+    n, h, f, e = 500, 128, 512, 4
+    g = torch.Generator().manual_seed(12)
+    x = torch.randn(n, h, generator=g).bfloat16().to(cuda_device)
+    flat = torch.randint(0, e, (2 * n,), generator=g).to(cuda_device)
+    mk = lambda *shape: (torch.randn(*shape, generator=g) / math.sqrt(shape[-1])).bfloat16().to(cuda_device)
+    w1 = torch.stack([ops.pack_w13(mk(f, h), mk(f, h)) for _ in range(e)])
+    w2 = torch.stack([mk(h, f) for _ in range(e)])
+    pos, seg, _ = ops.permute_plan(flat, e)
+    rows = ops.permute_rows(x, pos, 2)
+    status = torch.zeros(1, dtype=torch.int32, device=cuda_device)
+    want = ops.grouped_ffn(rows, w1, w2, seg, "swiglu", f, status)
+    ctrl = torch.zeros(e + 3 * 64, dtype=torch.int32, device=cuda_device)
+    back = torch.zeros((2 * n + 3, h), dtype=torch.bfloat16, device=cuda_device)
+    meta = torch.zeros(lib.dice_ep_meta_ints(1, e), dtype=torch.int32, device=cuda_device)
+    done = torch.zeros(2, dtype=torch.int32, device=cuda_device)
+    inter = torch.empty((2 * n, f), dtype=torch.bfloat16, device=cuda_device)
+    slab = torch.arange(e, dtype=torch.int32, device=cuda_device)
+    st = torch.cuda.current_stream().cuda_stream
+    tab = lambda p: (ctypes.c_void_p * 1)(p)
+    f_cnt, f_back = ctrl.data_ptr() + e * 4, ctrl.data_ptr() + (e + 128) * 4
+    for seq in (1, 2):
+        back.zero_()
+        assert lib.dice_ep_exchange_counts(seg.data_ptr(), tab(ctrl.data_ptr()), tab(f_cnt), meta.data_ptr(), 0, 1, e,
+                                           2 * n, seq, status.data_ptr(), st) == 0
+        seg_dev = meta[4:4 + e + 1]
+        assert lib.dice_grouped_ffn_return(rows.data_ptr(), 2 * n, h, f, 0, w1.data_ptr(), w2.data_ptr(), e,
+                                           seg_dev.data_ptr(), slab.data_ptr(), e, inter.data_ptr(), meta.data_ptr(),
+                                           tab(back.data_ptr()), tab(f_back), done[1:].data_ptr(), 0, 1, 2 * n, seq,
+                                           status.data_ptr(), st) == 0
+        assert lib.dice_ep_wait_flags(f_back, 1, seq, 1, status.data_ptr(), st) == 0
+        torch.cuda.synchronize()
+        ops.check_status(status)
+        assert torch.equal(back[: 2 * n], want)
+        assert bool((back[2 * n:] == 0).all()) and int(done.sum()) == 0
