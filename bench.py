@@ -299,7 +299,10 @@ def run_ours(args):
         step_device()
     # FFN launch durations, measured on the launching stream inside the timed region
     ExpertPack.timing = []
-    total_ms, clocks = timed(step_device, args.steps, ClockSampler(local_rank))
+    # time one FFN call in five (5 does not divide the calls per step, so every layer gets its turn); the clocks of
+    # this rank's GPU are sampled by rank 0 only: eight polling nvidia-smi processes slow every rank's launches down
+    ExpertPack.timing_every = 5
+    total_ms, clocks = timed(step_device, args.steps, ClockSampler(local_rank) if rank == 0 else None)
     ffn_events = ExpertPack.timing
     ExpertPack.timing = None
     torch.cuda.synchronize()
@@ -323,6 +326,7 @@ def run_ours(args):
     pk, pk_src = peaks()
     peak_tf = pk.get("bf16_tflops_sustained", FALLBACK_PEAKS["bf16_tflops_sustained"])
     # one FFN call = 2 grouped-GEMM launches; rows per rank = 2 * tokens under uniform routing
+    # (conditional communication sends one row per token on skip steps: the FLOP count below would be wrong)
     gemm_launches = 2 * len(routed)
     gemm_ms = sum(routed) / max(gemm_launches, 1)
     flops_per_launch = ffn_flops(tokens, args.variant) / 2
@@ -330,8 +334,11 @@ def run_ours(args):
     roofline = {"kernel": "grouped_gemm_pair_kernel (tcgen05 cta_group::2, fc1+fc2 of the routed experts)", "bound": "tensor",
                 "achieved": round(achieved, 1), "peak": peak_tf, "unit": "TFLOP/s", "frac": round(achieved / peak_tf, 4),
                 "peak_source": f"bf16_tflops_sustained of {pk_src}", "avg_launch_ms": round(gemm_ms, 4),
-                "launches_timed": gemm_launches, "flops_per_launch": flops_per_launch, "traffic": GEMM_TRAFFIC_BYTES if (world == 1 and args.variant == "gelu_tanh") else None}
+                "launches_timed": gemm_launches, "launches_in_region": 2 * args.layers * args.steps,
+                "flops_per_launch": flops_per_launch, "traffic": GEMM_TRAFFIC_BYTES if (world == 1 and args.variant == "gelu_tanh") else None}
 
+    if args.skip:
+        roofline.update({"achieved": None, "frac": None, "note": "rows per launch vary with conditional communication"})
     line = {
         "metric": "moe_block_tokens_per_s", "value": round(value, 1), "unit": "tokens/s", "n_gpus": world,
         "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(ms_per_step, 4),

@@ -190,6 +190,15 @@ class ExpertPack:
     # when set to a list, every FFN call appends (tag, start_event, end_event) recorded on the
     # launching stream (used by the benchmark to time the grouped-GEMM launches in place)
     timing = None
+    timing_every = 1   # record only every n-th call (keeps the host cost of the instrumentation negligible)
+    _timing_calls = 0
+
+    @classmethod
+    def _want_timing(cls) -> bool:
+        if cls.timing is None:
+            return False
+        cls._timing_calls += 1
+        return cls._timing_calls % cls.timing_every == 0
 
     def __init__(self, experts: Sequence[nn.Module], tag: str = "routed"):
         self._experts = experts
@@ -236,7 +245,7 @@ class ExpertPack:
 
     def run_offsets(self, rows: torch.Tensor, seg_offsets: torch.Tensor, seg_slab: Optional[torch.Tensor] = None):
         act, ffn, w1, w2 = self.get(rows.dtype)
-        if ExpertPack.timing is None:
+        if not ExpertPack._want_timing():
             return ops.grouped_ffn(rows, w1, w2, seg_offsets, act, ffn, status=self.status, seg_slab=seg_slab)
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         start.record()
@@ -255,7 +264,7 @@ class ExpertPack:
         x = info.xchg
         n_rows, h = rows.shape
         inter = torch.empty((n_rows, ffn), dtype=rows.dtype, device=rows.device)
-        timing = ExpertPack.timing
+        timing = ExpertPack.timing if ExpertPack._want_timing() else None
         if timing is not None:
             start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             start.record()
