@@ -48,7 +48,7 @@ TOKENS_PER_IMAGE = 256
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 # dram__bytes_read.sum + dram__bytes_write.sum of one grouped-GEMM launch of this workload,
 # scaled from the ncu capture summarised under profiles/ (None until a capture exists)
-GEMM_TRAFFIC_BYTES = 440.5e6  # mean of fc1 (409.7 MB) and fc2 (471.3 MB), profiles/grouped_gemm_dit_xl2_moe_block.md
+GEMM_TRAFFIC_BYTES = 440.5e6  # mean of fc1 (409.7 MB) and fc2 (471.3 MB) of the ncu capture summarised under profiles/
 
 
 def parse_args():
@@ -69,6 +69,9 @@ def parse_args():
     ap.add_argument("--nccl-exchange", action="store_true",
                     help="synchronous expert parallelism through NCCL all-to-all instead of the NVLink peer-memory exchange")
     ap.add_argument("--auto-gc", action="store_true", help="drop send buffers of completed exchanges (ep_cache_init auto_gc)")
+    ap.add_argument("--phases", action="store_true",
+                    help="after the timed runs, time the phases of the block (router, count exchange, dispatch, expert "
+                         "FFN, combine ...) with CUDA events on a few more steps and add them to the JSON line")
     ap.add_argument("--skip", action="store_true", help="conditional communication: noskip step 2, 'low' strategy")
     return ap.parse_args()
 
@@ -175,6 +178,40 @@ def build_blocks(layers, variant, para_mode, device, seed=0):
         blk.gate.norm_topk_prob = variant == "gelu_tanh"
         blocks.append(blk)
     return blocks
+
+
+def phase_times(step_fn, layers, steps=3):
+    """GPU time of each named phase of the block (the section names the reference's profiler uses,
+    ep_fwd.py:88-172, models.py:305-375), per layer, on this rank: CUDA events around every phase."""
+    import collections
+    import contextlib
+
+    from dice_b200.expertpara import diep
+
+    events = collections.defaultdict(list)
+
+    class Phases:
+        @staticmethod
+        @contextlib.contextmanager
+        def scope(name, stream=None, cpu=False):
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            yield
+            e.record()
+            events[name].append((s, e))
+
+    diep._profiler()  # make sure the hook variable exists
+    saved, diep._prof_cls = diep._prof_cls, Phases
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for _ in range(steps):
+        step_fn()
+    t1.record()
+    torch.cuda.synchronize()
+    diep._prof_cls = saved
+    out = {k: round(sum(a.elapsed_time(b) for a, b in v) / steps / layers * 1e3, 1) for k, v in events.items()}
+    out["whole_layer"] = round(t0.elapsed_time(t1) / steps / layers * 1e3, 1)
+    return out
 
 
 def kernels_per_block(variant, ep):
@@ -319,6 +356,8 @@ def run_ours(args):
         step_e2e()
     e2e_ms, _ = timed(step_e2e, args.steps)
 
+    phases = phase_times(step_device, args.layers) if args.phases else None
+
     ms_per_step = total_ms / args.steps
     value = world * tokens * args.layers / (ms_per_step * 1e-3)
     e2e_value = world * tokens * args.layers / (e2e_ms / args.steps * 1e-3)
@@ -353,6 +392,8 @@ def run_ours(args):
         "clocks": clocks, "roofline": roofline,
         "tokens_per_s_per_gpu": round(value / world, 1),
     }
+    if phases is not None:
+        line["phases_us_per_layer"] = phases
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline(blocks, xs, args.variant, budget_s=12.0)
     if rank == 0:

@@ -20,7 +20,9 @@ import os
 import sys
 import types
 
-DEFAULT_REFERENCE_ROOT = os.environ.get("DICE_REFERENCE_ROOT", "/root/reference")
+# the reference checkout: $DICE_REFERENCE_ROOT, else a directory "reference" next to this repository
+_REPO = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+DEFAULT_REFERENCE_ROOT = os.environ.get("DICE_REFERENCE_ROOT", os.path.join(os.path.dirname(_REPO), "reference"))
 
 
 def reference_available(root: str = DEFAULT_REFERENCE_ROOT) -> bool:

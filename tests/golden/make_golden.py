@@ -277,11 +277,14 @@ def _gen_ep(mode_name, ref_root, out_dir):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference-root", default="/root/reference")
+    ap.add_argument("--reference-root", default=None, help="DICE checkout (default: $DICE_REFERENCE_ROOT or ../reference)")
     ap.add_argument("--only", default=None, help="comma-separated subset: block_small,block_c0,ep")
     args = ap.parse_args()
     from oracle.reference_shim import load_reference
 
+    from oracle.reference_shim import DEFAULT_REFERENCE_ROOT
+
+    args.reference_root = args.reference_root or DEFAULT_REFERENCE_ROOT
     ref = load_reference(args.reference_root)
     only = set(args.only.split(",")) if args.only else {"block_small", "block_c0", "ep"}
     if "block_small" in only:
