@@ -69,6 +69,8 @@ def parse_args():
     ap.add_argument("--nccl-exchange", action="store_true",
                     help="synchronous expert parallelism through NCCL all-to-all instead of the NVLink peer-memory exchange")
     ap.add_argument("--auto-gc", action="store_true", help="drop send buffers of completed exchanges (ep_cache_init auto_gc)")
+    ap.add_argument("--no-full-model", action="store_true",
+                    help="skip the latency of one sampling step of the full DiT-MoE model (attention etc. in PyTorch)")
     ap.add_argument("--phases", action="store_true",
                     help="after the timed runs, time the phases of the block (router, count exchange, dispatch, expert "
                          "FFN, combine ...) with CUDA events on a few more steps and add them to the JSON line")
@@ -178,6 +180,41 @@ def build_blocks(layers, variant, para_mode, device, seed=0):
         blk.gate.norm_topk_prob = variant == "gelu_tanh"
         blocks.append(blk)
     return blocks
+
+
+def full_model_step(blocks, tokens, device, begin_step, barrier, ep, steps=10):
+    """Latency of one sampling step (CFG-doubled forward + Euler update) of the full DiT-MoE model built around the
+    same MoE blocks; the backbone is a measurement harness in plain PyTorch (bench_dit_model.py)."""
+    import torch.distributed as dist
+
+    from bench_dit_model import DiTBackbone
+
+    latent = int(round((TOKENS_PER_IMAGE) ** 0.5)) * 2
+    images = tokens // TOKENS_PER_IMAGE // 2
+    model = DiTBackbone(blocks, HIDDEN, latent=latent).to(device=device, dtype=torch.bfloat16).eval()
+    g = torch.Generator(device=device).manual_seed(5)
+    z = torch.randn(images, 4, latent, latent, generator=g, device=device).bfloat16()
+    cond = torch.randint(0, 1000, (images,), generator=g, device=device)
+    null = torch.full((images,), 1000, device=device)
+
+    def step(i):
+        begin_step()
+        return model.sampling_step(z, cond, null, t=1.0 - i / 50.0, dt=1.0 / 50.0)
+
+    for i in range(3):
+        step(i)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(steps):
+        step(i)
+    e1.record()
+    barrier()
+    ms = torch.tensor([e0.elapsed_time(e1) / steps], device=device)
+    if ep:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    return {"ms_per_step": round(float(ms.item()), 3), "images_per_gpu": images, "latent": latent,
+            "note": "MoE blocks: dice_b200 kernels; backbone (attention, adaLN, embeddings): PyTorch bf16 harness"}
 
 
 def phase_times(step_fn, layers, steps=3):
@@ -357,6 +394,7 @@ def run_ours(args):
     e2e_ms, _ = timed(step_e2e, args.steps)
 
     phases = phase_times(step_device, args.layers) if args.phases else None
+    dit = None if args.no_full_model else full_model_step(blocks, tokens, device, begin_step, barrier, ep, steps=10)
 
     ms_per_step = total_ms / args.steps
     value = world * tokens * args.layers / (ms_per_step * 1e-3)
@@ -394,6 +432,8 @@ def run_ours(args):
     }
     if phases is not None:
         line["phases_us_per_layer"] = phases
+    if dit is not None:
+        line["dit_sampling_step"] = dit
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline(blocks, xs, args.variant, budget_s=12.0)
     if rank == 0:
