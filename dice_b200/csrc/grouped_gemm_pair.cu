@@ -33,7 +33,9 @@ constexpr int PM = 256;                    // rows per tile pair
 constexpr int kPairStages = 6;
 constexpr int kPairTileBBytes = 128 * BK * 2;
 constexpr int kPairStageBytes = kTileABytes + kPairTileBBytes;  // 32 KB
-constexpr int kPairSmemBytes = kPairStages * kPairStageBytes + kAuxBytes + 1024;
+constexpr int kStoreStageBytes = 2048;  // per epilogue warp: 32 rows x 64 bytes, transposed between the tensor-memory
+                                        // layout (one row per lane) and full 64-byte row pieces per store
+constexpr int kPairSmemBytes = kPairStages * kPairStageBytes + kAuxBytes + kEpilogueWarps * kStoreStageBytes + 1024;
 
 __device__ __forceinline__ uint32_t cluster_cta_rank() {
   uint32_t r;
@@ -237,20 +239,49 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
       const int r = quad * 32 + lane;
       const bool row_ok = r < rows_valid;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + static_cast<uint32_t>(acc * BN);
-      __nv_bfloat16* out_row = p.out + static_cast<int64_t>(row0 + r) * p.ld_out;
-      bool row_ok_store = row_ok;
-      if (p.ret_world > 0) {
-        // the row goes straight into the buffer of the rank whose token it is, over NVLink
-        const int gr = row0 + r;
-        int src = 0;
-        while (src + 1 < p.ret_world && gr >= s_ret_src[src + 1]) ++src;
-        const int dst_row = s_ret_base[src] + (gr - s_ret_src[src]);
-        if (row_ok && dst_row >= p.ret_capacity_rows) {
-          row_ok_store = false;
-          if (p.status != nullptr) atomicCAS(p.status, 0u, DICE_STATUS_EXCHANGE_OVERFLOW);
+      // Stores go through a small per-warp transpose in shared memory: a lane holds 32 columns of ONE row,
+      // but a store instruction should cover whole 64-byte row pieces.  After the transpose lane l writes
+      // piece (l & 3) of rows (l >> 2) + 8 i, i < 4, whose destinations are resolved once per tile.
+      (void)row_ok;
+      __nv_bfloat16* dst_rows[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int rr = quad * 32 + i * 8 + (lane >> 2);
+        const int gr = row0 + rr;
+        dst_rows[i] = nullptr;
+        if (rr < rows_valid) {
+          if (p.ret_world > 0) {
+            // the row goes straight into the buffer of the rank whose token it is, over NVLink
+            int src = 0;
+            while (src + 1 < p.ret_world && gr >= s_ret_src[src + 1]) ++src;
+            const int dst_row = s_ret_base[src] + (gr - s_ret_src[src]);
+            if (dst_row < p.ret_capacity_rows)
+              dst_rows[i] = static_cast<__nv_bfloat16*>(p.ret_bufs[src]) + static_cast<int64_t>(dst_row) * p.ld_out;
+            else if (p.status != nullptr)
+              atomicCAS(p.status, 0u, DICE_STATUS_EXCHANGE_OVERFLOW);
+          } else {
+            dst_rows[i] = p.out + static_cast<int64_t>(gr) * p.ld_out;
+          }
         }
-        out_row = static_cast<__nv_bfloat16*>(p.ret_bufs[src]) + static_cast<int64_t>(dst_row) * p.ld_out;
       }
+      uint4* stage = reinterpret_cast<uint4*>(aux + kAuxBytes + (warp - 2) * kStoreStageBytes);
+      auto staged_store = [&](const float (&v)[32], int col, int n_left) {
+        const int swz = (lane >> 1) & 3;
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          stage[lane * 4 + (j ^ swz)] =
+              make_uint4(pack_bf16x2(v[8 * j + 0], v[8 * j + 1]), pack_bf16x2(v[8 * j + 2], v[8 * j + 3]),
+                         pack_bf16x2(v[8 * j + 4], v[8 * j + 5]), pack_bf16x2(v[8 * j + 6], v[8 * j + 7]));
+        __syncwarp();
+        const int piece = lane & 3;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int rr = i * 8 + (lane >> 2);
+          const uint4 val = stage[rr * 4 + (piece ^ ((rr >> 1) & 3))];
+          if (dst_rows[i] != nullptr && piece * 8 < n_left) *reinterpret_cast<uint4*>(dst_rows[i] + col + piece * 8) = val;
+        }
+        __syncwarp();
+      };
       if (p.epilogue == DICE_EPI_SWIGLU) {
         const int col0 = nb * (BN / 2);
         int n_valid = p.n_out - col0;
@@ -263,7 +294,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
           float v[32];
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] = silu_f(__uint_as_float(g[j])) * __uint_as_float(u[j]);
-          store_row_chunk(out_row + col0 + c, v, n_valid - c, row_ok_store);
+          staged_store(v, col0 + c, n_valid - c);
         }
       } else {
         const int col0 = nb * BN;
@@ -280,7 +311,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
             const float f = __uint_as_float(a[j]);
             v[j] = gelu ? gelu_tanh_f(f) : f;
           }
-          store_row_chunk(out_row + col0 + c, v, n_valid - c, row_ok_store);
+          staged_store(v, col0 + c, n_valid - c);
         }
       }
       tc_fence_before_sync();
