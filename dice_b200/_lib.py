@@ -18,7 +18,8 @@ SIGNATURES = {
     "dice_status_message": (c_char_p, [c_uint32]),
     "dice_router_top2": (
         c_int,
-        [c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
+        [c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+         c_void_p],
     ),
     "dice_top2_from_logits": (c_int, [c_void_p, c_int64, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
     "dice_permute_scratch_bytes": (c_size_t, [c_int64, c_int]),

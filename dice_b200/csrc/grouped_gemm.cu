@@ -436,7 +436,7 @@ extern "C" int dice_grouped_gemm(const void* a, int64_t n_rows, int k_dim, const
 // tokens, then every epilogue thread selects the top-2 of its own token.
 int dice_internal_router_tc(const void* x, const void* w_gate, int64_t n_tokens, int hidden, int n_experts, int renorm,
                             int64_t* out_idx, float* out_w, int32_t* out_hist, void* out_logits,
-                            cudaStream_t stream) {
+                            uint32_t* status, cudaStream_t stream) {
   const int sms = sm_count();
   if (sms <= 0) return DICE_ERR_CUDA;
   if (n_tokens >= 0x7fffff00LL) return DICE_ERR_LIMIT;
@@ -459,7 +459,7 @@ int dice_internal_router_tc(const void* x, const void* w_gate, int64_t n_tokens,
   p.epilogue = kEpiRouter;
   p.out = nullptr;
   p.ld_out = 0;
-  p.status = nullptr;
+  p.status = status;
   p.b_box_rows = b_box_rows;
   p.n_stages = ring_depth(b_box_rows);
   p.n_experts = n_experts;

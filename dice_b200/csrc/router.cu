@@ -297,7 +297,7 @@ int dispatch_select(const void* logits, int64_t n, int e, int renorm, int64_t* i
 
 extern "C" int dice_router_top2(const void* x, const void* w_gate, int64_t n_tokens, int hidden, int n_experts,
                                 int dtype, int renorm, int64_t* out_idx, float* out_w, int32_t* out_hist,
-                                void* out_logits, void* stream) {
+                                void* out_logits, uint32_t* status, void* stream) {
   DICE_CHECK_ARG(n_tokens >= 0 && hidden > 0, DICE_ERR_ARG);
   DICE_CHECK_ARG(n_experts >= 2 && n_experts <= 64, DICE_ERR_SHAPE);
   DICE_CHECK_ARG(dtype == DICE_BF16 || dtype == DICE_F32, DICE_ERR_DTYPE);
@@ -314,7 +314,7 @@ extern "C" int dice_router_top2(const void* x, const void* w_gate, int64_t n_tok
   // fp32 must not be rounded to tf32, so it takes the CUDA-core kernel of this file
   if (dtype == DICE_BF16)
     return dice_internal_router_tc(x, w_gate, n_tokens, hidden, n_experts, renorm, out_idx, out_w, out_hist,
-                                   out_logits, s);
+                                   out_logits, status, s);
   return dispatch_router<float>(x, w_gate, n_tokens, hidden, n_experts, renorm, out_idx, out_w, out_hist, out_logits,
                                 s);
 }

@@ -336,6 +336,7 @@ class SparseMoeBlock(nn.Module):
         self._shared_pack = ExpertPack([self.shared_experts], tag="shared") if self.n_shared_experts is not None else None
         self._gate_cast = {}
         self._seg_cache = {}
+        self._status = None
 
     # -- helpers ----------------------------------------------------------------
     def _gate_weight(self, dtype):
@@ -360,8 +361,15 @@ class SparseMoeBlock(nn.Module):
             self._seg_cache[key] = seg
         return seg
 
+    def _router_status(self, device):
+        if self._status is None or self._status.device != device:
+            self._status = torch.zeros(1, dtype=torch.int32, device=device)
+        return self._status
+
     def check_status(self):
         """Raise if a kernel of this block reported an expired wait (synchronises)."""
+        if self._status is not None:
+            ops.check_status(self._status, "router")
         self.experts._dice_pack.check()
         if self._shared_pack is not None:
             self._shared_pack.check()
@@ -384,7 +392,8 @@ class SparseMoeBlock(nn.Module):
         n_tokens = x.shape[0]
         assert self.num_experts_per_tok == 2, "the fused router selects exactly two experts per token"
         with _scope("moe.gate"):
-            topk_idx, topk_weight, hist, _ = ops.router_top2(x, self._gate_weight(cd), renorm=self.gate.norm_topk_prob)
+            topk_idx, topk_weight, hist, _ = ops.router_top2(x, self._gate_weight(cd), renorm=self.gate.norm_topk_prob,
+                                                             status=self._router_status(x.device))
         shared_out = None
         if self._shared_pack is not None:
             with _scope("moe.mlp_shared"):

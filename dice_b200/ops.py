@@ -61,7 +61,8 @@ def check_status(status: torch.Tensor, what: str = "dice_b200 kernel") -> None:
 
 
 def router_top2(
-    x2d: torch.Tensor, w_gate: torch.Tensor, renorm: bool = False, want_logits: bool = False
+    x2d: torch.Tensor, w_gate: torch.Tensor, renorm: bool = False, want_logits: bool = False,
+    status: Optional[torch.Tensor] = None,
 ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, Optional[torch.Tensor]]:
     """Fused gate: returns ``(topk_idx int64 [N,2], topk_weight fp32 [N,2],
     hist int32 [E], logits or None)``; replaces ``MoEGate.forward``
@@ -81,7 +82,7 @@ def router_top2(
     _lib.check(
         lib.dice_router_top2(
             _ptr(x2d), _ptr(w_gate), n, h, e, _dtype_code(x2d), int(renorm), _ptr(idx), _ptr(w), _ptr(hist),
-            _ptr(logits), _stream(),
+            _ptr(logits), _ptr(status), _stream(),
         ),
         "dice_router_top2",
     )

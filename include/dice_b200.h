@@ -83,11 +83,15 @@ DICE_API const char* dice_status_message(uint32_t status);
  *   out_logits  optional [n_tokens, n_experts] dtype (NULL to skip)
  * Logits are accumulated in fp32 and rounded to dtype before the softmax,
  * which is evaluated in fp32.  hidden*sizeof(dtype) must be a multiple of 16,
- * n_experts in [2, 64].
+ * n_experts in [2, 64].  bf16 runs as a 128 x E tcgen05 tile per 128 tokens
+ * with the selection in the epilogue, fp32 on the CUDA cores.  `status`
+ * (device uint32, may be NULL) receives a code if a bounded wait expires;
+ * tokens of a tile that gave up get expert -1 and weight 0 (fp32 kernel) or
+ * are left unwritten (bf16 kernel).
  */
 DICE_API int dice_router_top2(const void* x, const void* w_gate, int64_t n_tokens, int hidden, int n_experts,
                      int dtype, int renorm, int64_t* out_idx, float* out_w, int32_t* out_hist,
-                     void* out_logits, void* stream);
+                     void* out_logits, uint32_t* status, void* stream);
 
 /* The selection stage alone, on logits supplied by the caller (same outputs
  * as above).  Lets the selection be checked bit-exactly against
