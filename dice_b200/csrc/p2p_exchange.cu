@@ -175,8 +175,7 @@ ep_dispatch_kernel(const uint4* __restrict__ x, const int* __restrict__ pos, con
   if (threadIdx.x < world) s_base[threadIdx.x] = meta[threadIdx.x];
   __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int64_t t = static_cast<int64_t>(blockIdx.x) * 8 + warp;
-  if (t < n_tokens) {
+  for (int64_t t = static_cast<int64_t>(blockIdx.x) * 8 + warp; t < n_tokens; t += static_cast<int64_t>(gridDim.x) * 8) {
     uint4* dst[K];
 #pragma unroll
     for (int s = 0; s < K; ++s) {
@@ -271,8 +270,8 @@ extern "C" int dice_ep_exchange_counts(const int32_t* seg_offsets, const void* c
 extern "C" int dice_ep_dispatch_rows(const void* x, const int32_t* pos, const int32_t* seg_offsets,
                                      const int32_t* meta, const void* const* peer_recv, const void* const* peer_flags,
                                      uint32_t* done_counter, int64_t n_tokens, int k, int hidden, int dtype, int rank,
-                                     int world, int n_experts, int capacity_rows, uint32_t seq, uint32_t* status,
-                                     void* stream) {
+                                     int world, int n_experts, int capacity_rows, uint32_t seq, int max_ctas,
+                                     uint32_t* status, void* stream) {
   DICE_CHECK_ARG(n_tokens >= 0 && hidden > 0 && done_counter && meta && seg_offsets, DICE_ERR_ARG);
   DICE_CHECK_ARG(k == 1 || k == 2, DICE_ERR_SHAPE);
   DICE_CHECK_ARG(world >= 1 && world <= kMaxRanks && n_experts % world == 0, DICE_ERR_SHAPE);
@@ -288,6 +287,7 @@ extern "C" int dice_ep_dispatch_rows(const void* x, const int32_t* pos, const in
   const int row_vec = static_cast<int>(hidden * es / 16);
   int64_t blocks = (n_tokens + 7) / 8;
   if (blocks < 1) blocks = 1;  // the flags are raised even when this rank has nothing to send
+  if (max_ctas > 0 && blocks > max_ctas) blocks = max_ctas;  // a small grid leaves the SMs to a concurrent GEMM
   DICE_CHECK_ARG(blocks <= 0x7fffffffLL, DICE_ERR_LIMIT);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int el = n_experts / world;
@@ -313,7 +313,7 @@ extern "C" int dice_ep_wait_flags(const uint32_t* my_flags, int world, uint32_t 
 extern "C" int dice_ep_return_rows(const void* rows, const int32_t* meta, const void* const* peer_back,
                                    const void* const* peer_flags, uint32_t* done_counter, int hidden, int dtype,
                                    int rank, int world, int back_capacity_rows, int max_rows, uint32_t seq,
-                                   uint32_t* status, void* stream) {
+                                   int max_ctas, uint32_t* status, void* stream) {
   DICE_CHECK_ARG(rows && meta && done_counter && hidden > 0 && max_rows >= 0, DICE_ERR_ARG);
   DICE_CHECK_ARG(world >= 1 && world <= kMaxRanks, DICE_ERR_SHAPE);
   const size_t es = dice_dtype_size(dtype);
@@ -328,6 +328,7 @@ extern "C" int dice_ep_return_rows(const void* rows, const int32_t* meta, const 
   int64_t blocks = (static_cast<int64_t>(max_rows) + 7) / 8;
   if (blocks < 1) blocks = 1;
   if (blocks > 148 * 16) blocks = 148 * 16;  // grid-stride over the rows actually received
+  if (max_ctas > 0 && blocks > max_ctas) blocks = max_ctas;
   ep_return_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint4*>(rows), meta, b, f, done_counter, row_vec, rank, world, back_capacity_rows, seq, status);
   return cudaGetLastError() == cudaSuccess ? DICE_OK : DICE_ERR_CUDA;

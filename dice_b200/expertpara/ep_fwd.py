@@ -201,6 +201,7 @@ def _peer_push(info, async_op, dispatch=None, rows_back=None):
 
     x = info.xchg
     lib, tab, slot = x.lib, info.tab, info.slot
+    side_ctas = p2p.side_push_ctas() if async_op else 0
     if async_op:
         stream = x.fork_to_comm()  # the push runs on the side stream, after what the current stream has produced
         # the caching allocator must not hand these to someone else before the side stream has read them
@@ -213,12 +214,13 @@ def _peer_push(info, async_op, dispatch=None, rows_back=None):
         _lib.check(lib.dice_ep_dispatch_rows(
             inp.data_ptr(), dispatch.pos.data_ptr(), dispatch.seg_offsets.data_ptr(), x._meta_ptrs[slot], tab["recv"],
             tab["f_disp"], x._done_ptrs[2 * slot], inp.shape[0], dispatch.k_eff, inp.shape[1], _dtype_code(inp), x.rank,
-            x.world, x.n_experts, x.min_peer_cap, info.seq, x.status_ptr, stream), "dice_ep_dispatch_rows")
+            x.world, x.n_experts, x.min_peer_cap, info.seq, side_ctas, x.status_ptr, stream), "dice_ep_dispatch_rows")
         out, which = x._recv_views[slot], 0
     else:
         _lib.check(lib.dice_ep_return_rows(
             rows_back.data_ptr(), x._meta_ptrs[slot], tab["back"], tab["f_back"], x._done_ptrs[2 * slot + 1], x.hidden,
-            _dtype_code(rows_back), x.rank, x.world, x.min_peer_rows, x.capacity_rows, info.seq, x.status_ptr, stream),
+            _dtype_code(rows_back), x.rank, x.world, x.min_peer_rows, x.capacity_rows, info.seq, side_ctas, x.status_ptr,
+            stream),
             "dice_ep_return_rows")
         out, which = x.back[slot][: info.rows_sent], 1
     event = None

@@ -197,6 +197,14 @@ def enabled() -> bool:
     return _enabled and not _failed
 
 
+def side_push_ctas() -> int:
+    """Grid bound of pushes that run on the side stream next to the expert FFN
+    (DICE_EP_P2P_SIDE_CTAS; 0, the default, means one CTA per 8 rows).  A small
+    grid leaves the SMs to the GEMM but stretches the push: measured on 2 GPUs,
+    48 CTAs were no faster than the full grid and 16 CTAs were slower."""
+    return int(os.environ.get("DICE_EP_P2P_SIDE_CTAS", "0"))
+
+
 _fused_return = os.environ.get("DICE_EP_P2P_FUSED_RETURN", "0") == "1"
 
 

@@ -233,7 +233,9 @@ DICE_API int dice_grouped_ffn_f32(const void* rows_in, int64_t n_rows, int hidde
  *   seg_off[W*El+1] (segments of the receive buffer in (source, slot) order,
  *   ready for dice_grouped_ffn with seg_slab[s*El+i] = i) | total, overflow;
  *   seq: a number that grows with every use of the same buffers;
- *   done_counter: device uint32, zero before first use, one per call site.
+ *   done_counter: device uint32, zero before first use, one per call site;
+ *   max_ctas: upper bound of the grid of a push (0 = as many as there are
+ *   rows): a push that runs next to a GEMM on another stream should be small.
  */
 DICE_API int dice_ep_meta_ints(int world, int n_local_experts);
 DICE_API int dice_ep_exchange_counts(const int32_t* seg_offsets, const void* const* peer_matrices,
@@ -246,7 +248,7 @@ DICE_API int dice_ep_dispatch_rows(const void* x, const int32_t* pos, const int3
                           const int32_t* meta, const void* const* peer_recv,
                           const void* const* peer_flags, uint32_t* done_counter, int64_t n_tokens,
                           int k, int hidden, int dtype, int rank, int world, int n_experts,
-                          int capacity_rows, uint32_t seq, uint32_t* status, void* stream);
+                          int capacity_rows, uint32_t seq, int max_ctas, uint32_t* status, void* stream);
 /* wait (bounded) until every source raised flag >= seq; what: 0 dispatch, 1 combine */
 DICE_API int dice_ep_wait_flags(const uint32_t* my_flags, int world, uint32_t seq, int what,
                        uint32_t* status, void* stream);
@@ -255,7 +257,7 @@ DICE_API int dice_ep_wait_flags(const uint32_t* my_flags, int world, uint32_t se
 DICE_API int dice_ep_return_rows(const void* rows, const int32_t* meta, const void* const* peer_back,
                         const void* const* peer_flags, uint32_t* done_counter, int hidden, int dtype,
                         int rank, int world, int back_capacity_rows, int max_rows, uint32_t seq,
-                        uint32_t* status, void* stream);
+                        int max_ctas, uint32_t* status, void* stream);
 /* The expert FFN fused with the return: same as dice_grouped_ffn over the
  * receive buffer, but the second GEMM's epilogue stores every output row
  * straight into the combine buffer of the rank that owns the token (NVLink

@@ -352,10 +352,10 @@ def test_exchange_world_of_one(cuda_device):
         assert lib.dice_ep_exchange_counts(seg.data_ptr(), tab(ctrl.data_ptr()), tab(f(0)), meta.data_ptr(), 0, 1, e, cap,
                                            seq, status.data_ptr(), st) == 0
         assert lib.dice_ep_dispatch_rows(x.data_ptr(), pos.data_ptr(), seg.data_ptr(), meta.data_ptr(), tab(recv.data_ptr()),
-                                         tab(f(1)), done.data_ptr(), n, 2, h, 0, 0, 1, e, cap, seq, status.data_ptr(), st) == 0
+                                         tab(f(1)), done.data_ptr(), n, 2, h, 0, 0, 1, e, cap, seq, 7 * (seq - 1), status.data_ptr(), st) == 0
         assert lib.dice_ep_wait_flags(f(1), 1, seq, 0, status.data_ptr(), st) == 0
         assert lib.dice_ep_return_rows(recv.data_ptr(), meta.data_ptr(), tab(back.data_ptr()), tab(f(2)), done[1:].data_ptr(),
-                                       h, 0, 0, 1, 2 * n, cap, seq, status.data_ptr(), st) == 0
+                                       h, 0, 0, 1, 2 * n, cap, seq, 5 * (seq - 1), status.data_ptr(), st) == 0
         assert lib.dice_ep_wait_flags(f(2), 1, seq, 1, status.data_ptr(), st) == 0
         torch.cuda.synchronize()
         ops.check_status(status)
