@@ -119,7 +119,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
   for (int i = threadIdx.x; i <= p.n_seg; i += kThreads)
     s_seg_off[i] = p.seg_offsets != nullptr ? p.seg_offsets[i] : (i == 0 ? 0 : p.n_rows);
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kPairStages; ++s) {
+    for (int s = 0; s < kPairStages; ++s) {  // all slots' barriers exist even when fewer are used
       mbar_init(full_bar + 8 * s, 1);
       mbar_init(empty_bar + 8 * s, 1);
     }
@@ -183,7 +183,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
           if (leader) mbar_expect_tx(full_bar + 8 * stage, 2 * kPairStageBytes);
           tma_load_2d_pair(a_dst, &tm_a, kb * BK, row0, leader_full);
           tma_load_2d_pair(a_dst + kTileABytes, &tm_b, kb * BK, wrow0, leader_full);
-          if (++stage == kPairStages) { stage = 0; phase ^= 1u; }
+          if (++stage == p.n_stages) { stage = 0; phase ^= 1u; }
         }
       }
     }
@@ -215,7 +215,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
             umma_bf16_pair(d_tmem, a_desc + static_cast<uint64_t>(kk * 2), b_desc + static_cast<uint64_t>(kk * 2), idesc,
                            static_cast<uint32_t>((kb | kk) != 0));
           umma_commit_pair(empty_bar + 8 * stage);
-          if (++stage == kPairStages) { stage = 0; phase ^= 1u; }
+          if (++stage == p.n_stages) { stage = 0; phase ^= 1u; }
         }
         if (!alive) break;
         umma_commit_pair(acc_full_bar + 8 * acc);
@@ -352,6 +352,17 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
   }
 }
 
+// ring depth: kPairStages unless DICE_PAIR_STAGES asks for fewer (experiments)
+int pair_stages() {
+  static int cached = 0;
+  if (cached == 0) {
+    const char* e = getenv("DICE_PAIR_STAGES");
+    const int v = e != nullptr ? atoi(e) : kPairStages;
+    cached = v < 2 ? 2 : (v > kPairStages ? kPairStages : v);
+  }
+  return cached;
+}
+
 // number of CTA pairs that can be resident at once (cached per device); 0 on error
 int resident_pairs() {
   static int cached[64] = {0};
@@ -410,7 +421,7 @@ int dice_internal_gemm_pair(const void* a, int64_t n_rows, int k_dim, const void
   p.ld_out = ld_out;
   p.status = status;
   p.b_box_rows = 128;
-  p.n_stages = kPairStages;
+  p.n_stages = pair_stages();
   if (ret != nullptr) {
     if (ret->world < 1 || ret->world > kMaxPeerRanks || epilogue != DICE_EPI_STORE) return DICE_ERR_ARG;
     p.ret_world = ret->world;

@@ -60,6 +60,8 @@ def test_send_buffer_collected_only_after_completion():
     h.completed = True
     cache.put(2, (None, torch.randn(2), None))
     assert cache.get(0)[-1] is None and cache.get(0)[0] is None and cache.get(0)[1] is recv
+    # the byte accounting follows the collection
+    assert cache.tensors_size() == _nbytes(recv) + 2 * _nbytes(torch.randn(2))
 
 
 def test_recv_buffer_collection_is_manual_and_opt_in():
