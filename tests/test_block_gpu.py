@@ -161,3 +161,35 @@ def test_ep_world_of_one_on_gpu(cuda_device):
     finally:
         dist.destroy_process_group()
         ep_fwd._use_latest_expert_weights = None
+
+
+@pytest.mark.parametrize("variant", ["swiglu", "gelu_tanh"])
+def test_full_size_block_is_row_independent(cuda_device, variant):
+    """Size-independent property at the benchmark's size (16384 tokens, hidden
+    1152, 8 experts, bf16): a token's output does not depend on which other
+    tokens share the batch, so the block applied to half of the batch gives
+    the same bits as the matching half of the full-batch output, although the
+    permutation, the segment sizes and the tile list all differ."""
+    from dice_b200.moe_block import ParaMode, SparseMoeBlock
+
+    torch.manual_seed(0)
+    with torch.device(cuda_device):
+        blk = SparseMoeBlock(1152, 4, 8, 2, 1, 0, 1, ParaMode(), expert_act=variant,
+                             shared_expert=(variant == "swiglu"))
+    blk = blk.to(torch.bfloat16).eval()
+    for p in blk.parameters():
+        p.data.normal_(0.0, 0.02)
+    g = torch.Generator(device="cuda").manual_seed(1)
+    x = torch.randn(64, 256, 1152, generator=g, device=cuda_device).bfloat16()
+    y = blk(x)
+    y_half = blk(x[:32].contiguous())
+    y_odd = blk(x[1::2].contiguous())
+    blk.check_status()
+    assert bool(torch.isfinite(y.float()).all())
+    assert torch.equal(y[:32], y_half)
+    assert torch.equal(y[1::2], y_odd)
+    # and the routing histogram adds up
+    from dice_b200 import ops
+
+    _, _, hist, _ = ops.router_top2(x.view(-1, 1152), blk.gate.weight.detach())
+    assert int(hist.sum()) == 2 * 64 * 256
