@@ -41,6 +41,12 @@ def install(reference_root: str | None = None):
     models.MoEGate = moe_block.MoEGate
     models.MoeMLP = moe_block.MoeMLP
     models.trim_module_list = etrim.trim_module_list
+    # expert parallelism exchanges rows over NVLink peer memory unless DICE_EP_P2P=0 (NCCL is the fallback
+    # when peer memory cannot be mapped)
+    if os.environ.get("DICE_EP_P2P", "1") != "0":
+        from .expertpara import p2p
+
+        p2p.enable(True)
     return models
 
 
