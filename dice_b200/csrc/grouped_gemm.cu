@@ -404,7 +404,7 @@ extern "C" int dice_grouped_gemm(const void* a, int64_t n_rows, int k_dim, const
                   static_cast<uint64_t>(k_dim), static_cast<uint32_t>(b_box_rows));
   if (rc != DICE_OK) return rc;
 
-  GemmParams p;
+  GemmParams p = {};
   p.seg_offsets = seg_offsets;
   p.seg_slab = seg_slab;
   p.n_seg = n_seg;
@@ -447,7 +447,7 @@ int dice_internal_router_tc(const void* x, const void* w_gate, int64_t n_tokens,
   rc = encode_map(&tm_b, w_gate, static_cast<uint64_t>(n_experts), static_cast<uint64_t>(hidden),
                   static_cast<uint32_t>(b_box_rows));
   if (rc != DICE_OK) return rc;
-  GemmParams p;
+  GemmParams p = {};
   p.seg_offsets = nullptr;
   p.seg_slab = nullptr;
   p.n_seg = 1;
