@@ -24,7 +24,7 @@ order *inside* the exchanged buffers is an internal matter.
 from __future__ import annotations
 
 import contextlib
-from typing import List, Optional, Sequence, Tuple
+from typing import Optional, Sequence, Tuple
 
 import torch
 import torch.distributed as dist

@@ -180,6 +180,13 @@ class PeerExchange:
 
         ops.check_status(self.status, "peer-memory exchange")
 
+    def close(self) -> None:
+        """Unmap the peers' buffers (all ranks should have stopped using the exchange)."""
+        torch.cuda.synchronize(self.device)
+        for ptr, offset in self._imported:
+            self.lib.dice_ipc_close(ptr, offset)
+        self._imported = []
+
 
 _exchange: Optional[PeerExchange] = None
 _enabled = os.environ.get("DICE_EP_P2P", "0") == "1"
@@ -251,7 +258,10 @@ def get_exchange(n_experts: int, hidden: int, dtype: torch.dtype, rows: int, n_l
 
 
 def reset() -> None:
+    """Drop the process-wide exchange (a collective decision: every rank calls it)."""
     global _exchange, _failed
+    if _exchange is not None:
+        _exchange.close()
     _exchange = None
     _failed = False
 

@@ -40,9 +40,14 @@ def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
     return None if t is None else t.data_ptr()
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream() -> int:
-    # the raw handle of torch's current stream on the current device (the Stream object is slow to build)
-    return torch._C._cuda_getCurrentRawStream(torch.cuda.current_device())
+    """Raw handle of torch's current stream on the current device."""
+    if _raw_stream is not None:  # much cheaper than building a Stream object
+        return _raw_stream(torch.cuda.current_device())
+    return torch.cuda.current_stream().cuda_stream
 
 
 def check_status(status: torch.Tensor, what: str = "dice_b200 kernel") -> None:

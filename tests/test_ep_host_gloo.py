@@ -7,7 +7,6 @@ import socket
 import sys
 
 import numpy as np
-import pytest
 import torch
 
 HERE = os.path.dirname(os.path.abspath(__file__))
