@@ -52,8 +52,10 @@ __device__ __forceinline__ void cluster_barrier() {
   asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
   asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
+// Arrival on a barrier of the pair's other CTA with the default (CTA-scope) ordering.  It hands an accumulator
+// back, which the tcgen05 fences order; a cluster-scope release would also wait for the warp's global stores.
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 // TMA tile load of this CTA whose completion is counted on the leader's mbarrier
 __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int c0, int c1,
@@ -89,7 +91,7 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
 
 __global__ void __launch_bounds__(kThreads, 1)
 grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
-                         const GemmParams p) {
+                         const __grid_constant__ CUtensorMap tm_b_narrow, const GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* aux = smem + kPairStages * kPairStageBytes;
@@ -173,6 +175,10 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
         const int n_mma = (n_valid + 15) & ~15;
         // the MMA takes the first n_mma/2 weight rows of the tile from the leader and the rest from the peer
         const int wrow0 = slab * p.w_rows + nb * BN + static_cast<int>(cta_rank) * (n_mma / 2);
+        // a tile of at most 128 weight rows needs 64 of them per CTA: the narrow box moves half the bytes
+        const bool narrow = n_mma <= 128;
+        const CUtensorMap* map_b = narrow ? &tm_b_narrow : &tm_b;
+        const uint32_t pair_bytes = 2u * (kTileABytes + (narrow ? kPairTileBBytes / 2 : kPairTileBBytes));
         for (int kb = 0; kb < p.n_kblk; ++kb) {
           if (!mbar_wait(empty_bar + 8 * stage, phase ^ 1u, abort_flag, p.status, DICE_STATUS_WAIT_SMEM_EMPTY)) {
             alive = false;
@@ -180,9 +186,9 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
           }
           const uint32_t a_dst = tiles_smem + stage * kPairStageBytes;
           const uint32_t leader_full = map_to_cta(full_bar + 8 * stage, 0);
-          if (leader) mbar_expect_tx(full_bar + 8 * stage, 2 * kPairStageBytes);
+          if (leader) mbar_expect_tx(full_bar + 8 * stage, pair_bytes);
           tma_load_2d_pair(a_dst, &tm_a, kb * BK, row0, leader_full);
-          tma_load_2d_pair(a_dst + kTileABytes, &tm_b, kb * BK, wrow0, leader_full);
+          tma_load_2d_pair(a_dst + kTileABytes, map_b, kb * BK, wrow0, leader_full);
           if (++stage == p.n_stages) { stage = 0; phase ^= 1u; }
         }
       }
@@ -401,11 +407,14 @@ int dice_internal_gemm_pair(const void* a, int64_t n_rows, int k_dim, const void
                             const DiceReturnSpec* ret) {
   const int pairs = resident_pairs();
   if (pairs <= 0) return DICE_ERR_CUDA;
-  CUtensorMap tm_a, tm_b;
+  CUtensorMap tm_a, tm_b, tm_b_narrow;
   int rc = encode_map(&tm_a, a, static_cast<uint64_t>(n_rows), static_cast<uint64_t>(k_dim), BM);
   if (rc != DICE_OK) return rc;
   rc = encode_map(&tm_b, w, static_cast<uint64_t>(n_slabs) * static_cast<uint64_t>(w_rows), static_cast<uint64_t>(k_dim),
                   128);
+  if (rc != DICE_OK) return rc;
+  rc = encode_map(&tm_b_narrow, w, static_cast<uint64_t>(n_slabs) * static_cast<uint64_t>(w_rows),
+                  static_cast<uint64_t>(k_dim), 64);
   if (rc != DICE_OK) return rc;
   GemmParams p = {};
   p.seg_offsets = seg_offsets;
@@ -451,6 +460,6 @@ int dice_internal_gemm_pair(const void* a, int64_t n_rows, int k_dim, const void
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  if (cudaLaunchKernelEx(&cfg, grouped_gemm_pair_kernel, tm_a, tm_b, p) != cudaSuccess) return DICE_ERR_CUDA;
+  if (cudaLaunchKernelEx(&cfg, grouped_gemm_pair_kernel, tm_a, tm_b, tm_b_narrow, p) != cudaSuccess) return DICE_ERR_CUDA;
   return DICE_OK;
 }
