@@ -100,8 +100,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   const int64_t total_tiles = static_cast<int64_t>(total_mblk) * p.n_nblk;
 
   if (warp == 0) {
-    // ---------------- loader ----------------
-    if (lane == 0) {
+    // ---------------- loader (warp-wide loop, one elected lane issues the copies) ----------------
+    {
       // (tile, k-block) cursor over this CTA's share of the tile list
       struct Cursor { int64_t t; int kb, seg, row0, wrow0; bool valid; };
       auto decode = [&](Cursor& c) {
@@ -124,16 +124,19 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       while (cur.valid) {
         if (!mbar_wait(empty_bar + 8 * stage, phase ^ 1u, abort_flag, p.status, DICE_STATUS_WAIT_SMEM_EMPTY)) break;
         const uint32_t a_dst = tiles_smem + stage * stage_bytes;
-        mbar_expect_tx(full_bar + 8 * stage, stage_tx_bytes);
-        tma_load_2d(a_dst, &tm_a, cur.kb * BK, cur.row0, full_bar + 8 * stage);
-        tma_load_2d(a_dst + kTileABytes, &tm_b, cur.kb * BK, cur.wrow0, full_bar + 8 * stage);
+        if (elect_one()) {
+          mbar_expect_tx(full_bar + 8 * stage, stage_tx_bytes);
+          tma_load_2d(a_dst, &tm_a, cur.kb * BK, cur.row0, full_bar + 8 * stage);
+          tma_load_2d(a_dst + kTileABytes, &tm_b, cur.kb * BK, cur.wrow0, full_bar + 8 * stage);
+        }
+        __syncwarp();
         if (++stage == n_stages) { stage = 0; phase ^= 1u; }
         advance(cur);
       }
     }
   } else if (warp == 1) {
-    // ---------------- tensor-core issue ----------------
-    if (lane == 0) {
+    // ---------------- tensor-core issue (warp-wide loop, one elected lane issues) ----------------
+    {
       int stage = 0, acc = 0;
       uint32_t phase = 0, acc_phase = 0;
       bool alive = true;
@@ -154,17 +157,21 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
           const uint32_t a_addr = tiles_smem + stage * stage_bytes;
           const uint64_t a_desc = make_operand_desc(a_addr);
           const uint64_t b_desc = make_operand_desc(a_addr + kTileABytes);
+          if (elect_one()) {
 #pragma unroll
-          for (int kk = 0; kk < BK / UMMA_K; ++kk) {
-            // advance both operands by 16 elements (32 bytes) along K inside the swizzled row
-            umma_bf16(d_tmem, a_desc + static_cast<uint64_t>(kk * 2), b_desc + static_cast<uint64_t>(kk * 2), idesc,
-                      static_cast<uint32_t>((kb | kk) != 0));
+            for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+              // advance both operands by 16 elements (32 bytes) along K inside the swizzled row
+              umma_bf16(d_tmem, a_desc + static_cast<uint64_t>(kk * 2), b_desc + static_cast<uint64_t>(kk * 2), idesc,
+                        static_cast<uint32_t>((kb | kk) != 0));
+            }
+            umma_commit(empty_bar + 8 * stage);  // slot reusable once these MMAs have read it
           }
-          umma_commit(empty_bar + 8 * stage);  // slot reusable once these MMAs have read it
+          __syncwarp();
           if (++stage == n_stages) { stage = 0; phase ^= 1u; }
         }
         if (!alive) break;
-        umma_commit(acc_full_bar + 8 * acc);   // accumulator complete
+        if (elect_one()) umma_commit(acc_full_bar + 8 * acc);   // accumulator complete
+        __syncwarp();
         if (++acc == kAccStages) { acc = 0; acc_phase ^= 1u; }
       }
     }

@@ -89,6 +89,9 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
                : "memory");
 }
 
+// The loader and the tensor-core warp run their loops with all 32 lanes (the waits are warp-wide) and elect one
+// lane for the TMA / MMA instructions: loop state stays warp-uniform for the compiler, and the issue loop is
+// short enough to keep the tensor pipe fed (a single-lane loop under `lane == 0` was 15 % slower).
 __global__ void __launch_bounds__(kThreads, 1)
 grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                          const __grid_constant__ CUtensorMap tm_b_narrow, const GemmParams p) {
@@ -160,7 +163,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
 
   if (warp == 0) {
     // ---------------- loader (both CTAs) ----------------
-    if (lane == 0) {
+    {
       int stage = 0, seg = 0;
       uint32_t phase = 0;
       bool alive = true;
@@ -186,16 +189,19 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
           }
           const uint32_t a_dst = tiles_smem + stage * kPairStageBytes;
           const uint32_t leader_full = map_to_cta(full_bar + 8 * stage, 0);
-          if (leader) mbar_expect_tx(full_bar + 8 * stage, pair_bytes);
-          tma_load_2d_pair(a_dst, &tm_a, kb * BK, row0, leader_full);
-          tma_load_2d_pair(a_dst + kTileABytes, map_b, kb * BK, wrow0, leader_full);
+          if (elect_one()) {
+            if (leader) mbar_expect_tx(full_bar + 8 * stage, pair_bytes);
+            tma_load_2d_pair(a_dst, &tm_a, kb * BK, row0, leader_full);
+            tma_load_2d_pair(a_dst + kTileABytes, map_b, kb * BK, wrow0, leader_full);
+          }
+          __syncwarp();
           if (++stage == p.n_stages) { stage = 0; phase ^= 1u; }
         }
       }
     }
   } else if (warp == 1) {
     // ---------------- tensor-core issue (leader only) ----------------
-    if (leader && lane == 0) {
+    if (leader) {
       int stage = 0, acc = 0;
       uint32_t phase = 0, acc_phase = 0;
       bool alive = true;
@@ -216,15 +222,19 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
           const uint32_t a_addr = tiles_smem + stage * kPairStageBytes;
           const uint64_t a_desc = make_operand_desc(a_addr);
           const uint64_t b_desc = make_operand_desc(a_addr + kTileABytes);
+          if (elect_one()) {
 #pragma unroll
-          for (int kk = 0; kk < BK / UMMA_K; ++kk)
-            umma_bf16_pair(d_tmem, a_desc + static_cast<uint64_t>(kk * 2), b_desc + static_cast<uint64_t>(kk * 2), idesc,
-                           static_cast<uint32_t>((kb | kk) != 0));
-          umma_commit_pair(empty_bar + 8 * stage);
+            for (int kk = 0; kk < BK / UMMA_K; ++kk)
+              umma_bf16_pair(d_tmem, a_desc + static_cast<uint64_t>(kk * 2), b_desc + static_cast<uint64_t>(kk * 2), idesc,
+                             static_cast<uint32_t>((kb | kk) != 0));
+            umma_commit_pair(empty_bar + 8 * stage);
+          }
+          __syncwarp();
           if (++stage == p.n_stages) { stage = 0; phase ^= 1u; }
         }
         if (!alive) break;
-        umma_commit_pair(acc_full_bar + 8 * acc);
+        if (elect_one()) umma_commit_pair(acc_full_bar + 8 * acc);
+        __syncwarp();
         if (++acc == kAccStages) { acc = 0; acc_phase ^= 1u; }
       }
     }
