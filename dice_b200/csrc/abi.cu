@@ -1,5 +1,16 @@
 // Version / error-text entry points of the C ABI.
+#include <stdlib.h>
+
 #include "common.cuh"
+
+bool dice_pdl_enabled() {
+  static int cached = -1;
+  if (cached < 0) {
+    const char* e = getenv("DICE_PDL");
+    cached = (e != nullptr && e[0] == '0') ? 0 : 1;
+  }
+  return cached != 0;
+}
 
 extern "C" int dice_abi_version(void) { return DICE_ABI_VERSION; }
 

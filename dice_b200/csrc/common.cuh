@@ -34,9 +34,37 @@ static inline size_t dice_dtype_size(int dtype) {
   return dtype == DICE_BF16 ? 2 : (dtype == DICE_F32 ? 4 : 0);
 }
 
+// ---- programmatic dependent launch ------------------------------------------------
+// Kernels started with dice_launch() may become resident while the kernel before them in the stream is still
+// running (its blocks have all started and called pdl_trigger(), or exited).  Such a kernel does its set-up,
+// then calls pdl_wait(), which returns once the earlier kernels have completed and their writes are visible;
+// it touches no global memory before that.  Launch gaps and prologues then overlap the predecessor's tail.
+// DICE_PDL=0 in the environment turns the launch attribute off (plain stream order).
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+bool dice_pdl_enabled();  // abi.cu
+
+template <typename... KArgs, typename... Args>
+static inline cudaError_t dice_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                      Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = dice_pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
+// streaming 16-byte load (coherent: the kernels that use it may start while the producer of the data still runs)
 __device__ __forceinline__ uint4 ldg_stream16(const void* p) {
   uint4 v;
-  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+  asm volatile("ld.global.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
                : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
                : "l"(p));
   return v;

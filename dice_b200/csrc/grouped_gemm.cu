@@ -57,9 +57,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-  // a null offset table means one segment covering all rows
-  for (int i = threadIdx.x; i <= p.n_seg; i += kThreads)
-    s_seg_off[i] = p.seg_offsets != nullptr ? p.seg_offsets[i] : (i == 0 ? 0 : p.n_rows);
+  // Set-up that needs no global memory comes first: with a programmatic dependent launch this part overlaps the
+  // tail of the kernel before this one in the stream.
+  pdl_trigger();
   if (threadIdx.x < 64) s_hist[threadIdx.x] = 0;
   if (threadIdx.x == 0) {
     for (int s = 0; s < n_stages; ++s) {
@@ -73,6 +73,12 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
+  if (warp == 1) tmem_alloc(smem_u32(tmem_slot), kTmemCols);
+  pdl_wait();  // results of earlier kernels (segment table, rows) are visible from here on
+
+  // a null offset table means one segment covering all rows
+  for (int i = threadIdx.x; i <= p.n_seg; i += kThreads)
+    s_seg_off[i] = p.seg_offsets != nullptr ? p.seg_offsets[i] : (i == 0 ? 0 : p.n_rows);
   __syncthreads();
   if (threadIdx.x == 0) {
     int run = 0;
@@ -90,7 +96,6 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     }
     s_mprefix[p.n_seg] = run;
   }
-  if (warp == 1) tmem_alloc(smem_u32(tmem_slot), kTmemCols);
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
@@ -435,7 +440,9 @@ extern "C" int dice_grouped_gemm(const void* a, int64_t n_rows, int k_dim, const
 
   const int64_t max_tiles = ((n_rows + BM - 1) / BM + n_seg) * p.n_nblk;
   const int grid = static_cast<int>(max_tiles < sms ? max_tiles : sms);
-  grouped_gemm_kernel<<<grid, kThreads, kSmemBytes, static_cast<cudaStream_t>(stream)>>>(tm_a, tm_b, p);
+  if (dice_launch(grouped_gemm_kernel, dim3(grid), dim3(kThreads), kSmemBytes, static_cast<cudaStream_t>(stream), tm_a, tm_b,
+                  p) != cudaSuccess)
+    return DICE_ERR_CUDA;
   return cudaGetLastError() == cudaSuccess ? DICE_OK : DICE_ERR_CUDA;
 }
 
@@ -477,7 +484,8 @@ int dice_internal_router_tc(const void* x, const void* w_gate, int64_t n_tokens,
   p.logits_out = static_cast<__nv_bfloat16*>(out_logits);
   const int64_t tiles = (n_tokens + BM - 1) / BM;
   const int grid = static_cast<int>(tiles < sms ? tiles : sms);
-  grouped_gemm_kernel<<<grid, kThreads, kSmemBytes, stream>>>(tm_a, tm_b, p);
+  if (dice_launch(grouped_gemm_kernel, dim3(grid), dim3(kThreads), kSmemBytes, stream, tm_a, tm_b, p) != cudaSuccess)
+    return DICE_ERR_CUDA;
   return cudaGetLastError() == cudaSuccess ? DICE_OK : DICE_ERR_CUDA;
 }
 

@@ -113,16 +113,13 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t cta_rank = cluster_cta_rank();  // 0 = leader
-  if (p.ret_world > 0) {
-    if (threadIdx.x <= p.ret_world) s_ret_src[threadIdx.x] = p.ret_meta[2 * p.ret_world + threadIdx.x];
-    if (threadIdx.x < p.ret_world) s_ret_base[threadIdx.x] = p.ret_meta[p.ret_world + threadIdx.x];
-  }
   const bool leader = cta_rank == 0;
   const int64_t pair_id = blockIdx.x >> 1;
   const int64_t n_pairs = gridDim.x >> 1;
 
-  for (int i = threadIdx.x; i <= p.n_seg; i += kThreads)
-    s_seg_off[i] = p.seg_offsets != nullptr ? p.seg_offsets[i] : (i == 0 ? 0 : p.n_rows);
+  // Set-up that needs no global memory comes first: with a programmatic dependent launch this part overlaps the
+  // tail of the kernel before this one in the stream.
+  pdl_trigger();
   if (threadIdx.x == 0) {
     for (int s = 0; s < kPairStages; ++s) {  // all slots' barriers exist even when fewer are used
       mbar_init(full_bar + 8 * s, 1);
@@ -135,6 +132,15 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
+  if (warp == 1) tmem_alloc_pair(smem_u32(tmem_slot), kTmemCols);
+  pdl_wait();  // the segment table and the rows written by earlier kernels are visible from here on
+
+  if (p.ret_world > 0) {
+    if (threadIdx.x <= p.ret_world) s_ret_src[threadIdx.x] = p.ret_meta[2 * p.ret_world + threadIdx.x];
+    if (threadIdx.x < p.ret_world) s_ret_base[threadIdx.x] = p.ret_meta[p.ret_world + threadIdx.x];
+  }
+  for (int i = threadIdx.x; i <= p.n_seg; i += kThreads)
+    s_seg_off[i] = p.seg_offsets != nullptr ? p.seg_offsets[i] : (i == 0 ? 0 : p.n_rows);
   __syncthreads();
   if (threadIdx.x == 0) {
     int run = 0;
@@ -152,7 +158,6 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
     }
     s_mprefix[p.n_seg] = run;
   }
-  if (warp == 1) tmem_alloc_pair(smem_u32(tmem_slot), kTmemCols);
   tc_fence_before_sync();
   __syncthreads();
   cluster_barrier();  // the peer's mbarriers are initialised before anything signals them
@@ -463,13 +468,15 @@ int dice_internal_gemm_pair(const void* a, int64_t n_rows, int k_dim, const void
   cfg.blockDim = dim3(kThreads, 1, 1);
   cfg.dynamicSmemBytes = kPairSmemBytes;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 2;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = dice_pdl_enabled() ? 2 : 1;
   if (cudaLaunchKernelEx(&cfg, grouped_gemm_pair_kernel, tm_a, tm_b, tm_b_narrow, p) != cudaSuccess) return DICE_ERR_CUDA;
   return DICE_OK;
 }

@@ -23,8 +23,10 @@ constexpr int kMaxExperts = 64;
 __global__ void __launch_bounds__(kChunkRows)
 plan_count_kernel(const int64_t* __restrict__ flat_idx, int64_t n_rows, int n_experts, int* __restrict__ chunk_hist) {
   __shared__ int s_hist[kMaxExperts];
+  pdl_trigger();
   if (threadIdx.x < kMaxExperts) s_hist[threadIdx.x] = 0;
   __syncthreads();
+  pdl_wait();
   const int64_t r = static_cast<int64_t>(blockIdx.x) * kChunkRows + threadIdx.x;
   if (r < n_rows) {
     const int64_t e = flat_idx[r];
@@ -44,6 +46,8 @@ plan_scan_kernel(int* __restrict__ chunk_hist, int n_chunks, int n_experts, int*
   __shared__ int s_total[kMaxExperts];
   __shared__ int s_base[kMaxExperts + 1];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  pdl_trigger();
+  pdl_wait();
   for (int e = warp; e < n_experts; e += kScanThreads / 32) {
     int sum = 0;
     for (int c = lane; c < n_chunks; c += 32) sum += chunk_hist[static_cast<int64_t>(c) * n_experts + e];
@@ -83,8 +87,10 @@ plan_rank_kernel(const int64_t* __restrict__ flat_idx, int64_t n_rows, int n_exp
   constexpr int kWarps = kChunkRows / 32;
   __shared__ int s_warp_count[kWarps][kMaxExperts];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  pdl_trigger();
   for (int i = threadIdx.x; i < kWarps * kMaxExperts; i += kChunkRows) (&s_warp_count[0][0])[i] = 0;
   __syncthreads();
+  pdl_wait();
   const int64_t r = static_cast<int64_t>(blockIdx.x) * kChunkRows + threadIdx.x;
   int e = -1;
   if (r < n_rows) {
@@ -114,6 +120,8 @@ permute_rows_kernel(const uint4* __restrict__ x, const int* __restrict__ pos, in
                     uint4* __restrict__ out) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t t = static_cast<int64_t>(blockIdx.x) * 8 + warp;
+  pdl_trigger();
+  pdl_wait();
   if (t >= n_tokens) return;
   int64_t dst[K];
 #pragma unroll
@@ -162,6 +170,8 @@ unpermute_combine_kernel(const uint4* __restrict__ src0, const int* __restrict__
   constexpr int EL = Vec16<T>::kElems;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t t = static_cast<int64_t>(blockIdx.x) * 8 + warp;
+  pdl_trigger();
+  pdl_wait();
   if (t >= n_tokens) return;
   const int64_t i0 = idx0 ? static_cast<int64_t>(idx0[t * idx0_stride]) : t;
   const int64_t i1 = src1 ? (idx1 ? static_cast<int64_t>(idx1[t * idx1_stride]) : t) : -1;
@@ -238,10 +248,12 @@ extern "C" int dice_permute_plan(const int64_t* flat_idx, int64_t n_rows, int n_
   DICE_CHECK_ARG(scratch_bytes >= dice_permute_scratch_bytes(n_rows, n_experts), DICE_ERR_SCRATCH);
   const int chunks = static_cast<int>((n_rows + kChunkRows - 1) / kChunkRows);
   int* chunk_hist = static_cast<int*>(scratch);
-  plan_count_kernel<<<chunks, kChunkRows, 0, s>>>(flat_idx, n_rows, n_experts, chunk_hist);
-  plan_scan_kernel<<<1, kScanThreads, 0, s>>>(chunk_hist, chunks, n_experts, out_seg_offsets);
-  plan_rank_kernel<<<chunks, kChunkRows, 0, s>>>(flat_idx, n_rows, n_experts, chunk_hist, out_pos, out_order);
-  return cudaGetLastError() == cudaSuccess ? DICE_OK : DICE_ERR_CUDA;
+  DICE_CUDA_OK(dice_launch(plan_count_kernel, dim3(chunks), dim3(kChunkRows), 0, s, flat_idx, n_rows, n_experts, chunk_hist));
+  DICE_CUDA_OK(dice_launch(plan_scan_kernel, dim3(1), dim3(kScanThreads), 0, s, chunk_hist, chunks, n_experts,
+                           out_seg_offsets));
+  DICE_CUDA_OK(dice_launch(plan_rank_kernel, dim3(chunks), dim3(kChunkRows), 0, s, flat_idx, n_rows, n_experts,
+                           chunk_hist, out_pos, out_order));
+  return DICE_OK;
 }
 
 // Device address of g_plan_static_scratch on the current device, looked up once per device.
@@ -277,11 +289,14 @@ extern "C" int dice_permute_plan_static(const int64_t* flat_idx, int64_t n_rows,
   const int rc = static_plan_scratch(&chunk_hist);
   if (rc != DICE_OK) return rc;
   // pass 1 overwrites every cell the later passes read, so nothing has to be cleared between calls
-  plan_count_kernel<<<static_cast<int>(chunks), kChunkRows, 0, s>>>(flat_idx, n_rows, n_experts, chunk_hist);
-  plan_scan_kernel<<<1, kScanThreads, 0, s>>>(chunk_hist, static_cast<int>(chunks), n_experts, out_seg_offsets);
-  plan_rank_kernel<<<static_cast<int>(chunks), kChunkRows, 0, s>>>(flat_idx, n_rows, n_experts, chunk_hist, out_pos,
-                                                                    out_order);
-  return cudaGetLastError() == cudaSuccess ? DICE_OK : DICE_ERR_CUDA;
+  const int n_chunks = static_cast<int>(chunks);
+  DICE_CUDA_OK(dice_launch(plan_count_kernel, dim3(n_chunks), dim3(kChunkRows), 0, s, flat_idx, n_rows, n_experts,
+                           chunk_hist));
+  DICE_CUDA_OK(dice_launch(plan_scan_kernel, dim3(1), dim3(kScanThreads), 0, s, chunk_hist, n_chunks, n_experts,
+                           out_seg_offsets));
+  DICE_CUDA_OK(dice_launch(plan_rank_kernel, dim3(n_chunks), dim3(kChunkRows), 0, s, flat_idx, n_rows, n_experts,
+                           chunk_hist, out_pos, out_order));
+  return DICE_OK;
 }
 
 extern "C" int dice_permute_rows(const void* x, const int32_t* pos, int64_t n_tokens, int k, int hidden, int dtype,
@@ -298,13 +313,14 @@ extern "C" int dice_permute_rows(const void* x, const int32_t* pos, int64_t n_to
   const int64_t blocks = (n_tokens + 7) / 8;
   DICE_CHECK_ARG(blocks <= 0x7fffffffLL, DICE_ERR_LIMIT);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const dim3 grid(static_cast<unsigned>(blocks));
   if (k == 2)
-    permute_rows_kernel<2><<<static_cast<unsigned>(blocks), 256, 0, s>>>(static_cast<const uint4*>(x), pos, n_tokens,
-                                                                        row_vec, static_cast<uint4*>(out_rows));
+    DICE_CUDA_OK(dice_launch(permute_rows_kernel<2>, grid, dim3(256), 0, s, static_cast<const uint4*>(x), pos, n_tokens,
+                             row_vec, static_cast<uint4*>(out_rows)));
   else
-    permute_rows_kernel<1><<<static_cast<unsigned>(blocks), 256, 0, s>>>(static_cast<const uint4*>(x), pos, n_tokens,
-                                                                        row_vec, static_cast<uint4*>(out_rows));
-  return cudaGetLastError() == cudaSuccess ? DICE_OK : DICE_ERR_CUDA;
+    DICE_CUDA_OK(dice_launch(permute_rows_kernel<1>, grid, dim3(256), 0, s, static_cast<const uint4*>(x), pos, n_tokens,
+                             row_vec, static_cast<uint4*>(out_rows)));
+  return DICE_OK;
 }
 
 extern "C" int dice_unpermute_combine(const void* src0, const int32_t* idx0, int idx0_stride, const void* src1,
@@ -323,15 +339,17 @@ extern "C" int dice_unpermute_combine(const void* src0, const int32_t* idx0, int
   const int64_t blocks = (n_tokens + 7) / 8;
   DICE_CHECK_ARG(blocks <= 0x7fffffffLL, DICE_ERR_LIMIT);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const dim3 grid(static_cast<unsigned>(blocks));
   if (dtype == DICE_BF16)
-    unpermute_combine_kernel<__nv_bfloat16><<<static_cast<unsigned>(blocks), 256, 0, s>>>(
-        static_cast<const uint4*>(src0), idx0, idx0_stride, static_cast<const uint4*>(src1), idx1, idx1_stride, w0, w1,
-        w_stride, static_cast<const uint4*>(addend), n_tokens, row_vec, static_cast<uint4*>(out));
+    DICE_CUDA_OK(dice_launch(unpermute_combine_kernel<__nv_bfloat16>, grid, dim3(256), 0, s,
+                             static_cast<const uint4*>(src0), idx0, idx0_stride, static_cast<const uint4*>(src1), idx1,
+                             idx1_stride, w0, w1, w_stride, static_cast<const uint4*>(addend), n_tokens, row_vec,
+                             static_cast<uint4*>(out)));
   else
-    unpermute_combine_kernel<float><<<static_cast<unsigned>(blocks), 256, 0, s>>>(
-        static_cast<const uint4*>(src0), idx0, idx0_stride, static_cast<const uint4*>(src1), idx1, idx1_stride, w0, w1,
-        w_stride, static_cast<const uint4*>(addend), n_tokens, row_vec, static_cast<uint4*>(out));
-  return cudaGetLastError() == cudaSuccess ? DICE_OK : DICE_ERR_CUDA;
+    DICE_CUDA_OK(dice_launch(unpermute_combine_kernel<float>, grid, dim3(256), 0, s, static_cast<const uint4*>(src0),
+                             idx0, idx0_stride, static_cast<const uint4*>(src1), idx1, idx1_stride, w0, w1, w_stride,
+                             static_cast<const uint4*>(addend), n_tokens, row_vec, static_cast<uint4*>(out)));
+  return DICE_OK;
 }
 
 extern "C" int64_t dice_w13_rows(int ffn) { return ffn <= 0 ? 0 : (static_cast<int64_t>(ffn) + 127) / 128 * 256; }
