@@ -85,6 +85,8 @@ ep_counts_kernel(const int* __restrict__ seg_offsets,  // [E+1] this rank's key-
   __shared__ int s_cnt[kMaxRanks][kMaxKeys];
   __shared__ int s_ok;
   const int el = n_keys / world;
+  pdl_trigger();
+  pdl_wait();
   if (threadIdx.x == 0) s_ok = 1;
   // publish my row everywhere (my own matrix included)
   for (int i = threadIdx.x; i < world * n_keys; i += blockDim.x) {
@@ -171,6 +173,8 @@ ep_dispatch_kernel(const uint4* __restrict__ x, const int* __restrict__ pos, con
                    uint32_t* status) {
   __shared__ int s_first[kMaxRanks + 1];  // first sorted position of each owner's block
   __shared__ int s_base[kMaxRanks];
+  pdl_trigger();
+  pdl_wait();
   if (threadIdx.x <= world) s_first[threadIdx.x] = seg_offsets[threadIdx.x * el];
   if (threadIdx.x < world) s_base[threadIdx.x] = meta[threadIdx.x];
   __syncthreads();
@@ -204,6 +208,8 @@ ep_dispatch_kernel(const uint4* __restrict__ x, const int* __restrict__ pos, con
 // ---- 3. wait for all sources ------------------------------------------------------------
 __global__ void ep_wait_kernel(const uint32_t* __restrict__ my_flags, int world, uint32_t seq, uint32_t* status,
                                uint32_t code) {
+  pdl_trigger();
+  pdl_wait();
   if (threadIdx.x < world) wait_flag(my_flags + threadIdx.x, seq, status, code);
 }
 
@@ -214,6 +220,8 @@ ep_return_kernel(const uint4* __restrict__ rows, const int* __restrict__ meta, P
                  uint32_t* status) {
   __shared__ int s_src_off[kMaxRanks + 1];
   __shared__ int s_back[kMaxRanks];
+  pdl_trigger();
+  pdl_wait();
   if (threadIdx.x <= world) s_src_off[threadIdx.x] = meta[2 * world + threadIdx.x];
   if (threadIdx.x < world) s_back[threadIdx.x] = meta[world + threadIdx.x];
   __syncthreads();
@@ -261,10 +269,10 @@ extern "C" int dice_ep_exchange_counts(const int32_t* seg_offsets, const void* c
   if (rc != DICE_OK) return rc;
   rc = fill_table(&f, peer_flags, world);
   if (rc != DICE_OK) return rc;
-  ep_counts_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      seg_offsets, m, f, static_cast<int*>(m.ptr[rank]), static_cast<const uint32_t*>(f.ptr[rank]), meta, rank, world,
-      n_experts, capacity_rows, seq, status);
-  return cudaGetLastError() == cudaSuccess ? DICE_OK : DICE_ERR_CUDA;
+  DICE_CUDA_OK(dice_launch(ep_counts_kernel, dim3(1), dim3(256), 0, static_cast<cudaStream_t>(stream), seg_offsets, m, f,
+                           static_cast<int*>(m.ptr[rank]), static_cast<const uint32_t*>(f.ptr[rank]), meta, rank, world,
+                           n_experts, capacity_rows, seq, status));
+  return DICE_OK;
 }
 
 extern "C" int dice_ep_dispatch_rows(const void* x, const int32_t* pos, const int32_t* seg_offsets,
@@ -291,23 +299,23 @@ extern "C" int dice_ep_dispatch_rows(const void* x, const int32_t* pos, const in
   DICE_CHECK_ARG(blocks <= 0x7fffffffLL, DICE_ERR_LIMIT);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int el = n_experts / world;
+  const dim3 grid(static_cast<unsigned>(blocks));
   if (k == 2)
-    ep_dispatch_kernel<2><<<static_cast<unsigned>(blocks), 256, 0, s>>>(
-        static_cast<const uint4*>(x), pos, seg_offsets, meta, r, f, done_counter, n_tokens, row_vec, rank, world, el,
-        capacity_rows, seq, status);
+    DICE_CUDA_OK(dice_launch(ep_dispatch_kernel<2>, grid, dim3(256), 0, s, static_cast<const uint4*>(x), pos, seg_offsets,
+                             meta, r, f, done_counter, n_tokens, row_vec, rank, world, el, capacity_rows, seq, status));
   else
-    ep_dispatch_kernel<1><<<static_cast<unsigned>(blocks), 256, 0, s>>>(
-        static_cast<const uint4*>(x), pos, seg_offsets, meta, r, f, done_counter, n_tokens, row_vec, rank, world, el,
-        capacity_rows, seq, status);
-  return cudaGetLastError() == cudaSuccess ? DICE_OK : DICE_ERR_CUDA;
+    DICE_CUDA_OK(dice_launch(ep_dispatch_kernel<1>, grid, dim3(256), 0, s, static_cast<const uint4*>(x), pos, seg_offsets,
+                             meta, r, f, done_counter, n_tokens, row_vec, rank, world, el, capacity_rows, seq, status));
+  return DICE_OK;
 }
 
 extern "C" int dice_ep_wait_flags(const uint32_t* my_flags, int world, uint32_t seq, int what, uint32_t* status,
                                   void* stream) {
   DICE_CHECK_ARG(my_flags && world >= 1 && world <= kMaxRanks, DICE_ERR_ARG);
   const uint32_t code = what == 0 ? DICE_STATUS_WAIT_PEER_DISPATCH : DICE_STATUS_WAIT_PEER_COMBINE;
-  ep_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(my_flags, world, seq, status, code);
-  return cudaGetLastError() == cudaSuccess ? DICE_OK : DICE_ERR_CUDA;
+  DICE_CUDA_OK(dice_launch(ep_wait_kernel, dim3(1), dim3(32), 0, static_cast<cudaStream_t>(stream), my_flags, world, seq,
+                           status, code));
+  return DICE_OK;
 }
 
 extern "C" int dice_ep_return_rows(const void* rows, const int32_t* meta, const void* const* peer_back,
@@ -329,9 +337,10 @@ extern "C" int dice_ep_return_rows(const void* rows, const int32_t* meta, const 
   if (blocks < 1) blocks = 1;
   if (blocks > 148 * 16) blocks = 148 * 16;  // grid-stride over the rows actually received
   if (max_ctas > 0 && blocks > max_ctas) blocks = max_ctas;
-  ep_return_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const uint4*>(rows), meta, b, f, done_counter, row_vec, rank, world, back_capacity_rows, seq, status);
-  return cudaGetLastError() == cudaSuccess ? DICE_OK : DICE_ERR_CUDA;
+  DICE_CUDA_OK(dice_launch(ep_return_kernel, dim3(static_cast<unsigned>(blocks)), dim3(256), 0,
+                           static_cast<cudaStream_t>(stream), static_cast<const uint4*>(rows), meta, b, f, done_counter,
+                           row_vec, rank, world, back_capacity_rows, seq, status));
+  return DICE_OK;
 }
 
 // ---- CUDA IPC plumbing (set-up time only) ---------------------------------------------------

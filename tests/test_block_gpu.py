@@ -193,3 +193,22 @@ def test_full_size_block_is_row_independent(cuda_device, variant):
 
     _, _, hist, _ = ops.router_top2(x.view(-1, 1152), blk.gate.weight.detach())
     assert int(hist.sum()) == 2 * 64 * 256
+
+
+def test_dependent_launch_changes_nothing(cuda_device):
+    """The kernels are launched with programmatic dependent launch (a kernel may become resident while its
+    predecessor still runs and waits before touching memory).  A chain of six full-width blocks, repeated three
+    times, must give bit-identical outputs with the launch attribute on and off."""
+    import subprocess
+
+    root = os.path.dirname(HERE)
+    digests = []
+    for flag in ("1", "0"):
+        env = dict(os.environ, DICE_PDL=flag, PYTHONPATH=root + os.pathsep + os.environ.get("PYTHONPATH", ""))
+        r = subprocess.run([sys.executable, os.path.join(HERE, "pdl_worker.py")], env=env, capture_output=True,
+                           text=True, timeout=600)
+        assert r.returncode == 0, r.stderr[-2000:]
+        lines = [ln for ln in r.stdout.splitlines() if ln.startswith("DIGEST ")]
+        assert lines, r.stdout[-2000:]
+        digests.append(lines[-1])
+    assert digests[0] == digests[1]
