@@ -24,6 +24,7 @@
 // bounded by wall time; on expiry a status code is recorded and the kernel
 // returns (results of that call are then undefined, the context stays usable).
 #include <cuda.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include "common.cuh"
@@ -243,6 +244,235 @@ ep_return_kernel(const uint4* __restrict__ rows, const int* __restrict__ meta, P
   signal_when_grid_done(done_counter, flags, rank, world, seq);
 }
 
+
+// ---- bulk-copy variants of the two pushes ---------------------------------------------------
+// A push that has the GPU to itself (synchronous exchange) moves its rows with the copy unit instead of with
+// the SMs' load/store pipes: one warp per CTA streams chunks of rows through a ring of shared-memory buffers
+// (cp.async.bulk: global -> shared, completing on an mbarrier; shared -> global, local or peer, tracked in
+// bulk async-groups).  Local and remote destinations no longer share store queues, and the requests that
+// cross NVLink are whole rows.  The SIMT kernels above remain for pushes that run next to a GEMM on another
+// stream (they need no shared memory and fit beside its CTAs).
+constexpr int kBulkBufs = 4;
+constexpr int kBulkBufBytes = 32768;
+constexpr int kBulkLag = kBulkBufs - 2;  // chunks between a buffer's load and its stores
+constexpr uint64_t kBulkWaitLimitNs = 1000ull * 1000ull * 1000ull;
+
+__device__ __forceinline__ uint32_t smem_addr32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ void bulk_bar_init(uint32_t bar) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+               "l"(src), "r"(bytes), "r"(bar)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_store(void* dst, uint32_t src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// all but the most recent group of this thread have finished reading shared memory
+__device__ __forceinline__ void bulk_wait_read_1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
+// every group of this thread is complete: its writes are performed
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ bool bulk_bar_wait(uint32_t bar, uint32_t parity) {
+  const uint64_t t0 = timer_ns();
+  uint32_t spins = 0;
+  for (;;) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (ok) return true;
+    if ((++spins & 127u) == 0 && timer_ns() - t0 > kBulkWaitLimitNs) return false;
+  }
+}
+// after the last store: writes of the copy unit are ordered before the flag this CTA may raise
+__device__ __forceinline__ void bulk_drain() {
+  bulk_wait_all();
+  asm volatile("fence.proxy.async;" ::: "memory");
+}
+
+template <int K>
+__global__ void __launch_bounds__(32)
+ep_dispatch_bulk_kernel(const uint8_t* __restrict__ x, const int* __restrict__ pos, const int* __restrict__ seg_offsets,
+                        const int* __restrict__ meta, PeerTable recv_bufs, PeerTable flags, unsigned int* done_counter,
+                        int64_t n_tokens, uint32_t row_bytes, int tokens_per_chunk, int rank, int world, int el,
+                        int capacity_rows, uint32_t seq, uint32_t* status) {
+  extern __shared__ __align__(128) uint8_t bulk_bufs[];
+  __shared__ __align__(8) uint64_t bars[kBulkBufs];
+  __shared__ int s_first[kMaxRanks + 1];
+  __shared__ int s_base[kMaxRanks];
+  const int lane = threadIdx.x;
+  pdl_trigger();
+  if (lane == 0) {
+    for (int b = 0; b < kBulkBufs; ++b) bulk_bar_init(smem_addr32(&bars[b]));
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  pdl_wait();
+  if (lane <= world) s_first[lane] = seg_offsets[lane * el];
+  if (lane < world) s_base[lane] = meta[lane];
+  __syncwarp();
+  const int64_t n_chunks = (n_tokens + tokens_per_chunk - 1) / tokens_per_chunk;
+  const int64_t mine = n_chunks > blockIdx.x ? (n_chunks - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+  const uint32_t buf0 = smem_addr32(bulk_bufs);
+  for (int64_t j = 0; j < mine + kBulkLag; ++j) {
+    if (j < mine) {
+      if (j >= kBulkBufs) bulk_wait_read_1();  // the stores that read this buffer are done with it
+      __syncwarp();
+      if (lane == 0) {
+        const int64_t tok0 = (blockIdx.x + j * gridDim.x) * tokens_per_chunk;
+        const int64_t left = n_tokens - tok0;
+        const uint32_t n = static_cast<uint32_t>(left < tokens_per_chunk ? left : tokens_per_chunk);
+        const int b = static_cast<int>(j % kBulkBufs);
+        bulk_load(buf0 + b * kBulkBufBytes, x + tok0 * row_bytes, n * row_bytes, smem_addr32(&bars[b]));
+      }
+    }
+    const int64_t k = j - kBulkLag;
+    if (k >= 0) {
+      const int b = static_cast<int>(k % kBulkBufs);
+      // the same verdict in every lane, so that the warp leaves the loop together
+      if (!__all_sync(0xffffffffu, bulk_bar_wait(smem_addr32(&bars[b]), static_cast<uint32_t>((k / kBulkBufs) & 1)))) {
+        if (status != nullptr) atomicCAS(status, 0u, DICE_STATUS_WAIT_SMEM_FULL);
+        break;
+      }
+      const int64_t tok0 = (blockIdx.x + k * gridDim.x) * tokens_per_chunk;
+      const int64_t left = n_tokens - tok0;
+      const int n = static_cast<int>(left < tokens_per_chunk ? left : tokens_per_chunk);
+      if (lane < n * K) {
+        const int ti = lane / K;
+        const int p = pos[(tok0 + ti) * K + (lane - ti * K)];
+        if (p >= 0) {
+          int d = 0;
+          while (d + 1 < world && p >= s_first[d + 1]) ++d;
+          const int row = s_base[d] + (p - s_first[d]);
+          if (row < capacity_rows)
+            bulk_store(static_cast<uint8_t*>(recv_bufs.ptr[d]) + static_cast<int64_t>(row) * row_bytes,
+                       buf0 + b * kBulkBufBytes + ti * row_bytes, row_bytes);
+          else if (status != nullptr)
+            atomicCAS(status, 0u, DICE_STATUS_EXCHANGE_OVERFLOW);
+        }
+      }
+      bulk_commit();
+    }
+  }
+  bulk_drain();
+  signal_when_grid_done(done_counter, flags, rank, world, seq);
+}
+
+__global__ void __launch_bounds__(32)
+ep_return_bulk_kernel(const uint8_t* __restrict__ rows, const int* __restrict__ meta, PeerTable back_bufs, PeerTable flags,
+                      unsigned int* done_counter, uint32_t row_bytes, int rows_per_chunk, int rank, int world,
+                      int back_capacity_rows, uint32_t seq, uint32_t* status) {
+  extern __shared__ __align__(128) uint8_t bulk_bufs[];
+  __shared__ __align__(8) uint64_t bars[kBulkBufs];
+  __shared__ int s_src_off[kMaxRanks + 1];
+  __shared__ int s_back[kMaxRanks];
+  __shared__ int s_chunk0[kMaxRanks + 1];  // chunks before source s
+  const int lane = threadIdx.x;
+  pdl_trigger();
+  if (lane == 0) {
+    for (int b = 0; b < kBulkBufs; ++b) bulk_bar_init(smem_addr32(&bars[b]));
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  pdl_wait();
+  if (lane <= world) s_src_off[lane] = meta[2 * world + lane];
+  if (lane < world) s_back[lane] = meta[world + lane];
+  __syncwarp();
+  if (lane == 0) {
+    int run = 0;
+    for (int s = 0; s < world; ++s) {
+      s_chunk0[s] = run;
+      const int n = s_src_off[s + 1] - s_src_off[s];
+      run += n > 0 ? (n + rows_per_chunk - 1) / rows_per_chunk : 0;
+    }
+    s_chunk0[world] = run;
+  }
+  __syncwarp();
+  const int64_t n_chunks = s_chunk0[world];
+  const int64_t mine = n_chunks > blockIdx.x ? (n_chunks - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+  const uint32_t buf0 = smem_addr32(bulk_bufs);
+  // a chunk: `n` rows of source `s` starting at received row `r0`
+  auto locate = [&](int64_t j, int& s, int& r0, int& n) {
+    const int c = static_cast<int>(blockIdx.x + j * gridDim.x);
+    s = 0;
+    while (s + 1 < world && c >= s_chunk0[s + 1]) ++s;
+    r0 = s_src_off[s] + (c - s_chunk0[s]) * rows_per_chunk;
+    n = s_src_off[s + 1] - r0;
+    if (n > rows_per_chunk) n = rows_per_chunk;
+  };
+  if (lane == 0) {  // the whole pipeline is one lane's: one load and one store per chunk
+    bool alive = true;
+    for (int64_t j = 0; alive && j < mine + kBulkLag; ++j) {
+      if (j < mine) {
+        if (j >= kBulkBufs) bulk_wait_read_1();
+        int s, r0, n;
+        locate(j, s, r0, n);
+        const int b = static_cast<int>(j % kBulkBufs);
+        bulk_load(buf0 + b * kBulkBufBytes, rows + static_cast<int64_t>(r0) * row_bytes, static_cast<uint32_t>(n) * row_bytes,
+                  smem_addr32(&bars[b]));
+      }
+      const int64_t k = j - kBulkLag;
+      if (k >= 0) {
+        const int b = static_cast<int>(k % kBulkBufs);
+        if (!bulk_bar_wait(smem_addr32(&bars[b]), static_cast<uint32_t>((k / kBulkBufs) & 1))) {
+          if (status != nullptr) atomicCAS(status, 0u, DICE_STATUS_WAIT_SMEM_FULL);
+          alive = false;
+          break;
+        }
+        int s, r0, n;
+        locate(k, s, r0, n);
+        const int row = s_back[s] + (r0 - s_src_off[s]);
+        if (row + n > back_capacity_rows) {
+          if (status != nullptr) atomicCAS(status, 0u, DICE_STATUS_EXCHANGE_OVERFLOW);
+          n = back_capacity_rows > row ? back_capacity_rows - row : 0;
+        }
+        if (n > 0)
+          bulk_store(static_cast<uint8_t*>(back_bufs.ptr[s]) + static_cast<int64_t>(row) * row_bytes, buf0 + b * kBulkBufBytes,
+                     static_cast<uint32_t>(n) * row_bytes);
+        bulk_commit();
+      }
+    }
+    bulk_drain();
+  }
+  __syncwarp();
+  signal_when_grid_done(done_counter, flags, rank, world, seq);
+}
+
+// DICE_EP_P2P_BULK=0 keeps the SIMT pushes everywhere
+bool bulk_pushes() {
+  static int cached = -1;
+  if (cached < 0) {
+    const char* e = getenv("DICE_EP_P2P_BULK");
+    cached = (e != nullptr && e[0] == '0') ? 0 : 1;
+  }
+  return cached != 0;
+}
+
+int sm_count_here() {
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
+template <typename Kern>
+int bulk_smem_ready(Kern kernel) {
+  return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kBulkBufs * kBulkBufBytes) ==
+                 cudaSuccess
+             ? DICE_OK
+             : DICE_ERR_CUDA;
+}
+
 int fill_table(PeerTable* t, const void* const* ptrs, int world) {
   if (ptrs == nullptr || world < 1 || world > kMaxRanks) return DICE_ERR_ARG;
   for (int i = 0; i < kMaxRanks; ++i) t->ptr[i] = i < world ? const_cast<void*>(ptrs[i]) : nullptr;
@@ -293,12 +523,35 @@ extern "C" int dice_ep_dispatch_rows(const void* x, const int32_t* pos, const in
   rc = fill_table(&f, peer_flags, world);
   if (rc != DICE_OK) return rc;
   const int row_vec = static_cast<int>(hidden * es / 16);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int el = n_experts / world;
+  const size_t row_bytes = hidden * es;
+  if (max_ctas == 0 && bulk_pushes() && row_bytes <= kBulkBufBytes && n_tokens > 0) {
+    // the push has the GPU to itself: move the rows with the copy unit
+    const int sms = sm_count_here();
+    if (sms <= 0) return DICE_ERR_CUDA;
+    int tpc = static_cast<int>(kBulkBufBytes / row_bytes);
+    if (tpc > 32 / k) tpc = 32 / k;
+    const int64_t chunks = (n_tokens + tpc - 1) / tpc;
+    const dim3 grid(static_cast<unsigned>(chunks < sms ? chunks : sms));
+    const uint8_t* xb = static_cast<const uint8_t*>(x);
+    if (k == 2) {
+      DICE_CHECK_ARG(bulk_smem_ready(ep_dispatch_bulk_kernel<2>) == DICE_OK, DICE_ERR_CUDA);
+      DICE_CUDA_OK(dice_launch(ep_dispatch_bulk_kernel<2>, grid, dim3(32), kBulkBufs * kBulkBufBytes, s, xb, pos, seg_offsets,
+                               meta, r, f, done_counter, n_tokens, static_cast<uint32_t>(row_bytes), tpc, rank, world, el,
+                               capacity_rows, seq, status));
+    } else {
+      DICE_CHECK_ARG(bulk_smem_ready(ep_dispatch_bulk_kernel<1>) == DICE_OK, DICE_ERR_CUDA);
+      DICE_CUDA_OK(dice_launch(ep_dispatch_bulk_kernel<1>, grid, dim3(32), kBulkBufs * kBulkBufBytes, s, xb, pos, seg_offsets,
+                               meta, r, f, done_counter, n_tokens, static_cast<uint32_t>(row_bytes), tpc, rank, world, el,
+                               capacity_rows, seq, status));
+    }
+    return DICE_OK;
+  }
   int64_t blocks = (n_tokens + 7) / 8;
   if (blocks < 1) blocks = 1;  // the flags are raised even when this rank has nothing to send
   if (max_ctas > 0 && blocks > max_ctas) blocks = max_ctas;  // a small grid leaves the SMs to a concurrent GEMM
   DICE_CHECK_ARG(blocks <= 0x7fffffffLL, DICE_ERR_LIMIT);
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const int el = n_experts / world;
   const dim3 grid(static_cast<unsigned>(blocks));
   if (k == 2)
     DICE_CUDA_OK(dice_launch(ep_dispatch_kernel<2>, grid, dim3(256), 0, s, static_cast<const uint4*>(x), pos, seg_offsets,
@@ -333,6 +586,19 @@ extern "C" int dice_ep_return_rows(const void* rows, const int32_t* meta, const 
   rc = fill_table(&f, peer_flags, world);
   if (rc != DICE_OK) return rc;
   const int row_vec = static_cast<int>(hidden * es / 16);
+  const size_t row_bytes = hidden * es;
+  if (max_ctas == 0 && bulk_pushes() && row_bytes <= kBulkBufBytes && max_rows > 0) {
+    const int sms = sm_count_here();
+    if (sms <= 0) return DICE_ERR_CUDA;
+    const int rpc = static_cast<int>(kBulkBufBytes / row_bytes);
+    const int64_t chunks = (static_cast<int64_t>(max_rows) + rpc - 1) / rpc + world;
+    DICE_CHECK_ARG(bulk_smem_ready(ep_return_bulk_kernel) == DICE_OK, DICE_ERR_CUDA);
+    DICE_CUDA_OK(dice_launch(ep_return_bulk_kernel, dim3(static_cast<unsigned>(chunks < sms ? chunks : sms)), dim3(32),
+                             kBulkBufs * kBulkBufBytes, static_cast<cudaStream_t>(stream),
+                             static_cast<const uint8_t*>(rows), meta, b, f, done_counter, static_cast<uint32_t>(row_bytes), rpc,
+                             rank, world, back_capacity_rows, seq, status));
+    return DICE_OK;
+  }
   int64_t blocks = (static_cast<int64_t>(max_rows) + 7) / 8;
   if (blocks < 1) blocks = 1;
   if (blocks > 148 * 16) blocks = 148 * 16;  // grid-stride over the rows actually received

@@ -201,7 +201,8 @@ def _peer_push(info, async_op, dispatch=None, rows_back=None):
 
     x = info.xchg
     lib, tab, slot = x.lib, info.tab, info.slot
-    side_ctas = p2p.side_push_ctas() if async_op else 0
+    # 0: the push owns the GPU (bulk-copy kernels); asynchronous pushes run next to the expert FFN: SIMT kernels
+    side_ctas = (p2p.side_push_ctas() or -1) if async_op else 0
     if async_op:
         stream = x.fork_to_comm()  # the push runs on the side stream, after what the current stream has produced
         # the caching allocator must not hand these to someone else before the side stream has read them

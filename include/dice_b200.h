@@ -234,8 +234,11 @@ DICE_API int dice_grouped_ffn_f32(const void* rows_in, int64_t n_rows, int hidde
  *   ready for dice_grouped_ffn with seg_slab[s*El+i] = i) | total, overflow;
  *   seq: a number that grows with every use of the same buffers;
  *   done_counter: device uint32, zero before first use, one per call site;
- *   max_ctas: upper bound of the grid of a push (0 = as many as there are
- *   rows): a push that runs next to a GEMM on another stream should be small.
+ *   max_ctas: 0 = the push has the GPU to itself: rows move through shared
+ *   memory with the copy unit (cp.async.bulk), one warp per SM; > 0 = SIMT push
+ *   with at most that many CTAs, < 0 = SIMT push sized by the rows: a push that
+ *   runs next to a GEMM on another stream needs the SIMT form (no shared
+ *   memory, fits beside the GEMM's CTAs) and should be small.
  */
 DICE_API int dice_ep_meta_ints(int world, int n_local_experts);
 DICE_API int dice_ep_exchange_counts(const int32_t* seg_offsets, const void* const* peer_matrices,

@@ -373,6 +373,68 @@ def test_exchange_world_of_one(cuda_device):
         ops.check_status(status)
 
 
+
+@pytest.mark.parametrize("n,h,k,dtype", [(777, 256, 2, torch.bfloat16), (1000, 1152, 2, torch.bfloat16),
+                                         (333, 1152, 2, torch.float32), (129, 1792, 1, torch.bfloat16),
+                                         (5, 64, 2, torch.bfloat16), (4097, 1152, 2, torch.bfloat16)])
+def test_exchange_bulk_copy_pushes_equal_simt_pushes(cuda_device, n, h, k, dtype):
+    """Dispatch and return exist twice: SIMT kernels (max_ctas != 0) and kernels that move the rows with
+    cp.async.bulk through shared memory (max_ctas == 0).  World of one rank, a tenth of the rows left out
+    (expert -1, as conditional communication does): both forms must write the same bytes and touch nothing else."""
+    import ctypes
+
+    from dice_b200 import _lib
+
+    ops = _ops()
+    lib = _lib.load()
+    e = 8
+    g = torch.Generator().manual_seed(n + h)
+    x = torch.randn(n, h, generator=g).to(dtype).to(cuda_device)
+    flat = torch.randint(0, e, (k * n,), generator=g)
+    flat[torch.rand(k * n, generator=g) < 0.1] = -1
+    flat = flat.to(cuda_device)
+    pos, seg, _ = ops.permute_plan(flat, e)
+    rows = int(seg[-1].item())
+    cap = rows + 3
+    code = 0 if dtype == torch.bfloat16 else 1
+    st = torch.cuda.current_stream().cuda_stream
+    tab = lambda p: (ctypes.c_void_p * 1)(p)
+    outs = []
+    for max_ctas in (0, -1):
+        ctrl = torch.zeros(e + 3 * 64, dtype=torch.int32, device=cuda_device)
+        recv = torch.full((cap, h), 3.0, dtype=dtype, device=cuda_device)
+        back = torch.full((cap, h), 5.0, dtype=dtype, device=cuda_device)
+        meta = torch.zeros(lib.dice_ep_meta_ints(1, e), dtype=torch.int32, device=cuda_device)
+        done = torch.zeros(2, dtype=torch.int32, device=cuda_device)
+        status = torch.zeros(1, dtype=torch.int32, device=cuda_device)
+        f = lambda i: ctrl.data_ptr() + (e + 64 * i) * 4
+        for seq in (1, 2):
+            assert lib.dice_ep_exchange_counts(seg.data_ptr(), tab(ctrl.data_ptr()), tab(f(0)), meta.data_ptr(), 0, 1, e,
+                                               cap, seq, status.data_ptr(), st) == 0
+            assert lib.dice_ep_dispatch_rows(x.data_ptr(), pos.data_ptr(), seg.data_ptr(), meta.data_ptr(),
+                                             tab(recv.data_ptr()), tab(f(1)), done.data_ptr(), n, k, h, code, 0, 1, e, cap,
+                                             seq, max_ctas, status.data_ptr(), st) == 0
+            assert lib.dice_ep_wait_flags(f(1), 1, seq, 0, status.data_ptr(), st) == 0
+            assert lib.dice_ep_return_rows(recv.data_ptr(), meta.data_ptr(), tab(back.data_ptr()), tab(f(2)),
+                                           done[1:].data_ptr(), h, code, 0, 1, cap, cap, seq, max_ctas, status.data_ptr(),
+                                           st) == 0
+            assert lib.dice_ep_wait_flags(f(2), 1, seq, 1, status.data_ptr(), st) == 0
+        torch.cuda.synchronize()
+        ops.check_status(status)
+        outs.append((recv.clone(), back.clone()))
+    (recv_bulk, back_bulk), (recv_simt, back_simt) = outs
+    assert torch.equal(recv_bulk, recv_simt) and torch.equal(back_bulk, back_simt)
+    assert bool((recv_bulk[rows:] == 3.0).all()) and bool((back_bulk[rows:] == 5.0).all())
+    # and the rows are the permutation of x: row r of the receive order is the token whose slot has pos == r
+    p = pos.cpu().view(n, k)
+    t_of = torch.full((rows,), -1, dtype=torch.long)
+    for s in range(k):
+        m = p[:, s] >= 0
+        t_of[p[m, s].long()] = torch.nonzero(m).flatten()
+    assert bool((t_of >= 0).all())
+    assert torch.equal(recv_bulk[:rows].cpu(), x.cpu()[t_of])
+
+
 def test_ffn_with_fused_return_world_of_one(cuda_device):
     """dice_grouped_ffn_return on one GPU: the rows the second GEMM sends "home"
     land where the separate return kernel would put them and equal the plain
