@@ -435,6 +435,78 @@ def test_exchange_bulk_copy_pushes_equal_simt_pushes(cuda_device, n, h, k, dtype
     assert torch.equal(recv_bulk[:rows].cpu(), x.cpu()[t_of])
 
 
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+@pytest.mark.parametrize("max_ctas", [0, -1])
+def test_exchange_of_emulated_ranks_on_one_gpu(cuda_device, world, max_ctas):
+    """The whole exchange for `world` ranks whose buffers all live on this GPU.  The count matrices and count
+    flags are filled in beforehand and every push is launched before the first wait, so no kernel ever waits
+    for a later one.  With the identity as expert FFN, every rank must get back exactly its own key-sorted
+    rows, and every receive buffer must hold its sources' rows in (source, slot) order.  max_ctas 0: bulk-copy
+    pushes, -1: SIMT pushes."""
+    import ctypes
+
+    from dice_b200 import _lib
+
+    ops = _ops()
+    lib = _lib.load()
+    e, h, k = 8, 256, 2
+    el = e // world
+    n = [300 + 37 * r for r in range(world)]  # tokens per rank (ragged)
+    g = torch.Generator().manual_seed(world)
+    xs, poss, segs, sorted_rows = [], [], [], []
+    for r in range(world):
+        x = torch.randn(n[r], h, generator=g).bfloat16().to(cuda_device)
+        expert = torch.randint(0, e, (k * n[r],), generator=g)
+        key = (expert % world) * el + expert // world  # (owner rank, local slot) of a round-robin expert
+        pos, seg, _ = ops.permute_plan(key.to(cuda_device), e)
+        xs.append(x); poss.append(pos); segs.append(seg); sorted_rows.append(ops.permute_rows(x, pos, k))
+    seg_host = [s.cpu().tolist() for s in segs]
+    recv_rows = [sum(seg_host[s][(d + 1) * el] - seg_host[s][d * el] for s in range(world)) for d in range(world)]
+    cap = max(recv_rows) + 7
+    flag_base = world * e
+    ctrl = [torch.zeros(flag_base + 3 * 64, dtype=torch.int32, device=cuda_device) for _ in range(world)]
+    recv = [torch.full((cap, h), 3.0, dtype=torch.bfloat16, device=cuda_device) for _ in range(world)]
+    back_cap = k * max(n) + 2  # every rank offers the same return capacity
+    back = [torch.full((back_cap, h), 5.0, dtype=torch.bfloat16, device=cuda_device) for _ in range(world)]
+    meta = [torch.zeros(lib.dice_ep_meta_ints(world, el), dtype=torch.int32, device=cuda_device) for _ in range(world)]
+    done = [torch.zeros(2, dtype=torch.int32, device=cuda_device) for _ in range(world)]
+    status = torch.zeros(1, dtype=torch.int32, device=cuda_device)
+    st = torch.cuda.current_stream().cuda_stream
+    table = lambda ptrs: (ctypes.c_void_p * world)(*ptrs)
+    flags = lambda which: table([c.data_ptr() + (flag_base + 64 * which) * 4 for c in ctrl])
+    my_flags = lambda r, which: ctrl[r].data_ptr() + (flag_base + 64 * which) * 4
+    seq = 1
+    counts = torch.tensor([[seg_host[r][i + 1] - seg_host[r][i] for i in range(e)] for r in range(world)], dtype=torch.int32)
+    for d in range(world):  # what every rank's count kernel will publish, and the flags that say so
+        ctrl[d][:flag_base] = counts.flatten().to(cuda_device)
+        ctrl[d][flag_base:flag_base + world] = seq
+    for r in range(world):
+        assert lib.dice_ep_exchange_counts(segs[r].data_ptr(), table([c.data_ptr() for c in ctrl]), flags(0),
+                                           meta[r].data_ptr(), r, world, e, cap, seq, status.data_ptr(), st) == 0
+    for r in range(world):
+        assert lib.dice_ep_dispatch_rows(xs[r].data_ptr(), poss[r].data_ptr(), segs[r].data_ptr(), meta[r].data_ptr(),
+                                         table([t.data_ptr() for t in recv]), flags(1), done[r].data_ptr(), n[r], k, h, 0,
+                                         r, world, e, cap, seq, max_ctas, status.data_ptr(), st) == 0
+    for r in range(world):
+        assert lib.dice_ep_wait_flags(my_flags(r, 1), world, seq, 0, status.data_ptr(), st) == 0
+    for r in range(world):  # identity FFN: the received rows go straight back
+        assert lib.dice_ep_return_rows(recv[r].data_ptr(), meta[r].data_ptr(), table([t.data_ptr() for t in back]), flags(2),
+                                       done[r][1:].data_ptr(), h, 0, r, world, back_cap, cap, seq, max_ctas,
+                                       status.data_ptr(), st) == 0
+    for r in range(world):
+        assert lib.dice_ep_wait_flags(my_flags(r, 2), world, seq, 1, status.data_ptr(), st) == 0
+    torch.cuda.synchronize()
+    ops.check_status(status)
+    for r in range(world):
+        assert torch.equal(back[r][: k * n[r]], sorted_rows[r]), f"rank {r} did not get its rows back"
+        assert bool((back[r][k * n[r]:] == 5.0).all())
+    for d in range(world):
+        want = torch.cat([sorted_rows[s][seg_host[s][d * el]: seg_host[s][(d + 1) * el]] for s in range(world)])
+        assert torch.equal(recv[d][: recv_rows[d]], want), f"receive buffer of rank {d}"
+        assert bool((recv[d][recv_rows[d]:] == 3.0).all())
+
+
 def test_ffn_with_fused_return_world_of_one(cuda_device):
     """dice_grouped_ffn_return on one GPU: the rows the second GEMM sends "home"
     land where the separate return kernel would put them and equal the plain
