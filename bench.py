@@ -23,6 +23,16 @@ reference computes it (SwiGLU experts, un-normalised weights, shared expert).
 
 ``--impl reference`` times the CPU restatement of the reference path (the
 oracle) on the host cores, on a bounded sample of the same workload.
+
+Beyond the contract's keys the line carries: ``roofline`` (grouped GEMM, from
+CUDA events around the FFN launches inside the timed region), ``roofline_hbm``
+(router, row gather and combine kernels timed on per-layer inputs, against the
+measured copy bandwidth), ``gpu_reference`` (the reference's algorithm in stock
+PyTorch CUDA operations on the same GPUs: a comparator, not the product),
+``variants`` (N = 1: the reference-true SwiGLU block next to the GELU-tanh
+one), ``ep_parity`` and ``load`` (N > 1: the expert-parallel layer 0 against an
+unsharded block with the same weights on the rank's own tokens; rows per rank
+and per expert), ``phases_us_per_layer`` (N > 1) and ``host_us_per_layer``.
 """
 from __future__ import annotations
 
@@ -75,6 +85,16 @@ def parse_args():
                     help="after the timed runs, time the phases of the block (router, count exchange, dispatch, expert "
                          "FFN, combine ...) with CUDA events on a few more steps and add them to the JSON line")
     ap.add_argument("--skip", action="store_true", help="conditional communication: noskip step 2, 'low' strategy")
+    ap.add_argument("--route", default="router",
+                    help="router (Gaussian activations through the block's own router: near-uniform load) or "
+                         "zipf:S[:T]: one constant input channel and a per-expert router bias log(p_e)/T with "
+                         "p_e ~ 1/rank^S over a seeded permutation of the experts, so that the logits are "
+                         "N(0,1) + log(p_e)/T and the expert load is skewed")
+    ap.add_argument("--sync-steps", type=int, default=0,
+                    help="asynchronous modes: the first S of the timed steps are forced-synchronous steps "
+                         "(the warm-up steps of diffusion/warmup.py:11-20)")
+    ap.add_argument("--no-gpu-reference", action="store_true", help="skip the stock-PyTorch comparator on the GPU")
+    ap.add_argument("--no-variants", action="store_true", help="N = 1: skip the SwiGLU block next to the GELU-tanh one")
     return ap.parse_args()
 
 
@@ -165,18 +185,49 @@ class ClockSampler:
 # --------------------------------------------------------------------------- #
 
 
-def build_blocks(layers, variant, para_mode, device, seed=0):
+def _param_seed(seed, layer, name):
+    import zlib
+
+    return (seed * 1000003 + layer * 7919 + zlib.crc32(name.encode())) % (2 ** 31 - 1)
+
+
+def zipf_route(spec):
+    """(s, temperature) of ``--route zipf:S[:T]``, or None."""
+    if spec == "router":
+        return None
+    parts = spec.split(":")
+    if parts[0] != "zipf" or len(parts) not in (2, 3):
+        raise SystemExit(f"--route {spec}: expected router or zipf:S[:T]")
+    return float(parts[1]), float(parts[2]) if len(parts) == 3 else 1.0
+
+
+ZIPF_CHANNEL_VALUE = 4.0  # the constant input channel that carries the router bias
+
+
+def build_blocks(layers, variant, para_mode, device, seed=0, route=None, only_layer=None):
+    """One block per layer.  Every parameter is drawn from its own seed (layer, parameter name), so that a
+    rank's trimmed expert-parallel block and an unsharded block hold the same values for the same expert."""
     from dice_b200.moe_block import SparseMoeBlock
 
     blocks = []
-    gen = torch.Generator(device=device).manual_seed(seed)
-    for layer in range(layers):
+    gen = torch.Generator(device=device)
+    for layer in (range(layers) if only_layer is None else [only_layer]):
         with torch.device(device):
             blk = SparseMoeBlock(HIDDEN, MLP_RATIO, EXPERTS, 2, pretraining_tp=1, layer_idx=layer, total_layers=layers,
                                  para_mode=para_mode, expert_act=variant, shared_expert=(variant == "swiglu"))
         blk = blk.to(torch.bfloat16).eval()
-        for p in blk.parameters():
+        for name, p in blk.named_parameters():
+            gen.manual_seed(_param_seed(seed, layer, name))
             p.data.normal_(0.0, 0.02, generator=gen)
+        if route is not None:
+            # logits = N(0, 1) (unit-norm rows against N(0,1) activations) + log(p_e) / T through channel 0
+            s_exp, temp = route
+            gen.manual_seed(_param_seed(seed, layer, "zipf"))
+            w = torch.randn(EXPERTS, HIDDEN, generator=gen, device=device) / (HIDDEN - 1) ** 0.5
+            perm = torch.randperm(EXPERTS, generator=gen, device=device)
+            p_e = 1.0 / (perm.float() + 1.0) ** s_exp
+            w[:, 0] = torch.log(p_e / p_e.sum()) / temp / ZIPF_CHANNEL_VALUE
+            blk.gate.weight.data.copy_(w)
         blk.gate.norm_topk_prob = variant == "gelu_tanh"
         blocks.append(blk)
     return blocks
@@ -251,22 +302,88 @@ def phase_times(step_fn, layers, steps=3):
     return out
 
 
-def kernels_per_block(variant, ep):
-    # router, 3 plan kernels, row gather, 2 grouped GEMMs, combine (+ 2 GEMMs of the shared expert)
-    n = 1 + 3 + 1 + 2 + 1
-    if variant == "swiglu":
-        n += 2
-    if ep:
-        # peer-memory exchange: counts, dispatch (replaces the row gather), 2 flag waits, return
-        n += 4
-    return n
-
-
 def ffn_flops(tokens, variant):
     """Algorithmic FLOPs of one grouped-GEMM launch pair (routed experts only): 2 rows per token."""
     rows = 2 * tokens
     per_row = (6 if variant == "swiglu" else 4) * HIDDEN * MLP_RATIO * HIDDEN
     return rows * per_row
+
+
+def hbm_rooflines(blocks, xs, peak_gbs, reps=3):
+    """The HBM-bound kernels of the block, each timed alone with CUDA events over all layers' inputs (one
+    distinct 37.7 MB input per layer: the working set between two uses of a buffer exceeds the 126 MB L2),
+    against their algorithmic bytes: router N*h*2 + E*h*2 + 24 N + 4 E; row gather and combine N*h*2 + R*h*2 +
+    4 R (+ 8 N of gate weights for the combine)."""
+    from dice_b200 import ops
+
+    n, h, e = xs[0].shape[0] * xs[0].shape[1], xs[0].shape[2], EXPERTS
+    r = 2 * n
+    x2 = [x.view(-1, h) for x in xs]
+    gw = [b._gate_weight(torch.bfloat16) for b in blocks]
+    routed = [ops.router_top2(x, w) for x, w in zip(x2, gw)]
+    plans = [ops.permute_plan(idx.view(-1), e) for idx, _, _, _ in routed]
+    rows = [torch.empty((r, h), dtype=torch.bfloat16, device=xs[0].device) for _ in range(min(len(xs), 4))]
+    outs = [torch.empty((n, h), dtype=torch.bfloat16, device=xs[0].device) for _ in range(min(len(xs), 4))]
+
+    def timed(fn):
+        fn()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) * 1e-3 / (reps * len(xs))
+
+    def run_router():
+        for x, w in zip(x2, gw):
+            ops.router_top2(x, w)
+
+    def run_plan():
+        for idx, _, _, _ in routed:
+            ops.permute_plan(idx.view(-1), e)
+
+    def run_gather():
+        for i, (x, (pos, _, _)) in enumerate(zip(x2, plans)):
+            ops.permute_rows(x, pos, 2, out=rows[i % len(rows)])
+
+    def run_combine():
+        for i, ((_, w, _, _), (pos, _, _)) in enumerate(zip(routed, plans)):
+            src = rows[i % len(rows)]
+            ops.unpermute_combine(src, pos[0::2], src, pos[1::2], w[:, 0], w[:, 1], n, out=outs[i % len(outs)])
+
+    run_gather()
+    bytes_of = {"router": n * h * 2 + e * h * 2 + 24 * n + 4 * e, "row_gather": n * h * 2 + r * h * 2 + 4 * r,
+                "combine": n * h * 2 + r * h * 2 + 4 * r + 8 * n}
+    out = {}
+    for name, fn in (("router", run_router), ("row_gather", run_gather), ("combine", run_combine)):
+        t = timed(fn)
+        gbs = bytes_of[name] / t / 1e9
+        out[name] = {"us": round(t * 1e6, 2), "bytes": bytes_of[name], "achieved": round(gbs, 1), "peak": peak_gbs,
+                     "unit": "GB/s", "frac": round(gbs / peak_gbs, 4)}
+    out["permute_plan"] = {"us": round(timed(run_plan) * 1e6, 2), "note": "3 launches on 4-byte indices: latency-bound"}
+    return out
+
+
+def gpu_reference(blocks, xs, ep, budget_steps=2):
+    """The reference's algorithm in stock PyTorch CUDA operations (bench_torch_reference.py) on the same blocks
+    and inputs: tokens/s of this rank, a comparator only."""
+    import bench_torch_reference as R
+
+    fwd = R.block_forward_ep if ep else R.block_forward
+    n_layers = min(len(blocks), 4)
+    for blk, x in zip(blocks[:2], xs[:2]):
+        fwd(blk, x)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(budget_steps):
+        for blk, x in zip(blocks[:n_layers], xs[:n_layers]):
+            fwd(blk, x)
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) * 1e-3 / (budget_steps * n_layers), n_layers
 
 
 # --------------------------------------------------------------------------- #
@@ -277,8 +394,10 @@ def ffn_flops(tokens, variant):
 def run_ours(args):
     import torch.distributed as dist
 
+    from dice_b200 import _lib, ops
     from dice_b200.moe_block import ExpertPack, ParaMode
 
+    lib = _lib.load()
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -292,30 +411,37 @@ def run_ours(args):
         dist.init_process_group("nccl", device_id=device)
     tokens, wl_name = workload(world, args.shape)
     is_async = ep and args.ep_mode != "sync"
+    route = zipf_route(args.route)
     para_mode = ParaMode(ep=ep, ep_async=is_async, ep_async_mode=args.ep_async_mode if is_async else None,
                          ep_async_warm_up=0, strided_sync=0, ep_async_cool_down=0)
-    blocks = build_blocks(args.layers, args.variant, para_mode, device)
+    blocks = build_blocks(args.layers, args.variant, para_mode, device, route=route)
     step_counter = [10 ** 6]
     if ep:
-        from dice_b200.expertpara import diep, ep_fwd
+        from dice_b200.expertpara import diep, ep_fwd, p2p
 
         diep.ep_cache_init(args.layers, auto_gc=args.auto_gc, noskip_step=2 if args.skip else 1,
                            skip_mode="low" if args.skip else None, async_pipeline=args.ep_mode == "interweaved",
                            selective_async_strategy=args.ep_async_mode if is_async else None)
         ep_fwd.use_latest_expert_weights(True)
-        from dice_b200.expertpara import p2p
-
         p2p.enable(not args.nccl_exchange)
         wl_name += f", {args.ep_mode} exchange" + (f" ({args.ep_async_mode} layers async)" if is_async else "") + (
             ", conditional communication" if args.skip else "")
+    if route is not None:
+        wl_name += f", router logits N(0,1) + Zipf(s={route[0]}) bias / T={route[1]}"
     gen = torch.Generator(device=device).manual_seed(1000 + rank)
+
+    def make_input(g=gen, dev=device):
+        x = torch.randn(tokens // TOKENS_PER_IMAGE, TOKENS_PER_IMAGE, HIDDEN, generator=g, device=dev).bfloat16()
+        if route is not None:
+            x[..., 0] = ZIPF_CHANNEL_VALUE
+        return x
+
     # one distinct input per layer: together with >150 MB of expert weights per layer the working set
     # between two uses of any buffer is far larger than the 126 MB L2
-    xs = [torch.randn(tokens // TOKENS_PER_IMAGE, TOKENS_PER_IMAGE, HIDDEN, generator=gen, device=device).bfloat16()
-          for _ in range(args.layers)]
-    host_in = torch.randn(tokens // TOKENS_PER_IMAGE, TOKENS_PER_IMAGE, HIDDEN).bfloat16().pin_memory()
-    host_out = torch.empty_like(host_in).pin_memory()
-    dev_in = torch.empty_like(xs[0])
+    xs = [make_input() for _ in range(args.layers)]
+    host_in = [make_input(torch.Generator().manual_seed(7 + i), "cpu").pin_memory() for i in range(2)]
+    host_out = [torch.empty_like(host_in[0]).pin_memory() for _ in range(2)]
+    dev_in = [torch.empty_like(xs[0]) for _ in range(2)]
 
     def begin_step(forced=False):
         # what the sampler does around each model call (rectified_flow.py:91-114)
@@ -327,6 +453,14 @@ def run_ours(args):
             diep.diep_force_sync()
             diep.ep_cache_clear()
 
+    def forced_step():
+        begin_step(forced=True)
+        y = None
+        for blk, x in zip(blocks, xs):
+            y = blk(x)
+        diep.diep_cancel_sync()
+        return y
+
     def step_device():
         begin_step()
         y = None
@@ -334,28 +468,66 @@ def run_ours(args):
             y = blk(x)
         return y
 
+    # end to end: every step copies its inputs from pinned host memory and its result back, double-buffered on
+    # two copy streams so that the copies of neighbouring steps run under the blocks of this one
+    main = torch.cuda.current_stream()
+    copy_in, copy_out = torch.cuda.Stream(), torch.cuda.Stream()
+    ev_in = [torch.cuda.Event() for _ in range(2)]
+    ev_free = [torch.cuda.Event() for _ in range(2)]
+    ev_done = [torch.cuda.Event() for _ in range(2)]
+    ev_out = [torch.cuda.Event() for _ in range(2)]
+    e2e_state = {"i": 0, "checksum": 0.0}
+
     def step_e2e():
+        i = e2e_state["i"]
+        b = i & 1
+        e2e_state["i"] = i + 1
         begin_step()
-        dev_in.copy_(host_in, non_blocking=True)
+        with torch.cuda.stream(copy_in):
+            if i >= 2:
+                copy_in.wait_event(ev_free[b])   # the blocks of step i-2 have read this buffer
+            dev_in[b].copy_(host_in[b], non_blocking=True)
+            ev_in[b].record(copy_in)
+        main.wait_event(ev_in[b])
         y = None
         for blk in blocks:
-            y = blk(dev_in)
-        host_out.copy_(y, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
+            y = blk(dev_in[b])
+        ev_free[b].record(main)
+        ev_done[b].record(main)
+        if i >= 2:
+            ev_out[b].synchronize()              # the host has the result of step i-2 before its buffer is reused
+            e2e_state["checksum"] += float(host_out[b][0, 0, 0])
+        with torch.cuda.stream(copy_out):
+            copy_out.wait_event(ev_done[b])
+            y.record_stream(copy_out)
+            host_out[b].copy_(y, non_blocking=True)
+            ev_out[b].record(copy_out)
+
+    def e2e_drain():
+        for b in range(2):
+            ev_out[b].synchronize()
+            e2e_state["checksum"] += float(host_out[b][0, 0, 0])
 
     def barrier():
         if ep:
             dist.barrier()
         torch.cuda.synchronize()
 
-    def timed(fn, steps, sampler=None):
+    sync_steps = args.sync_steps if is_async else 0
+
+    def timed(fn, steps, sampler=None, tail=None, sync_steps=0):
         barrier()
         if sampler is not None:
             sampler.start()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        for _ in range(steps):
-            fn()
+        for i in range(steps):
+            if i < sync_steps:
+                forced_step()
+            else:
+                fn()
+        if tail is not None:
+            tail()
         e1.record()
         barrier()
         clocks = sampler.stop() if sampler is not None else None
@@ -364,11 +536,38 @@ def run_ours(args):
             dist.all_reduce(ms, op=dist.ReduceOp.MAX)
         return float(ms.item()), clocks
 
-    if is_async:  # the first step of a sampling run is always synchronous and fills the caches
-        begin_step(forced=True)
-        for blk, x in zip(blocks, xs):
+    ep_parity = load = None
+    if ep:
+        # Layer 0 of the expert-parallel model against an unsharded block with the same weights on this rank's
+        # own tokens (a synchronous step, so the same step's results come back): multi-GPU correctness in the line.
+        single = build_blocks(args.layers, args.variant, ParaMode(), device, route=route, only_layer=0)[0]
+        if is_async:
+            begin_step(forced=True)
+        else:
+            begin_step()
+        y_ep = blocks[0](xs[0])
+        for blk, x in zip(blocks[1:], xs[1:]):
             blk(x)
-        diep.diep_cancel_sync()
+        if is_async:
+            diep.diep_cancel_sync()
+        y_one = single(xs[0])
+        idx_ep, w_ep, hist, _ = ops.router_top2(xs[0].view(-1, HIDDEN), blocks[0]._gate_weight(torch.bfloat16),
+                                                renorm=blocks[0].gate.norm_topk_prob)
+        idx_one, _, _, _ = ops.router_top2(xs[0].view(-1, HIDDEN), single._gate_weight(torch.bfloat16),
+                                           renorm=single.gate.norm_topk_prob)
+        rel = ((y_ep.float() - y_one.float()).norm() / y_one.float().norm()).reshape(1)
+        stats = torch.stack([rel[0], (idx_ep != idx_one).any().float(), (y_ep != y_one).any().float()])
+        dist.all_reduce(stats, op=dist.ReduceOp.MAX)
+        ep_parity = {"routing_equal": bool(stats[1].item() == 0), "max_rel_err": float(stats[0].item()),
+                     "bit_identical": bool(stats[2].item() == 0), "layer": 0,
+                     "against": "unsharded single-GPU block, same weights, this rank's tokens; max over ranks"}
+        hists = [torch.zeros_like(hist) for _ in range(world)]
+        dist.all_gather(hists, hist)
+        per_expert = torch.stack(hists).sum(0).float()
+        per_rank = per_expert.view(EXPERTS // world, world).sum(0)  # expert e lives on rank e mod W
+        load = {"rows_per_rank_max_over_mean": round(float(per_rank.max() / per_rank.mean()), 3),
+                "rows_per_expert_max_over_mean": round(float(per_expert.max() / per_expert.mean()), 3), "layer": 0}
+        del single, y_one
     for _ in range(max(args.warmup, 3)):
         step_device()
     # FFN launch durations, measured on the launching stream inside the timed region
@@ -376,7 +575,9 @@ def run_ours(args):
     # time one FFN call in five (5 does not divide the calls per step, so every layer gets its turn); the clocks of
     # this rank's GPU are sampled by rank 0 only: eight polling nvidia-smi processes slow every rank's launches down
     ExpertPack.timing_every = 5
-    total_ms, clocks = timed(step_device, args.steps, ClockSampler(local_rank) if rank == 0 else None)
+    launches0 = lib.dice_kernel_launches()
+    total_ms, clocks = timed(step_device, args.steps, ClockSampler(local_rank) if rank == 0 else None, sync_steps=sync_steps)
+    launches = lib.dice_kernel_launches() - launches0
     ffn_events = ExpertPack.timing
     ExpertPack.timing = None
     torch.cuda.synchronize()
@@ -384,16 +585,28 @@ def run_ours(args):
     for blk in blocks:
         blk.check_status()
     exchange = "nccl"
+    capacity = None
     if ep:
         if p2p._exchange is not None:
             p2p._exchange.check()
             exchange = "nvlink peer memory (own kernels)"
+            capacity = {"rows": p2p._exchange.capacity_rows, "lossless": p2p._exchange.lossless}
+
+    # host cost of enqueueing one layer: two steps right after a synchronisation, while the launch queue is short
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(2):
+        step_device()
+    host_us = (time.perf_counter() - t0) / (2 * args.layers) * 1e6
+    torch.cuda.synchronize()
 
     for _ in range(2):
         step_e2e()
-    e2e_ms, _ = timed(step_e2e, args.steps)
+    e2e_drain()
+    e2e_state["i"] = 0
+    e2e_ms, _ = timed(step_e2e, args.steps, tail=e2e_drain)
 
-    phases = phase_times(step_device, args.layers) if args.phases else None
+    phases = phase_times(step_device, args.layers) if (args.phases or ep) else None
     dit = None if args.no_full_model else full_model_step(blocks, tokens, device, begin_step, barrier, ep, steps=10)
 
     ms_per_step = total_ms / args.steps
@@ -410,12 +623,17 @@ def run_ours(args):
     achieved = flops_per_launch / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else 0.0
     roofline = {"kernel": "grouped_gemm_pair_kernel (tcgen05 cta_group::2, fc1+fc2 of the routed experts)", "bound": "tensor",
                 "achieved": round(achieved, 1), "peak": peak_tf, "unit": "TFLOP/s", "frac": round(achieved / peak_tf, 4),
-                "peak_source": f"bf16_tflops_sustained of {pk_src}", "avg_launch_ms": round(gemm_ms, 4),
+                "peak_source": f"bf16_tflops_sustained of {pk_src}", "frac_of_burst": round(
+                    achieved / pk.get("bf16_tflops", FALLBACK_PEAKS["bf16_tflops"]), 4), "avg_launch_ms": round(gemm_ms, 4),
                 "launches_timed": gemm_launches, "launches_in_region": 2 * args.layers * args.steps,
-                "flops_per_launch": flops_per_launch, "traffic": GEMM_TRAFFIC_BYTES if (world == 1 and args.variant == "gelu_tanh") else None}
+                "flops_per_launch": flops_per_launch,
+                "traffic": GEMM_TRAFFIC_BYTES if (world == 1 and args.variant == "gelu_tanh" and args.shape == "xl") else None,
+                "traffic_source": "ncu capture summarised in profiles/grouped_gemm_dit_xl2_moe_block.md"}
 
-    if args.skip:
-        roofline.update({"achieved": None, "frac": None, "note": "rows per launch vary with conditional communication"})
+    if args.skip or route is not None:
+        roofline.update({"achieved": None, "frac": None, "frac_of_burst": None,
+                         "note": "rows per launch vary (conditional communication / skewed routing)"})
+    roofline_hbm = hbm_rooflines(blocks, xs, pk.get("hbm_gbs", FALLBACK_PEAKS["hbm_gbs"]))
     line = {
         "metric": "moe_block_tokens_per_s", "value": round(value, 1), "unit": "tokens/s", "n_gpus": world,
         "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(ms_per_step, 4),
@@ -423,17 +641,52 @@ def run_ours(args):
         "config": {"workload": wl_name, "variant": args.variant, "layers_per_step": args.layers, "tokens_per_gpu": tokens,
                    "hidden": HIDDEN, "experts": EXPERTS, "top_k": 2, "ffn": MLP_RATIO * HIDDEN,
                    "parallelism": "ep%d" % world if ep else "single", "exchange": exchange if ep else None,
+                   "forced_sync_steps_in_region": sync_steps,
                    "l2": "per-layer inputs and weights (>150 MB per layer) exceed the 126 MB L2; no explicit flush"},
         "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "ms_per_step": round(e2e_ms / args.steps, 4),
-                "h2d_bytes_per_step": host_in.numel() * 2, "d2h_bytes_per_step": host_out.numel() * 2},
-        "gpu_launches": kernels_per_block(args.variant, ep) * args.layers * args.steps,
-        "clocks": clocks, "roofline": roofline,
-        "tokens_per_s_per_gpu": round(value / world, 1),
+                "h2d_bytes_per_step": host_in[0].numel() * 2, "d2h_bytes_per_step": host_out[0].numel() * 2,
+                "copies": "double-buffered on two copy streams; the host reads every step's result"},
+        "gpu_launches": int(launches),
+        "gpu_launches_note": "kernels the library launched inside the timed region on this rank (its own launch counter)",
+        "clocks": clocks, "roofline": roofline, "roofline_hbm": roofline_hbm,
+        "tokens_per_s_per_gpu": round(value / world, 1), "host_us_per_layer": round(host_us, 1),
     }
+    if ep_parity is not None:
+        line["ep_parity"] = ep_parity
+        line["load"] = load
+        line["receive_capacity"] = capacity
     if phases is not None:
         line["phases_us_per_layer"] = phases
     if dit is not None:
         line["dit_sampling_step"] = dit
+    if not args.no_gpu_reference:
+        t_ref, n_ref = gpu_reference(blocks, xs, ep)
+        ref_ms = torch.tensor([t_ref], device=device)
+        if ep:
+            dist.all_reduce(ref_ms, op=dist.ReduceOp.MAX)
+        ref_value = world * tokens / float(ref_ms.item())
+        line["gpu_reference"] = {
+            "value": round(ref_value, 1), "unit": "tokens/s", "us_per_block": round(float(ref_ms.item()) * 1e6, 1),
+            "kind": "port", "speedup": round(value / ref_value, 2),
+            "what": "the reference's algorithm in stock PyTorch CUDA ops (ATen, cuBLAS" + (", NCCL all_to_all_single per "
+                    "expert slot" if ep else "") + "; per-expert Python loop, host reads for split sizes) on the same GPUs, "
+                    f"bf16, same blocks and inputs, {n_ref} layers x 2 passes: bench_torch_reference.py"}
+    if world == 1 and not args.no_variants and args.variant == "gelu_tanh" and args.shape == "xl" and route is None:
+        sw_blocks = build_blocks(args.layers, "swiglu", para_mode, device)
+
+        def step_swiglu():
+            for blk, x in zip(sw_blocks, xs):
+                blk(x)
+
+        for _ in range(3):
+            step_swiglu()
+        sw_steps = max(5, args.steps // 2)
+        sw_ms, _ = timed(step_swiglu, sw_steps)
+        line["variants"] = {"swiglu": {
+            "value": round(tokens * args.layers / (sw_ms / sw_steps * 1e-3), 1), "unit": "tokens/s",
+            "ms_per_step": round(sw_ms / sw_steps, 4), "steps": sw_steps,
+            "what": "the block as the reference computes it: SwiGLU experts, un-normalised top-2 weights, shared expert"}}
+        del sw_blocks
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline(blocks, xs, args.variant, budget_s=12.0)
     if rank == 0:

@@ -16,6 +16,7 @@ SIGNATURES = {
     "dice_abi_version": (c_int, []),
     "dice_strerror": (c_char_p, [c_int]),
     "dice_status_message": (c_char_p, [c_uint32]),
+    "dice_kernel_launches": (ctypes.c_uint64, []),
     "dice_router_top2": (
         c_int,
         [c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
@@ -39,12 +40,12 @@ SIGNATURES = {
     "dice_grouped_gemm": (
         c_int,
         [c_void_p, c_int64, c_int, c_void_p, c_int, c_int64, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int64,
-         c_int, c_void_p, c_void_p],
+         c_int, c_int, c_void_p, c_void_p],
     ),
     "dice_grouped_ffn": (
         c_int,
         [c_void_p, c_int64, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p,
-         c_void_p, c_void_p, c_void_p],
+         c_void_p, c_int, c_void_p, c_void_p],
     ),
     "dice_grouped_ffn_f32": (
         c_int,
@@ -66,13 +67,13 @@ SIGNATURES = {
     "dice_grouped_ffn_return": (
         c_int,
         [c_void_p, c_int64, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
-         c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_uint32, c_void_p, c_void_p]),
+         c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_uint32, c_int, c_void_p, c_void_p]),
     "dice_ipc_export": (c_int, [c_void_p, c_void_p, c_void_p]),
     "dice_ipc_import": (c_int, [c_void_p, ctypes.c_uint64, c_void_p]),
     "dice_ipc_close": (c_int, [c_void_p, ctypes.c_uint64]),
 }
 
-ABI_VERSION = 1
+ABI_VERSION = 2
 _lib = None
 
 

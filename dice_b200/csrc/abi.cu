@@ -1,7 +1,13 @@
 // Version / error-text entry points of the C ABI.
 #include <stdlib.h>
 
+#include <atomic>
+
 #include "common.cuh"
+
+static std::atomic<uint64_t> g_kernel_launches{0};
+void dice_count_launch() { g_kernel_launches.fetch_add(1, std::memory_order_relaxed); }
+extern "C" uint64_t dice_kernel_launches(void) { return g_kernel_launches.load(std::memory_order_relaxed); }
 
 bool dice_pdl_enabled() {
   static int cached = -1;
@@ -40,6 +46,7 @@ extern "C" const char* dice_status_message(uint32_t status) {
     case DICE_STATUS_WAIT_PEER_DISPATCH: return "timed out waiting for a peer rank's dispatched rows";
     case DICE_STATUS_WAIT_PEER_COMBINE: return "timed out waiting for a peer rank's expert outputs";
     case DICE_STATUS_EXCHANGE_OVERFLOW: return "a rank received more rows than its exchange buffer holds";
+    case DICE_STATUS_PEER_FAILED: return "a peer rank reported that the rows it sent are incomplete";
     default: return "unknown device status";
   }
 }

@@ -27,6 +27,7 @@
 #define DICE_STATUS_WAIT_PEER_DISPATCH 7u  // exchange: a peer's dispatched rows never arrived
 #define DICE_STATUS_WAIT_PEER_COMBINE 8u   // exchange: a peer's expert outputs never arrived
 #define DICE_STATUS_EXCHANGE_OVERFLOW 9u   // exchange: more rows than the receive buffer holds
+#define DICE_STATUS_PEER_FAILED 10u        // exchange: a source rank marked its push as incomplete
 
 static inline bool dice_aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
@@ -44,6 +45,7 @@ __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;"
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 bool dice_pdl_enabled();  // abi.cu
+void dice_count_launch();  // abi.cu: every kernel launch of the library is counted (dice_kernel_launches)
 
 template <typename... KArgs, typename... Args>
 static inline cudaError_t dice_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
@@ -58,6 +60,7 @@ static inline cudaError_t dice_launch(void (*kernel)(KArgs...), dim3 grid, dim3 
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = dice_pdl_enabled() ? 1 : 0;
+  dice_count_launch();
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
@@ -101,5 +104,5 @@ struct DiceReturnSpec {
 };
 int dice_internal_gemm_pair(const void* a, int64_t n_rows, int k_dim, const void* w, int n_slabs, int64_t w_rows,
                             const int32_t* seg_offsets, const int32_t* seg_slab, int n_seg, int epilogue, void* out,
-                            int64_t ld_out, int n_out, uint32_t* status, cudaStream_t stream,
+                            int64_t ld_out, int n_out, int reserve_sms, uint32_t* status, cudaStream_t stream,
                             const DiceReturnSpec* ret = nullptr);

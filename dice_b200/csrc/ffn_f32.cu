@@ -122,6 +122,7 @@ int launch_f32(const void* a, int64_t n_rows, int k_dim, const void* w, int64_t 
   const int64_t gx = (n_rows + TM - 1) / TM + n_seg;
   const int gy = (n_out + TN - 1) / TN;
   if (gx > 0x7fffffffLL || gy > 65535) return DICE_ERR_LIMIT;
+  dice_count_launch();
   grouped_gemm_f32_kernel<EPI><<<dim3(static_cast<unsigned>(gx), gy), 256, 0, s>>>(
       static_cast<const float*>(a), static_cast<const float*>(w), seg_offsets, seg_slab, n_seg, k_dim, w_rows, n_out,
       static_cast<float*>(out), ld_out);

@@ -388,8 +388,8 @@ int sm_count() {
 
 extern "C" int dice_grouped_gemm(const void* a, int64_t n_rows, int k_dim, const void* w, int n_slabs, int64_t w_rows,
                                  const int32_t* seg_offsets, const int32_t* seg_slab, int n_seg, int epilogue,
-                                 void* out, int64_t ld_out, int n_out, uint32_t* status, void* stream) {
-  DICE_CHECK_ARG(n_rows >= 0 && k_dim > 0 && n_slabs > 0 && w_rows > 0 && n_seg >= 0, DICE_ERR_ARG);
+                                 void* out, int64_t ld_out, int n_out, int reserve_sms, uint32_t* status, void* stream) {
+  DICE_CHECK_ARG(n_rows >= 0 && k_dim > 0 && n_slabs > 0 && w_rows > 0 && n_seg >= 0 && reserve_sms >= 0, DICE_ERR_ARG);
   DICE_CHECK_ARG(n_seg <= kMaxSeg, DICE_ERR_LIMIT);
   DICE_CHECK_ARG(epilogue == DICE_EPI_STORE || epilogue == DICE_EPI_GELU_TANH || epilogue == DICE_EPI_SWIGLU,
                  DICE_ERR_ARG);
@@ -405,9 +405,10 @@ extern "C" int dice_grouped_gemm(const void* a, int64_t n_rows, int k_dim, const
 
   if (use_cta_pairs())
     return dice_internal_gemm_pair(a, n_rows, k_dim, w, n_slabs, w_rows, seg_offsets, seg_slab, n_seg, epilogue, out,
-                                   ld_out, n_out, status, static_cast<cudaStream_t>(stream));
-  const int sms = sm_count();
+                                   ld_out, n_out, reserve_sms, status, static_cast<cudaStream_t>(stream));
+  int sms = sm_count();
   if (sms <= 0) return DICE_ERR_CUDA;
+  sms = sms - reserve_sms > 1 ? sms - reserve_sms : 1;
   CUtensorMap tm_a, tm_b;
   int rc = encode_map(&tm_a, a, static_cast<uint64_t>(n_rows), static_cast<uint64_t>(k_dim), BM);
   if (rc != DICE_OK) return rc;
@@ -491,20 +492,20 @@ int dice_internal_router_tc(const void* x, const void* w_gate, int64_t n_tokens,
 
 extern "C" int dice_grouped_ffn(const void* rows_in, int64_t n_rows, int hidden, int ffn, int act, const void* w1,
                                 const void* w2, int n_slabs, const int32_t* seg_offsets, const int32_t* seg_slab,
-                                int n_seg, void* inter, void* rows_out, uint32_t* status, void* stream) {
+                                int n_seg, void* inter, void* rows_out, int reserve_sms, uint32_t* status, void* stream) {
   DICE_CHECK_ARG(act == DICE_ACT_SWIGLU || act == DICE_ACT_GELU_TANH, DICE_ERR_ARG);
   DICE_CHECK_ARG(hidden > 0 && ffn > 0, DICE_ERR_ARG);
   if (n_rows > 0 && n_seg > 0) DICE_CHECK_ARG(inter != nullptr, DICE_ERR_ARG);
   int rc;
   if (act == DICE_ACT_SWIGLU)
     rc = dice_grouped_gemm(rows_in, n_rows, hidden, w1, n_slabs, dice_w13_rows(ffn), seg_offsets, seg_slab, n_seg,
-                           DICE_EPI_SWIGLU, inter, ffn, ffn, status, stream);
+                           DICE_EPI_SWIGLU, inter, ffn, ffn, reserve_sms, status, stream);
   else
     rc = dice_grouped_gemm(rows_in, n_rows, hidden, w1, n_slabs, ffn, seg_offsets, seg_slab, n_seg, DICE_EPI_GELU_TANH,
-                           inter, ffn, ffn, status, stream);
+                           inter, ffn, ffn, reserve_sms, status, stream);
   if (rc != DICE_OK) return rc;
   return dice_grouped_gemm(inter, n_rows, ffn, w2, n_slabs, hidden, seg_offsets, seg_slab, n_seg, DICE_EPI_STORE,
-                           rows_out, hidden, hidden, status, stream);
+                           rows_out, hidden, hidden, reserve_sms, status, stream);
 }
 
 // The expert FFN whose second GEMM writes its rows straight into the token owners' combine buffers
@@ -515,7 +516,7 @@ extern "C" int dice_grouped_ffn_return(const void* rows_in, int64_t n_rows, int 
                                        const int32_t* seg_slab, int n_seg, void* inter, const int32_t* meta,
                                        const void* const* peer_back, const void* const* peer_flags,
                                        uint32_t* done_counter, int rank, int world, int back_capacity_rows,
-                                       uint32_t seq, uint32_t* status, void* stream) {
+                                       uint32_t seq, int reserve_sms, uint32_t* status, void* stream) {
   DICE_CHECK_ARG(act == DICE_ACT_SWIGLU || act == DICE_ACT_GELU_TANH, DICE_ERR_ARG);
   DICE_CHECK_ARG(n_rows > 0 && n_seg > 0 && hidden > 0 && ffn > 0 && n_slabs > 0, DICE_ERR_ARG);
   DICE_CHECK_ARG(rows_in && w1 && w2 && seg_offsets && inter && meta && peer_back && peer_flags && done_counter,
@@ -527,10 +528,10 @@ extern "C" int dice_grouped_ffn_return(const void* rows_in, int64_t n_rows, int 
   int rc;
   if (act == DICE_ACT_SWIGLU)
     rc = dice_grouped_gemm(rows_in, n_rows, hidden, w1, n_slabs, dice_w13_rows(ffn), seg_offsets, seg_slab, n_seg,
-                           DICE_EPI_SWIGLU, inter, ffn, ffn, status, stream);
+                           DICE_EPI_SWIGLU, inter, ffn, ffn, reserve_sms, status, stream);
   else
     rc = dice_grouped_gemm(rows_in, n_rows, hidden, w1, n_slabs, ffn, seg_offsets, seg_slab, n_seg, DICE_EPI_GELU_TANH,
-                           inter, ffn, ffn, status, stream);
+                           inter, ffn, ffn, reserve_sms, status, stream);
   if (rc != DICE_OK) return rc;
   DiceReturnSpec ret;
   ret.world = world;
@@ -543,6 +544,6 @@ extern "C" int dice_grouped_ffn_return(const void* rows_in, int64_t n_rows, int 
   ret.seq = seq;
   // `out` is only a base for pointer arithmetic that the return mapping replaces
   return dice_internal_gemm_pair(inter, n_rows, ffn, w2, n_slabs, hidden, seg_offsets, seg_slab, n_seg, DICE_EPI_STORE,
-                                 const_cast<void*>(peer_back[rank]), hidden, hidden, status,
+                                 const_cast<void*>(peer_back[rank]), hidden, hidden, reserve_sms, status,
                                  static_cast<cudaStream_t>(stream), &ret);
 }

@@ -21,8 +21,6 @@
 //     can no longer signal it.
 // Every wait is bounded as in the single-CTA kernel.
 #include <cuda.h>
-#include <stdlib.h>
-
 #include "umma.cuh"
 
 using namespace dice_umma;
@@ -136,8 +134,8 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
   pdl_wait();  // the segment table and the rows written by earlier kernels are visible from here on
 
   if (p.ret_world > 0) {
-    if (threadIdx.x <= p.ret_world) s_ret_src[threadIdx.x] = p.ret_meta[2 * p.ret_world + threadIdx.x];
-    if (threadIdx.x < p.ret_world) s_ret_base[threadIdx.x] = p.ret_meta[p.ret_world + threadIdx.x];
+    if (threadIdx.x <= p.ret_world) s_ret_src[threadIdx.x] = p.ret_meta[2 + 2 * p.ret_world + threadIdx.x];
+    if (threadIdx.x < p.ret_world) s_ret_base[threadIdx.x] = p.ret_meta[2 + p.ret_world + threadIdx.x];
   }
   for (int i = threadIdx.x; i <= p.n_seg; i += kThreads)
     s_seg_off[i] = p.seg_offsets != nullptr ? p.seg_offsets[i] : (i == 0 ? 0 : p.n_rows);
@@ -373,17 +371,6 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
   }
 }
 
-// ring depth: kPairStages unless DICE_PAIR_STAGES asks for fewer (experiments)
-int pair_stages() {
-  static int cached = 0;
-  if (cached == 0) {
-    const char* e = getenv("DICE_PAIR_STAGES");
-    const int v = e != nullptr ? atoi(e) : kPairStages;
-    cached = v < 2 ? 2 : (v > kPairStages ? kPairStages : v);
-  }
-  return cached;
-}
-
 // number of CTA pairs that can be resident at once (cached per device); 0 on error
 int resident_pairs() {
   static int cached[64] = {0};
@@ -418,10 +405,13 @@ int resident_pairs() {
 // Internal entry used by dice_grouped_gemm: same arguments, already validated.
 int dice_internal_gemm_pair(const void* a, int64_t n_rows, int k_dim, const void* w, int n_slabs, int64_t w_rows,
                             const int32_t* seg_offsets, const int32_t* seg_slab, int n_seg, int epilogue, void* out,
-                            int64_t ld_out, int n_out, uint32_t* status, cudaStream_t stream,
+                            int64_t ld_out, int n_out, int reserve_sms, uint32_t* status, cudaStream_t stream,
                             const DiceReturnSpec* ret) {
-  const int pairs = resident_pairs();
+  int pairs = resident_pairs();
   if (pairs <= 0) return DICE_ERR_CUDA;
+  // SM pairs left to kernels of other streams (the side-stream pushes of the asynchronous exchange)
+  pairs -= (reserve_sms + 1) / 2;
+  if (pairs < 1) pairs = 1;
   CUtensorMap tm_a, tm_b, tm_b_narrow;
   int rc = encode_map(&tm_a, a, static_cast<uint64_t>(n_rows), static_cast<uint64_t>(k_dim), BM);
   if (rc != DICE_OK) return rc;
@@ -445,7 +435,7 @@ int dice_internal_gemm_pair(const void* a, int64_t n_rows, int k_dim, const void
   p.ld_out = ld_out;
   p.status = status;
   p.b_box_rows = 128;
-  p.n_stages = pair_stages();
+  p.n_stages = kPairStages;
   if (ret != nullptr) {
     if (ret->world < 1 || ret->world > kMaxPeerRanks || epilogue != DICE_EPI_STORE) return DICE_ERR_ARG;
     p.ret_world = ret->world;
@@ -477,6 +467,7 @@ int dice_internal_gemm_pair(const void* a, int64_t n_rows, int k_dim, const void
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = dice_pdl_enabled() ? 2 : 1;
+  dice_count_launch();
   if (cudaLaunchKernelEx(&cfg, grouped_gemm_pair_kernel, tm_a, tm_b, tm_b_narrow, p) != cudaSuccess) return DICE_ERR_CUDA;
   return DICE_OK;
 }

@@ -23,6 +23,18 @@
 // flags with release stores; waiters poll with acquire loads.  Every wait is
 // bounded by wall time; on expiry a status code is recorded and the kernel
 // returns (results of that call are then undefined, the context stays usable).
+//
+// Failures travel with the flags.  A flag array holds 64 words: [0, W) the
+// flags proper and [32, 32 + W) failure marks.  A push that could not complete
+// (its count exchange timed out, or one of its copies never arrived) writes the
+// exchange's sequence number into its failure mark on every peer before it
+// raises the flag, so that the peers, which would otherwise consume incomplete
+// rows with a clean status, record DICE_STATUS_PEER_FAILED themselves.
+//
+// A receive buffer that is too small for what the peers want to send is found
+// by EVERY rank in the count exchange (each holds the full count matrix): all
+// of them record DICE_STATUS_EXCHANGE_OVERFLOW, and the exchange degenerates to
+// one that moves no rows at all (nothing is read or written out of bounds).
 #include <cuda.h>
 #include <stdlib.h>
 #include <string.h>
@@ -52,6 +64,15 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
   asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
 }
+constexpr int kFailMarkBase = 32;  // failure marks of a flag array start at this word
+
+// meta block, fixed part (see meta_ints below)
+constexpr int kMetaTotal = 0;   // rows this rank receives
+constexpr int kMetaState = 1;   // 0 ok, kStateOverflow, kStateNoCounts
+constexpr int kMetaHead = 2;
+constexpr int kStateOverflow = 1;
+constexpr int kStateNoCounts = 2;
+
 // true when *flag reached `seq` within the time limit
 __device__ bool wait_flag(const uint32_t* flag, uint32_t seq, uint32_t* status, uint32_t code) {
   const uint64_t t0 = timer_ns();
@@ -69,12 +90,13 @@ __device__ bool wait_flag(const uint32_t* flag, uint32_t seq, uint32_t* status, 
 }
 
 // Layout of the per-slot meta block this rank derives in ep_counts_kernel (int32):
-//   [0, W)            send_base[d]   first row of this rank's block in peer d's dispatch buffer
-//   [W, 2W)           back_base[s]   first row of this rank's block in peer s's combine buffer
-//   [2W, 3W+1)        src_off[s]     first row received from source s (W+1 entries)
-//   [3W+1, 3W+2+W*El) seg_off[...]   offsets of the (source, slot) segments of the receive buffer
-//   then              total_recv, overflow
-__host__ __device__ inline int meta_ints(int w, int el) { return 3 * w + 1 + w * el + 1 + 2; }
+//   [0]                 total rows this rank receives
+//   [1]                 state: 0 ok, 1 a receive buffer would overflow, 2 the peers' counts never arrived
+//   [2, 2+W)            send_base[d]   first row of this rank's block in peer d's dispatch buffer
+//   [2+W, 2+2W)         back_base[s]   first row of this rank's block in peer s's combine buffer
+//   [2+2W, 3+3W)        src_off[s]     first row received from source s (W+1 entries)
+//   [3+3W, 4+3W+W*El)   seg_off[...]   offsets of the (source, slot) segments of the receive buffer
+__host__ __device__ inline int meta_ints(int w, int el) { return kMetaHead + 3 * w + 1 + w * el + 1; }
 
 // ---- 1. counts ---------------------------------------------------------------------
 __global__ void __launch_bounds__(256)
@@ -106,61 +128,81 @@ ep_counts_kernel(const int* __restrict__ seg_offsets,  // [E+1] this rank's key-
     s_cnt[i / n_keys][i % n_keys] = s_ok ? my_matrix[i] : 0;
   __syncthreads();
   if (threadIdx.x == 0) {
-    int* send_base = meta;
-    int* back_base = meta + world;
-    int* src_off = meta + 2 * world;
-    int* seg_off = meta + 3 * world + 1;
+    int* send_base = meta + kMetaHead;
+    int* back_base = send_base + world;
+    int* src_off = back_base + world;
+    int* seg_off = src_off + world + 1;
     // rows source s sends to owner d
     auto block_rows = [&](int s, int d) {
       int n = 0;
       for (int i = 0; i < el; ++i) n += s_cnt[s][d * el + i];
       return n;
     };
+    // every rank sees the whole matrix, so every rank finds an overflow anywhere
+    bool overflow = false;
     for (int d = 0; d < world; ++d) {
-      int base = 0;
-      for (int s = 0; s < rank; ++s) base += block_rows(s, d);
-      send_base[d] = base;
+      int64_t tot = 0;
+      for (int s = 0; s < world; ++s) tot += block_rows(s, d);
+      overflow = overflow || tot > capacity_rows;
     }
-    for (int s = 0; s < world; ++s) {
-      int base = 0;
-      for (int d = 0; d < rank; ++d) base += block_rows(s, d);
-      back_base[s] = base;
-    }
-    int run = 0, seg = 0;
-    for (int s = 0; s < world; ++s) {
-      src_off[s] = run;
-      for (int i = 0; i < el; ++i) {
-        seg_off[seg++] = run;
-        run += s_cnt[s][rank * el + i];
+    const int state = !s_ok ? kStateNoCounts : (overflow ? kStateOverflow : 0);
+    if (state == 0) {
+      for (int d = 0; d < world; ++d) {
+        int base = 0;
+        for (int s = 0; s < rank; ++s) base += block_rows(s, d);
+        send_base[d] = base;
       }
-    }
-    src_off[world] = run;
-    seg_off[seg] = run;
-    int* tail = seg_off + world * el + 1;
-    tail[0] = run;
-    tail[1] = run > capacity_rows ? 1 : 0;
-    if (run > capacity_rows) {
-      if (status != nullptr) atomicCAS(status, 0u, DICE_STATUS_EXCHANGE_OVERFLOW);
-      // keep the FFN inside the buffer: drop the segments (the call's result is invalid and flagged)
+      for (int s = 0; s < world; ++s) {
+        int base = 0;
+        for (int d = 0; d < rank; ++d) base += block_rows(s, d);
+        back_base[s] = base;
+      }
+      int run = 0, seg = 0;
+      for (int s = 0; s < world; ++s) {
+        src_off[s] = run;
+        for (int i = 0; i < el; ++i) {
+          seg_off[seg++] = run;
+          run += s_cnt[s][rank * el + i];
+        }
+      }
+      src_off[world] = run;
+      seg_off[seg] = run;
+      meta[kMetaTotal] = run;
+    } else {
+      // the exchange moves nothing: every destination row lies "beyond the buffer", no rows are received,
+      // no segment holds work (the layer's result is invalid and flagged on every rank)
+      if (state == kStateOverflow && status != nullptr) atomicCAS(status, 0u, DICE_STATUS_EXCHANGE_OVERFLOW);
+      for (int d = 0; d < world; ++d) { send_base[d] = capacity_rows; back_base[d] = 0; }
+      for (int s = 0; s <= world; ++s) src_off[s] = 0;
       for (int i = 0; i <= world * el; ++i) seg_off[i] = 0;
+      meta[kMetaTotal] = 0;
     }
+    meta[kMetaState] = state;
   }
 }
 
-// raise `flag[rank] = seq` on every peer once the whole grid has finished writing
+// Raise `flag[rank] = seq` on every peer once the whole grid has finished writing.  `fail` (shared memory,
+// non-zero when this CTA could not complete its part) is collected over the grid in the upper half of the
+// counter; the last CTA then writes the failure marks before it raises the flags.  Grids stay below 65536 CTAs.
 __device__ __forceinline__ void signal_when_grid_done(unsigned int* done_counter, PeerTable flags, int rank, int world,
-                                                      uint32_t seq) {
+                                                      uint32_t seq, const int* fail) {
   __threadfence_system();
   __syncthreads();
-  __shared__ int s_last;
+  __shared__ int s_last, s_any_fail;
   if (threadIdx.x == 0) {
-    const unsigned int prev = atomicAdd(done_counter, 1u);
-    s_last = prev == gridDim.x - 1;
+    const unsigned int inc = *fail != 0 ? 0x10001u : 1u;
+    const unsigned int now = atomicAdd(done_counter, inc) + inc;
+    s_last = (now & 0xffffu) == gridDim.x;
+    s_any_fail = (now >> 16) != 0u;
   }
   __syncthreads();
   if (s_last) {
     __threadfence_system();
-    if (threadIdx.x < world) st_release_sys(static_cast<uint32_t*>(flags.ptr[threadIdx.x]) + rank, seq);
+    if (threadIdx.x < world) {
+      uint32_t* f = static_cast<uint32_t*>(flags.ptr[threadIdx.x]);
+      if (s_any_fail) f[kFailMarkBase + rank] = seq;  // ordered before the flag by the release store below
+      st_release_sys(f + rank, seq);
+    }
     if (threadIdx.x == 0) *done_counter = 0;  // ready for the next launch on this stream
   }
 }
@@ -174,10 +216,12 @@ ep_dispatch_kernel(const uint4* __restrict__ x, const int* __restrict__ pos, con
                    uint32_t* status) {
   __shared__ int s_first[kMaxRanks + 1];  // first sorted position of each owner's block
   __shared__ int s_base[kMaxRanks];
+  __shared__ int s_fail;
   pdl_trigger();
   pdl_wait();
   if (threadIdx.x <= world) s_first[threadIdx.x] = seg_offsets[threadIdx.x * el];
-  if (threadIdx.x < world) s_base[threadIdx.x] = meta[threadIdx.x];
+  if (threadIdx.x < world) s_base[threadIdx.x] = meta[kMetaHead + threadIdx.x];
+  if (threadIdx.x == 0) s_fail = meta[kMetaState] == kStateNoCounts;
   __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   for (int64_t t = static_cast<int64_t>(blockIdx.x) * 8 + warp; t < n_tokens; t += static_cast<int64_t>(gridDim.x) * 8) {
@@ -203,7 +247,7 @@ ep_dispatch_kernel(const uint4* __restrict__ x, const int* __restrict__ pos, con
         if (dst[s] != nullptr) dst[s][c] = v;
     }
   }
-  signal_when_grid_done(done_counter, flags, rank, world, seq);
+  signal_when_grid_done(done_counter, flags, rank, world, seq, &s_fail);
 }
 
 // ---- 3. wait for all sources ------------------------------------------------------------
@@ -211,22 +255,29 @@ __global__ void ep_wait_kernel(const uint32_t* __restrict__ my_flags, int world,
                                uint32_t code) {
   pdl_trigger();
   pdl_wait();
-  if (threadIdx.x < world) wait_flag(my_flags + threadIdx.x, seq, status, code);
+  if (threadIdx.x < world) {
+    if (wait_flag(my_flags + threadIdx.x, seq, status, code) &&
+        ld_acquire_sys(my_flags + kFailMarkBase + threadIdx.x) == seq && status != nullptr)
+      atomicCAS(status, 0u, DICE_STATUS_PEER_FAILED);  // the source says its rows are incomplete
+  }
 }
 
 // ---- 4. return: expert outputs go back to the token owners --------------------------------
 __global__ void __launch_bounds__(256)
 ep_return_kernel(const uint4* __restrict__ rows, const int* __restrict__ meta, PeerTable back_bufs, PeerTable flags,
-                 unsigned int* done_counter, int row_vec, int rank, int world, int back_capacity_rows, uint32_t seq,
-                 uint32_t* status) {
+                 unsigned int* done_counter, int row_vec, int rank, int world, int back_capacity_rows, int max_rows,
+                 uint32_t seq, uint32_t* status) {
   __shared__ int s_src_off[kMaxRanks + 1];
   __shared__ int s_back[kMaxRanks];
+  __shared__ int s_fail;
   pdl_trigger();
   pdl_wait();
-  if (threadIdx.x <= world) s_src_off[threadIdx.x] = meta[2 * world + threadIdx.x];
-  if (threadIdx.x < world) s_back[threadIdx.x] = meta[world + threadIdx.x];
+  if (threadIdx.x <= world) s_src_off[threadIdx.x] = meta[kMetaHead + 2 * world + threadIdx.x];
+  if (threadIdx.x < world) s_back[threadIdx.x] = meta[kMetaHead + world + threadIdx.x];
+  if (threadIdx.x == 0) s_fail = meta[kMetaState] == kStateNoCounts;
   __syncthreads();
-  const int total = s_src_off[world];
+  int total = s_src_off[world];
+  if (total > max_rows) total = max_rows;  // never read past the receive buffer, whatever the meta block says
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   for (int64_t r = static_cast<int64_t>(blockIdx.x) * 8 + warp; r < total; r += static_cast<int64_t>(gridDim.x) * 8) {
     int s = 0;
@@ -241,21 +292,33 @@ ep_return_kernel(const uint4* __restrict__ rows, const int* __restrict__ meta, P
 #pragma unroll 4
     for (int c = lane; c < row_vec; c += 32) dst[c] = ldg_stream16(src + c);
   }
-  signal_when_grid_done(done_counter, flags, rank, world, seq);
+  signal_when_grid_done(done_counter, flags, rank, world, seq, &s_fail);
 }
 
 
 // ---- bulk-copy variants of the two pushes ---------------------------------------------------
-// A push that has the GPU to itself (synchronous exchange) moves its rows with the copy unit instead of with
-// the SMs' load/store pipes: one warp per CTA streams chunks of rows through a ring of shared-memory buffers
-// (cp.async.bulk: global -> shared, completing on an mbarrier; shared -> global, local or peer, tracked in
-// bulk async-groups).  Local and remote destinations no longer share store queues, and the requests that
-// cross NVLink are whole rows.  The SIMT kernels above remain for pushes that run next to a GEMM on another
-// stream (they need no shared memory and fit beside its CTAs).
-constexpr int kBulkBufs = 4;
-constexpr int kBulkBufBytes = 32768;
-constexpr int kBulkLag = kBulkBufs - 2;  // chunks between a buffer's load and its stores
+// The rows move with the copy unit instead of with the SMs' load/store pipes: a warp streams chunks of rows
+// through its own ring of shared-memory buffers (cp.async.bulk: global -> shared, completing on an mbarrier;
+// shared -> global, local or peer, tracked in bulk async-groups).  Local and remote destinations do not share
+// store queues, and the requests that cross NVLink are whole rows.  Two shapes of the same kernels:
+//   * the push has the GPU to itself (synchronous exchange): one warp per CTA, one CTA per SM, 4 x 32 KB;
+//   * the push runs on a side stream next to the expert FFN (displaced / interweaved exchange): a handful of
+//     CTAs of four warps with 3 x 16 KB each, launched as clusters of two so that they fill whole SM pairs;
+//     the grouped GEMM leaves that many SMs free, and neither kernel disturbs the other's SMs.
+// The SIMT kernels above remain as the form that needs no shared memory.
+constexpr int kBulkMaxWarps = 4;
+constexpr int kBulkMaxBufs = 4;
 constexpr uint64_t kBulkWaitLimitNs = 1000ull * 1000ull * 1000ull;
+constexpr uint64_t kBulkDrainLimitNs = 50ull * 1000ull * 1000ull;
+
+struct BulkShape {
+  int warps;           // warps per CTA, each with its own ring
+  int bufs;            // buffers per ring; a buffer is stored (bufs - 2) chunks after its load was issued
+  uint32_t buf_bytes;  // multiple of 128
+};
+__host__ __device__ inline size_t bulk_smem_bytes(const BulkShape& b) {
+  return static_cast<size_t>(b.warps) * b.bufs * b.buf_bytes;
+}
 
 __device__ __forceinline__ uint32_t smem_addr32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 __device__ __forceinline__ void bulk_bar_init(uint32_t bar) {
@@ -275,7 +338,7 @@ __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.comm
 __device__ __forceinline__ void bulk_wait_read_1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
 // every group of this thread is complete: its writes are performed
 __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
-__device__ bool bulk_bar_wait(uint32_t bar, uint32_t parity) {
+__device__ bool bulk_bar_wait(uint32_t bar, uint32_t parity, uint64_t limit_ns) {
   const uint64_t t0 = timer_ns();
   uint32_t spins = 0;
   for (;;) {
@@ -288,7 +351,7 @@ __device__ bool bulk_bar_wait(uint32_t bar, uint32_t parity) {
         : "r"(bar), "r"(parity)
         : "memory");
     if (ok) return true;
-    if ((++spins & 127u) == 0 && timer_ns() - t0 > kBulkWaitLimitNs) return false;
+    if ((++spins & 127u) == 0 && timer_ns() - t0 > limit_ns) return false;
   }
 }
 // after the last store: writes of the copy unit are ordered before the flag this CTA may raise
@@ -296,51 +359,69 @@ __device__ __forceinline__ void bulk_drain() {
   bulk_wait_all();
   asm volatile("fence.proxy.async;" ::: "memory");
 }
+// A ring that gave up at chunk `k` still has the loads of chunks (k, last_loaded] in flight: give them a
+// short, bounded time to land before the CTA's shared memory is released.
+__device__ __forceinline__ void bulk_settle(const uint64_t* bars, int bufs, int64_t k, int64_t last_loaded) {
+  for (int64_t i = k + 1; i <= last_loaded; ++i)
+    bulk_bar_wait(smem_addr32(&bars[i % bufs]), static_cast<uint32_t>((i / bufs) & 1), kBulkDrainLimitNs);
+}
 
 template <int K>
-__global__ void __launch_bounds__(32)
+__global__ void __launch_bounds__(32 * kBulkMaxWarps)
 ep_dispatch_bulk_kernel(const uint8_t* __restrict__ x, const int* __restrict__ pos, const int* __restrict__ seg_offsets,
                         const int* __restrict__ meta, PeerTable recv_bufs, PeerTable flags, unsigned int* done_counter,
                         int64_t n_tokens, uint32_t row_bytes, int tokens_per_chunk, int rank, int world, int el,
-                        int capacity_rows, uint32_t seq, uint32_t* status) {
+                        int capacity_rows, uint32_t seq, uint32_t* status, BulkShape shape) {
   extern __shared__ __align__(128) uint8_t bulk_bufs[];
-  __shared__ __align__(8) uint64_t bars[kBulkBufs];
+  __shared__ __align__(8) uint64_t bars_all[kBulkMaxWarps][kBulkMaxBufs];
   __shared__ int s_first[kMaxRanks + 1];
   __shared__ int s_base[kMaxRanks];
-  const int lane = threadIdx.x;
+  __shared__ int s_fail;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int bufs = shape.bufs, lag = shape.bufs - 2;
+  uint64_t* bars = bars_all[warp];
   pdl_trigger();
   if (lane == 0) {
-    for (int b = 0; b < kBulkBufs; ++b) bulk_bar_init(smem_addr32(&bars[b]));
+    for (int b = 0; b < bufs; ++b) bulk_bar_init(smem_addr32(&bars[b]));
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   pdl_wait();
-  if (lane <= world) s_first[lane] = seg_offsets[lane * el];
-  if (lane < world) s_base[lane] = meta[lane];
-  __syncwarp();
+  if (threadIdx.x <= world) s_first[threadIdx.x] = seg_offsets[threadIdx.x * el];
+  if (threadIdx.x < world) s_base[threadIdx.x] = meta[kMetaHead + threadIdx.x];
+  if (threadIdx.x == 0) s_fail = meta[kMetaState] == kStateNoCounts;
+  __syncthreads();
+  // every warp of the grid is one worker; chunks are dealt round-robin over the workers
+  const int64_t worker = static_cast<int64_t>(blockIdx.x) * shape.warps + warp;
+  const int64_t n_workers = static_cast<int64_t>(gridDim.x) * shape.warps;
   const int64_t n_chunks = (n_tokens + tokens_per_chunk - 1) / tokens_per_chunk;
-  const int64_t mine = n_chunks > blockIdx.x ? (n_chunks - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
-  const uint32_t buf0 = smem_addr32(bulk_bufs);
-  for (int64_t j = 0; j < mine + kBulkLag; ++j) {
+  const int64_t mine = n_chunks > worker ? (n_chunks - worker + n_workers - 1) / n_workers : 0;
+  const uint32_t buf0 = smem_addr32(bulk_bufs) + static_cast<uint32_t>(warp) * bufs * shape.buf_bytes;
+  for (int64_t j = 0; j < mine + lag; ++j) {
     if (j < mine) {
-      if (j >= kBulkBufs) bulk_wait_read_1();  // the stores that read this buffer are done with it
+      if (j >= bufs) bulk_wait_read_1();  // the stores that read this buffer are done with it
       __syncwarp();
       if (lane == 0) {
-        const int64_t tok0 = (blockIdx.x + j * gridDim.x) * tokens_per_chunk;
+        const int64_t tok0 = (worker + j * n_workers) * tokens_per_chunk;
         const int64_t left = n_tokens - tok0;
         const uint32_t n = static_cast<uint32_t>(left < tokens_per_chunk ? left : tokens_per_chunk);
-        const int b = static_cast<int>(j % kBulkBufs);
-        bulk_load(buf0 + b * kBulkBufBytes, x + tok0 * row_bytes, n * row_bytes, smem_addr32(&bars[b]));
+        const int b = static_cast<int>(j % bufs);
+        bulk_load(buf0 + b * shape.buf_bytes, x + tok0 * row_bytes, n * row_bytes, smem_addr32(&bars[b]));
       }
     }
-    const int64_t k = j - kBulkLag;
+    const int64_t k = j - lag;
     if (k >= 0) {
-      const int b = static_cast<int>(k % kBulkBufs);
+      const int b = static_cast<int>(k % bufs);
       // the same verdict in every lane, so that the warp leaves the loop together
-      if (!__all_sync(0xffffffffu, bulk_bar_wait(smem_addr32(&bars[b]), static_cast<uint32_t>((k / kBulkBufs) & 1)))) {
+      if (!__all_sync(0xffffffffu, bulk_bar_wait(smem_addr32(&bars[b]), static_cast<uint32_t>((k / bufs) & 1), kBulkWaitLimitNs))) {
         if (status != nullptr) atomicCAS(status, 0u, DICE_STATUS_WAIT_SMEM_FULL);
+        if (lane == 0) {
+          atomicExch(&s_fail, 1);
+          bulk_settle(bars, bufs, k, (j < mine ? j : mine - 1));
+        }
+        __syncwarp();
         break;
       }
-      const int64_t tok0 = (blockIdx.x + k * gridDim.x) * tokens_per_chunk;
+      const int64_t tok0 = (worker + k * n_workers) * tokens_per_chunk;
       const int64_t left = n_tokens - tok0;
       const int n = static_cast<int>(left < tokens_per_chunk ? left : tokens_per_chunk);
       if (lane < n * K) {
@@ -352,7 +433,7 @@ ep_dispatch_bulk_kernel(const uint8_t* __restrict__ x, const int* __restrict__ p
           const int row = s_base[d] + (p - s_first[d]);
           if (row < capacity_rows)
             bulk_store(static_cast<uint8_t*>(recv_bufs.ptr[d]) + static_cast<int64_t>(row) * row_bytes,
-                       buf0 + b * kBulkBufBytes + ti * row_bytes, row_bytes);
+                       buf0 + b * shape.buf_bytes + ti * row_bytes, row_bytes);
           else if (status != nullptr)
             atomicCAS(status, 0u, DICE_STATUS_EXCHANGE_OVERFLOW);
         }
@@ -361,29 +442,36 @@ ep_dispatch_bulk_kernel(const uint8_t* __restrict__ x, const int* __restrict__ p
     }
   }
   bulk_drain();
-  signal_when_grid_done(done_counter, flags, rank, world, seq);
+  signal_when_grid_done(done_counter, flags, rank, world, seq, &s_fail);
 }
 
-__global__ void __launch_bounds__(32)
+__global__ void __launch_bounds__(32 * kBulkMaxWarps)
 ep_return_bulk_kernel(const uint8_t* __restrict__ rows, const int* __restrict__ meta, PeerTable back_bufs, PeerTable flags,
                       unsigned int* done_counter, uint32_t row_bytes, int rows_per_chunk, int rank, int world,
-                      int back_capacity_rows, uint32_t seq, uint32_t* status) {
+                      int back_capacity_rows, int max_rows, uint32_t seq, uint32_t* status, BulkShape shape) {
   extern __shared__ __align__(128) uint8_t bulk_bufs[];
-  __shared__ __align__(8) uint64_t bars[kBulkBufs];
+  __shared__ __align__(8) uint64_t bars_all[kBulkMaxWarps][kBulkMaxBufs];
   __shared__ int s_src_off[kMaxRanks + 1];
   __shared__ int s_back[kMaxRanks];
   __shared__ int s_chunk0[kMaxRanks + 1];  // chunks before source s
-  const int lane = threadIdx.x;
+  __shared__ int s_fail;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int bufs = shape.bufs, lag = shape.bufs - 2;
+  uint64_t* bars = bars_all[warp];
   pdl_trigger();
   if (lane == 0) {
-    for (int b = 0; b < kBulkBufs; ++b) bulk_bar_init(smem_addr32(&bars[b]));
+    for (int b = 0; b < bufs; ++b) bulk_bar_init(smem_addr32(&bars[b]));
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   pdl_wait();
-  if (lane <= world) s_src_off[lane] = meta[2 * world + lane];
-  if (lane < world) s_back[lane] = meta[world + lane];
-  __syncwarp();
-  if (lane == 0) {
+  if (threadIdx.x <= world) {
+    int v = meta[kMetaHead + 2 * world + threadIdx.x];
+    s_src_off[threadIdx.x] = v < max_rows ? v : max_rows;  // never read past the receive buffer
+  }
+  if (threadIdx.x < world) s_back[threadIdx.x] = meta[kMetaHead + world + threadIdx.x];
+  if (threadIdx.x == 0) s_fail = meta[kMetaState] == kStateNoCounts;
+  __syncthreads();
+  if (threadIdx.x == 0) {
     int run = 0;
     for (int s = 0; s < world; ++s) {
       s_chunk0[s] = run;
@@ -392,36 +480,38 @@ ep_return_bulk_kernel(const uint8_t* __restrict__ rows, const int* __restrict__ 
     }
     s_chunk0[world] = run;
   }
-  __syncwarp();
+  __syncthreads();
+  const int64_t worker = static_cast<int64_t>(blockIdx.x) * shape.warps + warp;
+  const int64_t n_workers = static_cast<int64_t>(gridDim.x) * shape.warps;
   const int64_t n_chunks = s_chunk0[world];
-  const int64_t mine = n_chunks > blockIdx.x ? (n_chunks - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
-  const uint32_t buf0 = smem_addr32(bulk_bufs);
+  const int64_t mine = n_chunks > worker ? (n_chunks - worker + n_workers - 1) / n_workers : 0;
+  const uint32_t buf0 = smem_addr32(bulk_bufs) + static_cast<uint32_t>(warp) * bufs * shape.buf_bytes;
   // a chunk: `n` rows of source `s` starting at received row `r0`
   auto locate = [&](int64_t j, int& s, int& r0, int& n) {
-    const int c = static_cast<int>(blockIdx.x + j * gridDim.x);
+    const int c = static_cast<int>(worker + j * n_workers);
     s = 0;
     while (s + 1 < world && c >= s_chunk0[s + 1]) ++s;
     r0 = s_src_off[s] + (c - s_chunk0[s]) * rows_per_chunk;
     n = s_src_off[s + 1] - r0;
     if (n > rows_per_chunk) n = rows_per_chunk;
   };
-  if (lane == 0) {  // the whole pipeline is one lane's: one load and one store per chunk
-    bool alive = true;
-    for (int64_t j = 0; alive && j < mine + kBulkLag; ++j) {
+  if (lane == 0) {  // a ring is one lane's: one load and one store per chunk
+    for (int64_t j = 0; j < mine + lag; ++j) {
       if (j < mine) {
-        if (j >= kBulkBufs) bulk_wait_read_1();
+        if (j >= bufs) bulk_wait_read_1();
         int s, r0, n;
         locate(j, s, r0, n);
-        const int b = static_cast<int>(j % kBulkBufs);
-        bulk_load(buf0 + b * kBulkBufBytes, rows + static_cast<int64_t>(r0) * row_bytes, static_cast<uint32_t>(n) * row_bytes,
+        const int b = static_cast<int>(j % bufs);
+        bulk_load(buf0 + b * shape.buf_bytes, rows + static_cast<int64_t>(r0) * row_bytes, static_cast<uint32_t>(n) * row_bytes,
                   smem_addr32(&bars[b]));
       }
-      const int64_t k = j - kBulkLag;
+      const int64_t k = j - lag;
       if (k >= 0) {
-        const int b = static_cast<int>(k % kBulkBufs);
-        if (!bulk_bar_wait(smem_addr32(&bars[b]), static_cast<uint32_t>((k / kBulkBufs) & 1))) {
+        const int b = static_cast<int>(k % bufs);
+        if (!bulk_bar_wait(smem_addr32(&bars[b]), static_cast<uint32_t>((k / bufs) & 1), kBulkWaitLimitNs)) {
           if (status != nullptr) atomicCAS(status, 0u, DICE_STATUS_WAIT_SMEM_FULL);
-          alive = false;
+          atomicExch(&s_fail, 1);
+          bulk_settle(bars, bufs, k, (j < mine ? j : mine - 1));
           break;
         }
         int s, r0, n;
@@ -432,7 +522,7 @@ ep_return_bulk_kernel(const uint8_t* __restrict__ rows, const int* __restrict__ 
           n = back_capacity_rows > row ? back_capacity_rows - row : 0;
         }
         if (n > 0)
-          bulk_store(static_cast<uint8_t*>(back_bufs.ptr[s]) + static_cast<int64_t>(row) * row_bytes, buf0 + b * kBulkBufBytes,
+          bulk_store(static_cast<uint8_t*>(back_bufs.ptr[s]) + static_cast<int64_t>(row) * row_bytes, buf0 + b * shape.buf_bytes,
                      static_cast<uint32_t>(n) * row_bytes);
         bulk_commit();
       }
@@ -440,7 +530,7 @@ ep_return_bulk_kernel(const uint8_t* __restrict__ rows, const int* __restrict__ 
     bulk_drain();
   }
   __syncwarp();
-  signal_when_grid_done(done_counter, flags, rank, world, seq);
+  signal_when_grid_done(done_counter, flags, rank, world, seq, &s_fail);
 }
 
 // DICE_EP_P2P_BULK=0 keeps the SIMT pushes everywhere
@@ -465,12 +555,73 @@ int sm_count_here() {
   return cached[dev];
 }
 
+// the two shapes of the bulk-copy pushes (see above)
+constexpr BulkShape kBulkAlone = {1, 4, 32768};
+constexpr BulkShape kBulkBeside = {4, 3, 16384};
+
 template <typename Kern>
 int bulk_smem_ready(Kern kernel) {
-  return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kBulkBufs * kBulkBufBytes) ==
-                 cudaSuccess
+  return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                              static_cast<int>(bulk_smem_bytes(kBulkBeside) > bulk_smem_bytes(kBulkAlone)
+                                                   ? bulk_smem_bytes(kBulkBeside)
+                                                   : bulk_smem_bytes(kBulkAlone))) == cudaSuccess
              ? DICE_OK
              : DICE_ERR_CUDA;
+}
+
+// dependent launch, optionally as clusters of two CTAs (which fill whole SM pairs)
+template <typename... KArgs, typename... Args>
+cudaError_t launch_push(void (*kernel)(KArgs...), unsigned grid, unsigned threads, size_t smem, cudaStream_t stream,
+                        bool pairs, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid, 1, 1);
+  cfg.blockDim = dim3(threads, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  int n = 0;
+  if (pairs) {
+    attr[n].id = cudaLaunchAttributeClusterDimension;
+    attr[n].val.clusterDim.x = 2;
+    attr[n].val.clusterDim.y = 1;
+    attr[n].val.clusterDim.z = 1;
+    ++n;
+  }
+  if (dice_pdl_enabled()) {
+    attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[n].val.programmaticStreamSerializationAllowed = 1;
+    ++n;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = n;
+  dice_count_launch();
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
+// Grid and shape of a bulk-copy push.  max_ctas == 0: one single-warp CTA per SM; max_ctas > 0: at most that
+// many four-warp CTAs, an even number of them (they are launched as clusters of two).
+struct BulkPlan {
+  BulkShape shape;
+  unsigned grid;
+  bool pairs;
+};
+BulkPlan plan_bulk(int max_ctas, int sms, int64_t chunks_alone, int64_t chunks_beside) {
+  BulkPlan p;
+  if (max_ctas == 0) {
+    p.shape = kBulkAlone;
+    p.grid = static_cast<unsigned>(chunks_alone < sms ? (chunks_alone > 0 ? chunks_alone : 1) : sms);
+    p.pairs = false;
+  } else {
+    p.shape = kBulkBeside;
+    int64_t ctas = (chunks_beside + p.shape.warps - 1) / p.shape.warps;
+    if (ctas > max_ctas) ctas = max_ctas;
+    if (ctas > sms) ctas = sms;
+    ctas = (ctas + 1) & ~int64_t(1);
+    if (ctas < 2) ctas = 2;
+    p.grid = static_cast<unsigned>(ctas);
+    p.pairs = true;
+  }
+  return p;
 }
 
 int fill_table(PeerTable* t, const void* const* ptrs, int world) {
@@ -526,32 +677,34 @@ extern "C" int dice_ep_dispatch_rows(const void* x, const int32_t* pos, const in
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int el = n_experts / world;
   const size_t row_bytes = hidden * es;
-  if (max_ctas == 0 && bulk_pushes() && row_bytes <= kBulkBufBytes && n_tokens > 0) {
-    // the push has the GPU to itself: move the rows with the copy unit
-    const int sms = sm_count_here();
-    if (sms <= 0) return DICE_ERR_CUDA;
-    int tpc = static_cast<int>(kBulkBufBytes / row_bytes);
-    if (tpc > 32 / k) tpc = 32 / k;
-    const int64_t chunks = (n_tokens + tpc - 1) / tpc;
-    const dim3 grid(static_cast<unsigned>(chunks < sms ? chunks : sms));
+  const int sms = sm_count_here();
+  if (sms <= 0) return DICE_ERR_CUDA;
+  if (max_ctas >= 0 && bulk_pushes() && row_bytes <= kBulkBeside.buf_bytes && n_tokens > 0) {
+    auto tokens_per_chunk = [&](const BulkShape& b) {
+      int t = static_cast<int>(b.buf_bytes / row_bytes);
+      return t > 32 / k ? 32 / k : t;
+    };
+    const int tpc_alone = tokens_per_chunk(kBulkAlone), tpc_beside = tokens_per_chunk(kBulkBeside);
+    const BulkPlan bp = plan_bulk(max_ctas, sms, (n_tokens + tpc_alone - 1) / tpc_alone, (n_tokens + tpc_beside - 1) / tpc_beside);
+    const int tpc = max_ctas == 0 ? tpc_alone : tpc_beside;
     const uint8_t* xb = static_cast<const uint8_t*>(x);
     if (k == 2) {
       DICE_CHECK_ARG(bulk_smem_ready(ep_dispatch_bulk_kernel<2>) == DICE_OK, DICE_ERR_CUDA);
-      DICE_CUDA_OK(dice_launch(ep_dispatch_bulk_kernel<2>, grid, dim3(32), kBulkBufs * kBulkBufBytes, s, xb, pos, seg_offsets,
-                               meta, r, f, done_counter, n_tokens, static_cast<uint32_t>(row_bytes), tpc, rank, world, el,
-                               capacity_rows, seq, status));
+      DICE_CUDA_OK(launch_push(ep_dispatch_bulk_kernel<2>, bp.grid, 32u * bp.shape.warps, bulk_smem_bytes(bp.shape), s, bp.pairs,
+                               xb, pos, seg_offsets, meta, r, f, done_counter, n_tokens, static_cast<uint32_t>(row_bytes), tpc,
+                               rank, world, el, capacity_rows, seq, status, bp.shape));
     } else {
       DICE_CHECK_ARG(bulk_smem_ready(ep_dispatch_bulk_kernel<1>) == DICE_OK, DICE_ERR_CUDA);
-      DICE_CUDA_OK(dice_launch(ep_dispatch_bulk_kernel<1>, grid, dim3(32), kBulkBufs * kBulkBufBytes, s, xb, pos, seg_offsets,
-                               meta, r, f, done_counter, n_tokens, static_cast<uint32_t>(row_bytes), tpc, rank, world, el,
-                               capacity_rows, seq, status));
+      DICE_CUDA_OK(launch_push(ep_dispatch_bulk_kernel<1>, bp.grid, 32u * bp.shape.warps, bulk_smem_bytes(bp.shape), s, bp.pairs,
+                               xb, pos, seg_offsets, meta, r, f, done_counter, n_tokens, static_cast<uint32_t>(row_bytes), tpc,
+                               rank, world, el, capacity_rows, seq, status, bp.shape));
     }
     return DICE_OK;
   }
   int64_t blocks = (n_tokens + 7) / 8;
   if (blocks < 1) blocks = 1;  // the flags are raised even when this rank has nothing to send
-  if (max_ctas > 0 && blocks > max_ctas) blocks = max_ctas;  // a small grid leaves the SMs to a concurrent GEMM
-  DICE_CHECK_ARG(blocks <= 0x7fffffffLL, DICE_ERR_LIMIT);
+  if (blocks > sms * 16) blocks = sms * 16;  // the kernel strides over the tokens
+  if (max_ctas < -1 && blocks > -max_ctas) blocks = -max_ctas;
   const dim3 grid(static_cast<unsigned>(blocks));
   if (k == 2)
     DICE_CUDA_OK(dice_launch(ep_dispatch_kernel<2>, grid, dim3(256), 0, s, static_cast<const uint4*>(x), pos, seg_offsets,
@@ -587,25 +740,27 @@ extern "C" int dice_ep_return_rows(const void* rows, const int32_t* meta, const 
   if (rc != DICE_OK) return rc;
   const int row_vec = static_cast<int>(hidden * es / 16);
   const size_t row_bytes = hidden * es;
-  if (max_ctas == 0 && bulk_pushes() && row_bytes <= kBulkBufBytes && max_rows > 0) {
-    const int sms = sm_count_here();
-    if (sms <= 0) return DICE_ERR_CUDA;
-    const int rpc = static_cast<int>(kBulkBufBytes / row_bytes);
-    const int64_t chunks = (static_cast<int64_t>(max_rows) + rpc - 1) / rpc + world;
+  const int sms = sm_count_here();
+  if (sms <= 0) return DICE_ERR_CUDA;
+  if (max_ctas >= 0 && bulk_pushes() && row_bytes <= kBulkBeside.buf_bytes && max_rows > 0) {
+    const int rpc_alone = static_cast<int>(kBulkAlone.buf_bytes / row_bytes);
+    const int rpc_beside = static_cast<int>(kBulkBeside.buf_bytes / row_bytes);
+    const BulkPlan bp = plan_bulk(max_ctas, sms, (static_cast<int64_t>(max_rows) + rpc_alone - 1) / rpc_alone + world,
+                                  (static_cast<int64_t>(max_rows) + rpc_beside - 1) / rpc_beside + world);
     DICE_CHECK_ARG(bulk_smem_ready(ep_return_bulk_kernel) == DICE_OK, DICE_ERR_CUDA);
-    DICE_CUDA_OK(dice_launch(ep_return_bulk_kernel, dim3(static_cast<unsigned>(chunks < sms ? chunks : sms)), dim3(32),
-                             kBulkBufs * kBulkBufBytes, static_cast<cudaStream_t>(stream),
-                             static_cast<const uint8_t*>(rows), meta, b, f, done_counter, static_cast<uint32_t>(row_bytes), rpc,
-                             rank, world, back_capacity_rows, seq, status));
+    DICE_CUDA_OK(launch_push(ep_return_bulk_kernel, bp.grid, 32u * bp.shape.warps, bulk_smem_bytes(bp.shape),
+                             static_cast<cudaStream_t>(stream), bp.pairs, static_cast<const uint8_t*>(rows), meta, b, f,
+                             done_counter, static_cast<uint32_t>(row_bytes), max_ctas == 0 ? rpc_alone : rpc_beside, rank, world,
+                             back_capacity_rows, max_rows, seq, status, bp.shape));
     return DICE_OK;
   }
   int64_t blocks = (static_cast<int64_t>(max_rows) + 7) / 8;
   if (blocks < 1) blocks = 1;
-  if (blocks > 148 * 16) blocks = 148 * 16;  // grid-stride over the rows actually received
-  if (max_ctas > 0 && blocks > max_ctas) blocks = max_ctas;
+  if (blocks > sms * 16) blocks = sms * 16;  // grid-stride over the rows actually received
+  if (max_ctas < -1 && blocks > -max_ctas) blocks = -max_ctas;
   DICE_CUDA_OK(dice_launch(ep_return_kernel, dim3(static_cast<unsigned>(blocks)), dim3(256), 0,
                            static_cast<cudaStream_t>(stream), static_cast<const uint4*>(rows), meta, b, f, done_counter,
-                           row_vec, rank, world, back_capacity_rows, seq, status));
+                           row_vec, rank, world, back_capacity_rows, max_rows, seq, status));
   return DICE_OK;
 }
 

@@ -365,6 +365,7 @@ extern "C" int dice_pack_w13(const void* gate_proj, const void* up_proj, int hid
   const int64_t out_rows = dice_w13_rows(ffn);
   const int64_t total = out_rows * row_vec;
   const int blocks = static_cast<int>(total / 256 + 1 < 4096 ? total / 256 + 1 : 4096);
+  dice_count_launch();
   pack_w13_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint4*>(gate_proj), static_cast<const uint4*>(up_proj), row_vec, ffn, out_rows,
       static_cast<uint4*>(out_w13));

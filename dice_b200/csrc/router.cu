@@ -249,6 +249,7 @@ int launch_router(const void* x, const void* wg, int64_t n, int h, int e, int re
   int per_sm = static_cast<int>((220 * 1024) / (smem + 1024));
   per_sm = per_sm < 1 ? 1 : (per_sm > 6 ? 6 : per_sm);
   const int64_t grid = n_tiles < static_cast<int64_t>(sms) * per_sm ? n_tiles : static_cast<int64_t>(sms) * per_sm;
+  dice_count_launch();
   kernel<<<static_cast<unsigned>(grid), kRouterWarps * 32, smem, s>>>(static_cast<const T*>(x), static_cast<const T*>(wg),
                                                                       n, h, e, renorm, idx, w, hist,
                                                                       static_cast<T*>(logits));
@@ -279,6 +280,7 @@ int launch_select(const void* logits, int64_t n, int e, int renorm, int64_t* idx
                   cudaStream_t s) {
   const int64_t blocks = (n + 127) / 128;
   if (blocks > 0x7fffffffLL) return DICE_ERR_LIMIT;
+  dice_count_launch();
   top2_from_logits_kernel<T, EP><<<static_cast<unsigned>(blocks), 128, 0, s>>>(static_cast<const T*>(logits), n, e,
                                                                               renorm, idx, w, hist);
   return cudaGetLastError() == cudaSuccess ? DICE_OK : DICE_ERR_CUDA;

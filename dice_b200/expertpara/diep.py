@@ -93,9 +93,20 @@ def ep_get_max_mem():
 # ---- step / skip policy (diep.py:57-98) ----------------------------------------
 
 
+def _poll_device_status():
+    """A failure that a kernel recorded on the device (an expired wait, an
+    exchange buffer that was too small, a peer that gave up) becomes a Python
+    exception here, without a synchronisation: see ``ops.poll_status``."""
+    if torch.cuda.is_available() and torch.cuda.is_initialized():
+        from .. import ops
+
+        ops.poll_status()
+
+
 def ep_set_step(step):
     global _step
     _step = step
+    _poll_device_status()
 
 
 def ep_skip_enabled():
@@ -182,6 +193,7 @@ def ep_cache_init(cache_capacity, auto_gc=False, noskip_step=1, skip_mode=None, 
 
 
 def ep_cache_clear():
+    _poll_device_status()
     _diep_cache_dispatch.clear()
     _diep_cache_combine.clear()
     _diep_cache_skip.clear()

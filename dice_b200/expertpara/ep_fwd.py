@@ -201,8 +201,10 @@ def _peer_push(info, async_op, dispatch=None, rows_back=None):
 
     x = info.xchg
     lib, tab, slot = x.lib, info.tab, info.slot
-    # 0: the push owns the GPU (bulk-copy kernels); asynchronous pushes run next to the expert FFN: SIMT kernels
+    # 0: the push owns the GPU (one copy-unit warp per SM); an asynchronous push runs next to the expert FFN on
+    # the few SMs that the FFN leaves free (p2p.reserve_sms)
     side_ctas = (p2p.side_push_ctas() or -1) if async_op else 0
+    p2p.note_push(async_op)
     if async_op:
         stream = x.fork_to_comm()  # the push runs on the side stream, after what the current stream has produced
         # the caching allocator must not hand these to someone else before the side stream has read them
@@ -254,7 +256,8 @@ def proc_experts(inp, experts, token_counts_global, num_local_experts):
             if inp.dtype == torch.bfloat16 and p2p.fused_return():
                 pack.run_offsets_return(inp, token_counts_global)
                 return p2p.ReturnedRows(token_counts_global)
-            return pack.run_offsets(inp, token_counts_global.seg_dev, token_counts_global.xchg.seg_slab_dev)
+            return pack.run_offsets(inp, token_counts_global.seg_dev, token_counts_global.xchg.seg_slab_dev,
+                                    reserve_sms=p2p.reserve_sms())
         offs = token_counts_global.seg_dev.tolist()  # arbitrary expert modules need the bounds on the host
         outp = torch.empty_like(inp)
         for j, slot in enumerate(seg_slab):
@@ -375,7 +378,7 @@ def moe_infer_ep(inp: torch.Tensor, experts: nn.ModuleList, flat_expert_indices,
         with _scope("exchange_token_counts"):
             _lib.check(xchg.lib.dice_ep_exchange_counts(
                 seg_offsets.data_ptr(), tab["matrix"], tab["f_cnt"], xchg._meta_ptrs[slot], xchg.rank, xchg.world,
-                xchg.n_experts, xchg.capacity_rows, seq, xchg.status_ptr, _stream()), "dice_ep_exchange_counts")
+                xchg.n_experts, xchg.min_peer_cap, seq, xchg.status_ptr, _stream()), "dice_ep_exchange_counts")
         counts_local = None
         counts_global = p2p.SegInfo(xchg, slot, seq, tab, n_tokens * k_eff)
         grouped_dup_inp = p2p.PendingRows(inp, pos, seg_offsets, k_eff, counts_global)

@@ -14,9 +14,19 @@ to be consumed, while the same layer launches the next ones (the displaced
 protocol consumes a dispatch one step and its results two steps after launch;
 peers are never more than a step ahead, so three slots per layer suffice):
 
-* ``ctrl``  int32: count matrix ``[W][E]`` + three flag arrays ``[W]``
+* ``ctrl``  int32: count matrix ``[W][E]`` + three flag arrays (64 words each:
+  flags ``[W]`` and, from word 32, the failure marks ``[W]``)
 * ``recv``  rows received for this rank's experts, ``capacity_rows x hidden``
 * ``back``  expert outputs returned for this rank's tokens, ``max_rows x hidden``
+
+Receive capacity.  The reference has no capacity: ``all_to_all_single`` receives
+whatever the router sends (``ep_fwd.py:247-293``).  Here the receive buffers are
+allocated once, so ``capacity_rows`` is ``W x`` the largest sender's rows (which
+no routing can exceed) whenever all slots then fit into a share of the free
+device memory (``DICE_EP_P2P_MEM_FRACTION``, default 0.5), and otherwise as
+many rows as that share holds, never fewer than twice the largest sender.  A
+routing that still does not fit is detected by every rank in the count exchange
+and reported through the device status word (``ops.poll_status``).
 """
 from __future__ import annotations
 
@@ -34,8 +44,8 @@ _FLAG_PAD = 64  # ints; keeps the three flag arrays on separate 256-byte lines
 
 
 class PeerExchange:
-    def __init__(self, n_experts: int, hidden: int, dtype: torch.dtype, max_rows: int, capacity_factor: float = 2.0,
-                 n_layers: int = 1, n_par: int = 3, group=None):
+    def __init__(self, n_experts: int, hidden: int, dtype: torch.dtype, max_rows: int,
+                 capacity_factor: Optional[float] = None, n_layers: int = 1, n_par: int = 3, group=None):
         n_slots = n_layers * n_par
         self.n_layers, self.n_par = n_layers, n_par
         self.uses = [0] * n_layers
@@ -51,11 +61,21 @@ class PeerExchange:
         self.calls = 0
         self._comm = None
 
-        # every rank sizes its receive buffer from the largest sender
+        # every rank sizes its receive buffer from the largest sender and the tightest memory, so that all
+        # ranks arrive at the same capacity
         sizes = [None] * self.world
-        dist.all_gather_object(sizes, self.max_rows, group=group)
-        biggest = max(sizes)
-        self.capacity_rows = int(min(self.world * biggest, math.ceil(capacity_factor * biggest)))
+        free_bytes = torch.cuda.mem_get_info(self.device)[0]
+        dist.all_gather_object(sizes, (self.max_rows, free_bytes), group=group)
+        biggest = max(r for r, _ in sizes)
+        lossless = self.world * biggest
+        if capacity_factor is not None:
+            self.capacity_rows = int(min(lossless, math.ceil(capacity_factor * biggest)))
+        else:
+            share = float(os.environ.get("DICE_EP_P2P_MEM_FRACTION", "0.5")) * min(f for _, f in sizes)
+            row_bytes = hidden * torch.empty((), dtype=dtype).element_size()
+            fit = int((share / n_slots - self.max_rows * row_bytes) // row_bytes)  # recv + back per slot
+            self.capacity_rows = int(min(lossless, max(2 * biggest, fit)))
+        self.lossless = self.capacity_rows >= lossless
 
         w, e = self.world, n_experts
         self.ctrl_stride = ((w * e + _FLAG_PAD - 1) // _FLAG_PAD + 3) * _FLAG_PAD
@@ -66,7 +86,9 @@ class PeerExchange:
         self.meta_ints = self.lib.dice_ep_meta_ints(w, self.el)
         self.meta = torch.zeros((n_slots, self.meta_ints), dtype=torch.int32, device=self.device)
         self.done = torch.zeros(2 * n_slots, dtype=torch.int32, device=self.device)
-        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        from .. import ops
+
+        self.status = ops.device_status(self.device)  # shared with the other kernels: polled once per step
         self.seq = [0] * n_slots
         torch.cuda.synchronize()
 
@@ -120,7 +142,7 @@ class PeerExchange:
         # the smallest receive / return capacity among the peers bounds what this rank may write
         self.min_peer_cap = min(self.peer_cap)
         self.min_peer_rows = min(self.peer_max_rows)
-        a = 3 * self.world + 1
+        a = 3 * self.world + 3  # first of the (source, slot) segment offsets in a meta block
         self._seg_views = [self.meta[s, a:a + self.world * self.el + 1] for s in range(n_slots)]
         self._meta_ptrs = [self.meta[s].data_ptr() for s in range(n_slots)]
         self._done_ptrs = [self.done.data_ptr() + 4 * i for i in range(2 * n_slots)]
@@ -205,11 +227,32 @@ def enabled() -> bool:
 
 
 def side_push_ctas() -> int:
-    """Grid bound of pushes that run on the side stream next to the expert FFN
-    (DICE_EP_P2P_SIDE_CTAS; 0, the default, means one CTA per 8 rows).  A small
-    grid leaves the SMs to the GEMM but stretches the push: measured on 2 GPUs,
-    48 CTAs were no faster than the full grid and 16 CTAs were slower."""
-    return int(os.environ.get("DICE_EP_P2P_SIDE_CTAS", "0"))
+    """How many CTAs a push may use when it runs on the side stream next to
+    the expert FFN (``DICE_EP_P2P_SIDE_CTAS``, default 8; -1 selects the SIMT
+    push over all SMs).  The FFN's persistent kernel is told to leave the same
+    number of SMs free, so the two never compete for an SM: the push moves its
+    rows with the copy unit through shared memory, the GEMM keeps its own SMs
+    to itself."""
+    return int(os.environ.get("DICE_EP_P2P_SIDE_CTAS", "8"))
+
+
+_side_pushes = False
+
+
+def note_push(async_op: bool) -> None:
+    """Remember whether the exchange is in an asynchronous phase (the last push
+    went to the side stream)."""
+    global _side_pushes
+    _side_pushes = bool(async_op)
+
+
+def reserve_sms() -> int:
+    """SMs the expert FFN should leave free: the side pushes' CTAs while the
+    exchange is asynchronous, else none."""
+    if not _side_pushes:
+        return 0
+    n = side_push_ctas()
+    return n if n > 0 else 0
 
 
 _fused_return = os.environ.get("DICE_EP_P2P_FUSED_RETURN", "0") == "1"
@@ -245,7 +288,8 @@ def get_exchange(n_experts: int, hidden: int, dtype: torch.dtype, rows: int, n_l
                                "p2p.reset() to change shapes")
         return x
     try:
-        factor = float(os.environ.get("DICE_EP_P2P_CAPACITY", "2.0"))
+        factor = os.environ.get("DICE_EP_P2P_CAPACITY")
+        factor = float(factor) if factor else None
         n_par = int(os.environ.get("DICE_EP_P2P_SLOTS", "3"))
         _exchange = PeerExchange(n_experts, hidden, dtype, max_rows=int(rows * 1.25) + 256, capacity_factor=factor,
                                  n_layers=max(1, n_layers), n_par=n_par)
@@ -259,11 +303,12 @@ def get_exchange(n_experts: int, hidden: int, dtype: torch.dtype, rows: int, n_l
 
 def reset() -> None:
     """Drop the process-wide exchange (a collective decision: every rank calls it)."""
-    global _exchange, _failed
+    global _exchange, _failed, _side_pushes
     if _exchange is not None:
         _exchange.close()
     _exchange = None
     _failed = False
+    _side_pushes = False
 
 
 # ---- stand-ins that travel through the exchange protocol of ep_fwd / diep -------------------

@@ -238,18 +238,21 @@ class ExpertPack:
                 w1 = torch.stack([e.fc1.weight.to(dtype) for e in local]).contiguous()
                 w2 = torch.stack([e.fc2.weight.to(dtype) for e in local]).contiguous()
             if self.status is None:
-                self.status = torch.zeros(1, dtype=torch.int32, device=dev)
+                self.status = ops.device_status(dev)
         built = (act, ffn, w1, w2)
         self._built[dtype] = (sig, built)
         return built
 
-    def run_offsets(self, rows: torch.Tensor, seg_offsets: torch.Tensor, seg_slab: Optional[torch.Tensor] = None):
+    def run_offsets(self, rows: torch.Tensor, seg_offsets: torch.Tensor, seg_slab: Optional[torch.Tensor] = None,
+                    reserve_sms: int = 0):
         act, ffn, w1, w2 = self.get(rows.dtype)
         if not ExpertPack._want_timing():
-            return ops.grouped_ffn(rows, w1, w2, seg_offsets, act, ffn, status=self.status, seg_slab=seg_slab)
+            return ops.grouped_ffn(rows, w1, w2, seg_offsets, act, ffn, status=self.status, seg_slab=seg_slab,
+                                   reserve_sms=reserve_sms)
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         start.record()
-        out = ops.grouped_ffn(rows, w1, w2, seg_offsets, act, ffn, status=self.status, seg_slab=seg_slab)
+        out = ops.grouped_ffn(rows, w1, w2, seg_offsets, act, ffn, status=self.status, seg_slab=seg_slab,
+                              reserve_sms=reserve_sms)
         end.record()
         ExpertPack.timing.append((self.tag, start, end))
         return out
@@ -272,7 +275,7 @@ class ExpertPack:
             rows.data_ptr(), n_rows, h, ffn, ops.ACT_CODES[act], w1.data_ptr(), w2.data_ptr(), w1.shape[0],
             info.seg_dev.data_ptr(), x.seg_slab_dev.data_ptr(), x.world * x.el, inter.data_ptr(), x._meta_ptrs[info.slot],
             info.tab["back"], info.tab["f_back"], x._done_ptrs[2 * info.slot + 1], x.rank, x.world, x.min_peer_rows,
-            info.seq, self.status.data_ptr(), ops._stream()), "dice_grouped_ffn_return")
+            info.seq, 0, self.status.data_ptr(), ops._stream()), "dice_grouped_ffn_return")
         if timing is not None:
             end.record()
             timing.append((self.tag, start, end))
@@ -363,7 +366,7 @@ class SparseMoeBlock(nn.Module):
 
     def _router_status(self, device):
         if self._status is None or self._status.device != device:
-            self._status = torch.zeros(1, dtype=torch.int32, device=device)
+            self._status = ops.device_status(device)
         return self._status
 
     def check_status(self):
@@ -391,13 +394,20 @@ class SparseMoeBlock(nn.Module):
         x = x.contiguous() if x.dtype == cd else x.to(cd)
         n_tokens = x.shape[0]
         assert self.num_experts_per_tok == 2, "the fused router selects exactly two experts per token"
+        if not self.layer_idx:  # once per model forward (first layer, or a block used on its own)
+            ops.poll_status(x.device)
+        reserve = 0
+        if self.para_mode.ep:
+            from .expertpara import p2p
+
+            reserve = p2p.reserve_sms()
         with _scope("moe.gate"):
             topk_idx, topk_weight, hist, _ = ops.router_top2(x, self._gate_weight(cd), renorm=self.gate.norm_topk_prob,
                                                              status=self._router_status(x.device))
         shared_out = None
         if self._shared_pack is not None:
             with _scope("moe.mlp_shared"):
-                shared_out = self._shared_pack.run_offsets(x, self._segment_all(n_tokens, x.device))
+                shared_out = self._shared_pack.run_offsets(x, self._segment_all(n_tokens, x.device), reserve_sms=reserve)
         if not self.para_mode.ep:
             y = self.moe_infer(x, topk_idx.view(-1), topk_weight.view(-1, 1), _addend=shared_out)
         else:

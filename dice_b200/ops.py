@@ -60,6 +60,65 @@ def check_status(status: torch.Tensor, what: str = "dice_b200 kernel") -> None:
         raise RuntimeError(f"{what}: device status {code}: {msg}")
 
 
+class _StatusWord:
+    """The status word every kernel of this process reports to on one device,
+    with a pinned host mirror that is refreshed by asynchronous copies."""
+
+    def __init__(self, device: torch.device):
+        self.dev = torch.zeros(1, dtype=torch.int32, device=device)
+        self.host = torch.zeros(1, dtype=torch.int32).pin_memory()
+        self.event = torch.cuda.Event()
+        self.pending = False
+
+
+_status_words = {}
+
+
+def _status_word(device) -> _StatusWord:
+    device = torch.device(device)
+    if device.index is None:
+        device = torch.device("cuda", torch.cuda.current_device())
+    word = _status_words.get(device)
+    if word is None:
+        word = _status_words[device] = _StatusWord(device)
+    return word
+
+
+def device_status(device) -> torch.Tensor:
+    """The int32 status word shared by the kernels this package launches on
+    ``device`` (the first failure wins; see ``dice_status_message``)."""
+    return _status_word(device).dev
+
+
+def poll_status(device=None) -> None:
+    """Look at the device status word WITHOUT synchronising: raise if the copy
+    enqueued by an earlier call has landed and shows a failure (an expired
+    wait, an exchange buffer that was too small, a peer that gave up), then
+    enqueue the next copy on the current stream.  Called once per model
+    forward and per sampling step by the block and by ``ep_set_step`` /
+    ``ep_cache_clear``, so a failure surfaces within a step or two instead of
+    turning into silently wrong images."""
+    if device is None:
+        device = torch.device("cuda", torch.cuda.current_device())
+    if torch.cuda.is_current_stream_capturing():
+        return
+    word = _status_word(device)
+    if word.pending:
+        if not word.event.query():
+            return
+        word.pending = False
+        code = int(word.host[0])
+        if code != 0:
+            word.dev.zero_()
+            word.host.zero_()
+            raise RuntimeError(f"dice_b200 kernels reported device status {code}: "
+                               + _lib.load().dice_status_message(code).decode())
+    with torch.cuda.device(device):
+        word.host.copy_(word.dev, non_blocking=True)
+        word.event.record()
+    word.pending = True
+
+
 # --------------------------------------------------------------------------- #
 # router
 # --------------------------------------------------------------------------- #
@@ -235,6 +294,7 @@ def grouped_gemm(
     status: torch.Tensor,
     seg_slab: Optional[torch.Tensor] = None,
     out: Optional[torch.Tensor] = None,
+    reserve_sms: int = 0,
 ) -> torch.Tensor:
     """One grouped GEMM stage on the tensor cores (bf16):
     ``out[r] = epilogue(a[r] @ w[slab(seg(r))].T)``."""
@@ -251,7 +311,7 @@ def grouped_gemm(
     _lib.check(
         _lib.load().dice_grouped_gemm(
             _ptr(a), n_rows, k_dim, _ptr(w), n_slabs, w_rows, _ptr(seg_offsets), _ptr(seg_slab), n_seg, epilogue,
-            _ptr(out), out.stride(0), n_out, _ptr(status), _stream(),
+            _ptr(out), out.stride(0), n_out, reserve_sms, _ptr(status), _stream(),
         ),
         "dice_grouped_gemm",
     )
@@ -269,12 +329,14 @@ def grouped_ffn(
     seg_slab: Optional[torch.Tensor] = None,
     inter: Optional[torch.Tensor] = None,
     out: Optional[torch.Tensor] = None,
+    reserve_sms: int = 0,
 ) -> torch.Tensor:
     """Expert FFN over expert-sorted rows (ep_fwd.py:199-211; models.py:368-376).
 
     ``w1``: packed gate/up ``[S, w13_rows(F), h]`` (swiglu) or fc1 ``[S, F, h]``
     (gelu_tanh); ``w2``: ``[S, h, F]``.  bf16 runs on the tensor cores, fp32 on
-    the CUDA cores."""
+    the CUDA cores.  ``reserve_sms`` SMs are left to kernels of other streams
+    (the side-stream pushes of the asynchronous exchange)."""
     _require_cuda(rows, w1, w2, seg_offsets, status, seg_slab, inter, out)
     assert rows.is_contiguous() and w1.is_contiguous() and w2.is_contiguous()
     assert seg_offsets.dtype == torch.int32
@@ -293,7 +355,7 @@ def grouped_ffn(
         _lib.check(
             lib.dice_grouped_ffn(
                 _ptr(rows), n_rows, h, ffn, ACT_CODES[act], _ptr(w1), _ptr(w2), n_slabs, _ptr(seg_offsets),
-                _ptr(seg_slab), n_seg, _ptr(inter), _ptr(out), _ptr(status), _stream(),
+                _ptr(seg_slab), n_seg, _ptr(inter), _ptr(out), reserve_sms, _ptr(status), _stream(),
             ),
             "dice_grouped_ffn",
         )

@@ -31,7 +31,7 @@
 extern "C" {
 #endif
 
-#define DICE_ABI_VERSION 1
+#define DICE_ABI_VERSION 2
 
 #if defined(__GNUC__)
 #define DICE_API __attribute__((visibility("default")))
@@ -67,6 +67,9 @@ DICE_API int dice_abi_version(void);
 DICE_API const char* dice_strerror(int code);
 /* text for a device status word written by a kernel (0 = "ok") */
 DICE_API const char* dice_status_message(uint32_t status);
+/* kernels this library has launched in this process so far (a benchmark reads
+ * it before and after a region to report measured launches) */
+DICE_API uint64_t dice_kernel_launches(void);
 
 /* ---------------------------------------------------------------------------
  * Router: logits -> softmax -> top-2 (+ expert histogram), one fused kernel.
@@ -189,14 +192,18 @@ DICE_API int dice_pack_w13(const void* gate_proj, const void* up_proj, int hidde
  *   out          [n_rows, ld_out]           bf16; columns [0, n_out)
  *   n_out        logical output width: w_rows for STORE/GELU_TANH, ffn for
  *                SWIGLU (where w_rows = dice_w13_rows(ffn))
+ *   reserve_sms  SMs the persistent kernel leaves free for kernels of other
+ *                streams (0 = use the whole GPU).  The asynchronous exchange
+ *                runs its pushes on those SMs next to the expert FFN
+ *                (diep.py:219-259, :284-310 overlap the all-to-all with compute).
  *   status       device uint32, non-zero after a bounded wait expired
  * k_dim, ld_out, n_out multiples of 8; n_seg <= 256.  The tile list is derived
  * on the device from seg_offsets, so no host synchronisation is needed.
  */
 DICE_API int dice_grouped_gemm(const void* a, int64_t n_rows, int k_dim, const void* w, int n_slabs,
                       int64_t w_rows, const int32_t* seg_offsets, const int32_t* seg_slab, int n_seg,
-                      int epilogue, void* out, int64_t ld_out, int n_out, uint32_t* status,
-                      void* stream);
+                      int epilogue, void* out, int64_t ld_out, int n_out, int reserve_sms,
+                      uint32_t* status, void* stream);
 
 /* The expert FFN over expert-sorted rows: two dice_grouped_gemm launches
  * (ep_fwd.py:199-211 proc_experts; models.py:368-376).
@@ -206,7 +213,8 @@ DICE_API int dice_grouped_gemm(const void* a, int64_t n_rows, int k_dim, const v
  */
 DICE_API int dice_grouped_ffn(const void* rows_in, int64_t n_rows, int hidden, int ffn, int act, const void* w1,
                      const void* w2, int n_slabs, const int32_t* seg_offsets, const int32_t* seg_slab,
-                     int n_seg, void* inter, void* rows_out, uint32_t* status, void* stream);
+                     int n_seg, void* inter, void* rows_out, int reserve_sms, uint32_t* status,
+                     void* stream);
 
 /* fp32 variant of the expert FFN on the CUDA cores (no tensor-core rounding;
  * used where fp32 parity at 1e-5 is asked for).  Same arguments as
@@ -228,17 +236,29 @@ DICE_API int dice_grouped_ffn_f32(const void* rows_in, int64_t n_rows, int hidde
  *   keys are (owner rank, local slot) = owner * (n_experts / world) + slot, so
  *   seg_offsets [n_experts+1] (from dice_permute_plan on those keys) lists this
  *   rank's rows per destination;
+ *   flag arrays: every entry of a `peer_flags` table points at 64 uint32 words
+ *   of that peer: [0, world) the flags, [32, 32 + world) failure marks (a push
+ *   that could not complete writes its sequence number there before raising the
+ *   flag; the waiting peer then records "a peer rank reported ...");
  *   meta: int32 [dice_ep_meta_ints(world, n_experts/world)], written by
- *   dice_ep_exchange_counts: send_base[W] | back_base[W] | src_off[W+1] |
- *   seg_off[W*El+1] (segments of the receive buffer in (source, slot) order,
- *   ready for dice_grouped_ffn with seg_slab[s*El+i] = i) | total, overflow;
+ *   dice_ep_exchange_counts: total rows received | state (0 ok, 1 a receive
+ *   buffer is too small, 2 the peers' counts never arrived) | send_base[W] |
+ *   back_base[W] | src_off[W+1] | seg_off[W*El+1] (segments of the receive
+ *   buffer in (source, slot) order, ready for dice_grouped_ffn with
+ *   seg_slab[s*El+i] = i).  Every rank holds the whole count matrix, so a
+ *   receive buffer that is too small ANYWHERE is found by every rank: all of
+ *   them record the overflow status and the exchange then moves no rows (the
+ *   reference has no capacity and never drops a row: size the buffers so that
+ *   this cannot happen, capacity_rows = world * the largest sender is always
+ *   enough);
  *   seq: a number that grows with every use of the same buffers;
  *   done_counter: device uint32, zero before first use, one per call site;
- *   max_ctas: 0 = the push has the GPU to itself: rows move through shared
- *   memory with the copy unit (cp.async.bulk), one warp per SM; > 0 = SIMT push
- *   with at most that many CTAs, < 0 = SIMT push sized by the rows: a push that
- *   runs next to a GEMM on another stream needs the SIMT form (no shared
- *   memory, fits beside the GEMM's CTAs) and should be small.
+ *   max_ctas selects the form of a push: 0 = the push has the GPU to itself:
+ *   rows move through shared memory with the copy unit (cp.async.bulk), one
+ *   warp per SM; > 0 = the same with at most that many CTAs (rounded up to an
+ *   even number, four warps each), for a push that runs on another stream next
+ *   to an expert FFN which was given reserve_sms = max_ctas; -1 = SIMT push (no
+ *   shared memory) sized by the rows, < -1 = SIMT push of at most -max_ctas CTAs.
  */
 DICE_API int dice_ep_meta_ints(int world, int n_local_experts);
 DICE_API int dice_ep_exchange_counts(const int32_t* seg_offsets, const void* const* peer_matrices,
@@ -252,11 +272,13 @@ DICE_API int dice_ep_dispatch_rows(const void* x, const int32_t* pos, const int3
                           const void* const* peer_flags, uint32_t* done_counter, int64_t n_tokens,
                           int k, int hidden, int dtype, int rank, int world, int n_experts,
                           int capacity_rows, uint32_t seq, int max_ctas, uint32_t* status, void* stream);
-/* wait (bounded) until every source raised flag >= seq; what: 0 dispatch, 1 combine */
+/* wait (bounded) until every source raised flag >= seq, then look at the
+ * sources' failure marks; what: 0 dispatch, 1 combine */
 DICE_API int dice_ep_wait_flags(const uint32_t* my_flags, int world, uint32_t seq, int what,
                        uint32_t* status, void* stream);
 /* expert outputs back to the token owners, in the order the rows were sent
- * (ep_fwd.py:326-340); max_rows bounds the rows received (grid sizing only) */
+ * (ep_fwd.py:326-340); max_rows = rows the buffer `rows` holds (nothing beyond
+ * it is read) */
 DICE_API int dice_ep_return_rows(const void* rows, const int32_t* meta, const void* const* peer_back,
                         const void* const* peer_flags, uint32_t* done_counter, int hidden, int dtype,
                         int rank, int world, int back_capacity_rows, int max_rows, uint32_t seq,
@@ -272,7 +294,7 @@ DICE_API int dice_grouped_ffn_return(const void* rows_in, int64_t n_rows, int hi
                             const int32_t* seg_slab, int n_seg, void* inter, const int32_t* meta,
                             const void* const* peer_back, const void* const* peer_flags,
                             uint32_t* done_counter, int rank, int world, int back_capacity_rows,
-                            uint32_t seq, uint32_t* status, void* stream);
+                            uint32_t seq, int reserve_sms, uint32_t* status, void* stream);
 /* CUDA IPC plumbing for the above (set-up time): export the allocation that
  * holds `ptr` (64-byte handle + offset of ptr inside it); import maps a peer's
  * allocation into this process and enables peer access. */

@@ -2,7 +2,7 @@
 
 Every function cites the reference lines it follows (paths are relative to the
 reference project's root).  The restatement is checked against the reference's
-own modules by ``tests/test_oracle_vs_reference.py`` whenever the reference
+own modules by ``tests/test_oracle_golden.py`` whenever the reference
 checkout is present, and against the fixtures under ``tests/golden`` (generated
 from the reference by ``tests/golden/make_golden.py``) everywhere else.
 

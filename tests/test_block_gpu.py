@@ -118,47 +118,70 @@ def test_empty_and_single_token_batches(cuda_device):
 
 
 def test_ep_world_of_one_on_gpu(cuda_device):
-    """The expert-parallel code path on one GPU (NCCL world of one rank): the
-    synchronous exchange equals the single-device block; the displaced
-    exchange returns the result of two steps earlier."""
+    """The expert-parallel code path on one GPU (NCCL world of one rank, once over NCCL and once over the
+    peer-memory exchange): the synchronous exchange equals the single-device block at every step; the displaced
+    exchange returns the result of two steps earlier and the interweaved one (two layers) that of one step
+    earlier, at EVERY step (diep.py:196-310; the reference's tests/test_ep.py:113-121 pins the displaced case).
+    The blocks have no shared expert, so the whole output is stale and is compared bit for bit."""
     import socket
 
     import torch.distributed as dist
 
-    from dice_b200.expertpara import diep, ep_fwd
+    from dice_b200.expertpara import diep, ep_fwd, p2p
     from dice_b200.moe_block import ParaMode, SparseMoeBlock
 
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
         port = s.getsockname()[1]
     dist.init_process_group("nccl", init_method=f"tcp://127.0.0.1:{port}", world_size=1, rank=0)
+    h, e, layers, steps = 64, 8, 2, 6
     try:
-        g, sd = _small()
-        ref_blk = _block(32, 8, sd, cuda_device, torch.bfloat16)
-        xs = [torch.randn(2, 77, 32, device=cuda_device, generator=torch.Generator(device="cuda").manual_seed(i)).bfloat16()
-              for i in range(5)]
-        want = [ref_blk(x) for x in xs]
-        for async_mode in (False, True):
-            pm = ParaMode(ep=True, ep_async=async_mode, ep_async_mode="all", ep_async_warm_up=0, strided_sync=0,
-                          ep_async_cool_down=0)
-            blk = SparseMoeBlock(32, 4, 8, 2, 1, 0, 1, pm)
-            blk.load_state_dict(sd)
-            blk = blk.to(device=cuda_device, dtype=torch.bfloat16).eval()
-            diep.ep_cache_init(1, selective_async_strategy="all")
-            ep_fwd.use_latest_expert_weights(False)
-            for i, x in enumerate(xs):
-                if async_mode and i == 0:
-                    diep.diep_force_sync()
-                y = blk(x)
-                if async_mode and i == 0:
-                    diep.diep_cancel_sync()
-                # stale rows arrive two steps late; the always-fresh shared expert does not
-                src = max(0, i - 2) if async_mode else i
-                if src == i:
-                    torch.testing.assert_close(y.float(), want[i].float(), rtol=2e-2, atol=2e-2)
-            blk.check_status()
-            assert diep.ep_cached_tensors_size() >= 0
+        def make(pm, layer):
+            torch.manual_seed(50 + layer)
+            blk = SparseMoeBlock(h, 4, e, 2, 1, layer, layers, pm, shared_expert=False)
+            return blk.to(device=cuda_device, dtype=torch.bfloat16).eval()
+
+        g = torch.Generator(device="cuda").manual_seed(11)
+        xs = [[torch.randn(2, 77 + 5 * l, h, device=cuda_device, generator=g).bfloat16() for l in range(layers)]
+              for _ in range(steps)]
+        ref = [make(ParaMode(), l) for l in range(layers)]
+        want = [[ref[l](xs[t][l]) for l in range(layers)] for t in range(steps)]
+        for l in range(layers):  # inputs differ enough between steps for a wrong staleness to show
+            assert not torch.allclose(want[0][l].float(), want[1][l].float(), atol=1e-2)
+        a = dict(ep=True, ep_async=True, ep_async_mode="all", ep_async_warm_up=0, strided_sync=0, ep_async_cool_down=0)
+        cases = [
+            ("sync", ParaMode(ep=True), {}, lambda t: t),
+            ("displaced", ParaMode(**a), dict(async_pipeline=False, selective_async_strategy="all"), lambda t: max(0, t - 2)),
+            ("interweaved", ParaMode(**a), dict(async_pipeline=True, selective_async_strategy="all"), lambda t: max(0, t - 1)),
+        ]
+        for use_peer_memory in (False, True):
+            p2p.enable(use_peer_memory)
+            for name, pm, cache_kw, source_step in cases:
+                blocks = [make(pm, l) for l in range(layers)]
+                diep.ep_cache_init(layers, **cache_kw)
+                ep_fwd.use_latest_expert_weights(False)
+                for t in range(steps):
+                    diep.ep_set_step(steps - t)
+                    forced = pm.ep_async and t == 0
+                    if forced:
+                        diep.diep_force_sync()
+                        diep.ep_cache_clear()
+                    for l in range(layers):
+                        y = blocks[l](xs[t][l])
+                        src = source_step(t)
+                        assert y.shape == xs[t][l].shape
+                        assert torch.equal(y, want[src][l]), f"{name} peer={use_peer_memory} step {t} layer {l}"
+                    if forced:
+                        diep.diep_cancel_sync()
+                for b in blocks:
+                    b.check_status()
+                assert diep.ep_cached_tensors_size() >= 0
+            if use_peer_memory:
+                assert p2p._exchange is not None and p2p._exchange.lossless
+                p2p._exchange.check()
     finally:
+        p2p.enable(False)
+        p2p.reset()
         dist.destroy_process_group()
         ep_fwd._use_latest_expert_weights = None
 

@@ -363,8 +363,9 @@ def test_exchange_world_of_one(cuda_device):
         assert torch.equal(recv[: 2 * n], want) and torch.equal(back, want)
         assert bool((recv[2 * n:] == 3.0).all())
         m = meta.cpu().tolist()
-        assert m[0] == 0 and m[1] == 0 and m[2:4] == [0, 2 * n]           # send_base, back_base, src_off
-        assert m[4:4 + e + 1] == seg.cpu().tolist() and m[4 + e + 1] == 2 * n and m[4 + e + 2] == 0
+        assert m[0] == 2 * n and m[1] == 0                                # rows received, state
+        assert m[2] == 0 and m[3] == 0 and m[4:6] == [0, 2 * n]           # send_base, back_base, src_off
+        assert m[6:6 + e + 1] == seg.cpu().tolist()
     # a receive buffer that is too small is reported, not overrun
     assert lib.dice_ep_exchange_counts(seg.data_ptr(), tab(ctrl.data_ptr()), tab(f(0)), meta.data_ptr(), 0, 1, e, 100, 3,
                                        status.data_ptr(), st) == 0
@@ -378,8 +379,9 @@ def test_exchange_world_of_one(cuda_device):
                                          (333, 1152, 2, torch.float32), (129, 1792, 1, torch.bfloat16),
                                          (5, 64, 2, torch.bfloat16), (4097, 1152, 2, torch.bfloat16)])
 def test_exchange_bulk_copy_pushes_equal_simt_pushes(cuda_device, n, h, k, dtype):
-    """Dispatch and return exist twice: SIMT kernels (max_ctas != 0) and kernels that move the rows with
-    cp.async.bulk through shared memory (max_ctas == 0).  World of one rank, a tenth of the rows left out
+    """Dispatch and return exist in three forms: SIMT kernels (max_ctas < 0), kernels that move the rows with
+    cp.async.bulk through shared memory on every SM (max_ctas == 0), and the same on a few four-warp CTAs
+    launched as clusters of two (max_ctas > 0, the form that runs next to the expert FFN).  World of one rank, a tenth of the rows left out
     (expert -1, as conditional communication does): both forms must write the same bytes and touch nothing else."""
     import ctypes
 
@@ -400,7 +402,7 @@ def test_exchange_bulk_copy_pushes_equal_simt_pushes(cuda_device, n, h, k, dtype
     st = torch.cuda.current_stream().cuda_stream
     tab = lambda p: (ctypes.c_void_p * 1)(p)
     outs = []
-    for max_ctas in (0, -1):
+    for max_ctas in (0, -1, 6):
         ctrl = torch.zeros(e + 3 * 64, dtype=torch.int32, device=cuda_device)
         recv = torch.full((cap, h), 3.0, dtype=dtype, device=cuda_device)
         back = torch.full((cap, h), 5.0, dtype=dtype, device=cuda_device)
@@ -422,8 +424,9 @@ def test_exchange_bulk_copy_pushes_equal_simt_pushes(cuda_device, n, h, k, dtype
         torch.cuda.synchronize()
         ops.check_status(status)
         outs.append((recv.clone(), back.clone()))
-    (recv_bulk, back_bulk), (recv_simt, back_simt) = outs
+    (recv_bulk, back_bulk), (recv_simt, back_simt), (recv_few, back_few) = outs
     assert torch.equal(recv_bulk, recv_simt) and torch.equal(back_bulk, back_simt)
+    assert torch.equal(recv_bulk, recv_few) and torch.equal(back_bulk, back_few)
     assert bool((recv_bulk[rows:] == 3.0).all()) and bool((back_bulk[rows:] == 5.0).all())
     # and the rows are the permutation of x: row r of the receive order is the token whose slot has pos == r
     p = pos.cpu().view(n, k)
@@ -437,13 +440,13 @@ def test_exchange_bulk_copy_pushes_equal_simt_pushes(cuda_device, n, h, k, dtype
 
 
 @pytest.mark.parametrize("world", [2, 4, 8])
-@pytest.mark.parametrize("max_ctas", [0, -1])
+@pytest.mark.parametrize("max_ctas", [0, -1, 4])
 def test_exchange_of_emulated_ranks_on_one_gpu(cuda_device, world, max_ctas):
     """The whole exchange for `world` ranks whose buffers all live on this GPU.  The count matrices and count
     flags are filled in beforehand and every push is launched before the first wait, so no kernel ever waits
     for a later one.  With the identity as expert FFN, every rank must get back exactly its own key-sorted
     rows, and every receive buffer must hold its sources' rows in (source, slot) order.  max_ctas 0: bulk-copy
-    pushes, -1: SIMT pushes."""
+    pushes, -1: SIMT pushes, 4: bulk-copy pushes on at most four CTAs."""
     import ctypes
 
     from dice_b200 import _lib
@@ -507,6 +510,191 @@ def test_exchange_of_emulated_ranks_on_one_gpu(cuda_device, world, max_ctas):
         assert bool((recv[d][recv_rows[d]:] == 3.0).all())
 
 
+class _EmulatedRanks:
+    """Buffers of `world` ranks on one GPU for the exchange kernels, as PeerExchange lays them out per slot."""
+
+    def __init__(self, world, e, h, cap, back_cap, device, lib):
+        import ctypes
+
+        self.world, self.e, self.el, self.h, self.cap, self.back_cap = world, e, e // world, h, cap, back_cap
+        self.flag_base = world * e
+        self.ctrl = [torch.zeros(self.flag_base + 3 * 64, dtype=torch.int32, device=device) for _ in range(world)]
+        self.recv = [torch.full((cap + 4, h), 3.0, dtype=torch.bfloat16, device=device) for _ in range(world)]  # 4 guard rows
+        self.back = [torch.full((back_cap + 4, h), 5.0, dtype=torch.bfloat16, device=device) for _ in range(world)]
+        self.meta = [torch.zeros(lib.dice_ep_meta_ints(world, self.el), dtype=torch.int32, device=device) for _ in range(world)]
+        self.done = [torch.zeros(2, dtype=torch.int32, device=device) for _ in range(world)]
+        self.status = [torch.zeros(1, dtype=torch.int32, device=device) for _ in range(world)]
+        self._ct = ctypes
+
+    def table(self, ptrs):
+        return (self._ct.c_void_p * self.world)(*ptrs)
+
+    def flags(self, which):
+        return self.table([c.data_ptr() + (self.flag_base + 64 * which) * 4 for c in self.ctrl])
+
+    def my_flags(self, r, which):
+        return self.ctrl[r].data_ptr() + (self.flag_base + 64 * which) * 4
+
+    def publish_counts(self, seg_host, seq, ranks=None):
+        """What the count kernels of `ranks` would publish on every peer, and the flags that say so."""
+        e = self.e
+        for r in (range(self.world) if ranks is None else ranks):
+            row = torch.tensor([seg_host[r][i + 1] - seg_host[r][i] for i in range(e)], dtype=torch.int32)
+            for d in range(self.world):
+                self.ctrl[d][r * e:(r + 1) * e] = row.to(self.ctrl[d].device)
+                self.ctrl[d][self.flag_base + r] = seq
+
+
+def _emulated_inputs(world, e, h, n, k, device, seed, hot_owner=None):
+    ops = _ops()
+    el = e // world
+    g = torch.Generator().manual_seed(seed)
+    xs, poss, segs = [], [], []
+    for r in range(world):
+        x = torch.randn(n[r], h, generator=g).bfloat16().to(device)
+        expert = torch.randint(0, e, (k * n[r],), generator=g)
+        if hot_owner is not None:  # three quarters of the rows go to one rank's experts
+            hot = torch.rand(k * n[r], generator=g) < 0.75
+            expert[hot] = hot_owner + world * torch.randint(0, el, (int(hot.sum()),), generator=g)
+        key = (expert % world) * el + expert // world
+        pos, seg, _ = ops.permute_plan(key.to(device), e)
+        xs.append(x); poss.append(pos); segs.append(seg)
+    return xs, poss, segs
+
+
+@pytest.mark.parametrize("max_ctas", [0, -1, 4])
+def test_exchange_overflow_is_found_by_every_rank_and_touches_nothing(cuda_device, max_ctas):
+    """A routing that sends one rank more rows than its receive buffer holds (the reference has no capacity,
+    ep_fwd.py:247-293, so this can only be reported, not reproduced): every rank records the overflow in the
+    count exchange, the pushes and the return then move nothing, the guard rows behind every buffer stay
+    untouched, and no flag is left unraised."""
+    from dice_b200 import _lib
+
+    ops = _ops()
+    lib = _lib.load()
+    world, e, h, k = 4, 8, 256, 2
+    n = [400, 380, 420, 390]
+    xs, poss, segs = _emulated_inputs(world, e, h, n, k, cuda_device, seed=21, hot_owner=2)
+    seg_host = [s.cpu().tolist() for s in segs]
+    el = e // world
+    recv_rows = [sum(seg_host[s][(d + 1) * el] - seg_host[s][d * el] for s in range(world)) for d in range(world)]
+    cap = 2 * max(n)  # what two average senders fill: too small for the hot rank
+    assert recv_rows[2] > cap > max(recv_rows[:2] + recv_rows[3:])
+    R = _EmulatedRanks(world, e, h, cap, k * max(n), cuda_device, lib)
+    st = torch.cuda.current_stream().cuda_stream
+    seq = 1
+    R.publish_counts(seg_host, seq)
+    for r in range(world):
+        assert lib.dice_ep_exchange_counts(segs[r].data_ptr(), R.table([c.data_ptr() for c in R.ctrl]), R.flags(0),
+                                           R.meta[r].data_ptr(), r, world, e, cap, seq, R.status[r].data_ptr(), st) == 0
+    for r in range(world):
+        assert lib.dice_ep_dispatch_rows(xs[r].data_ptr(), poss[r].data_ptr(), segs[r].data_ptr(), R.meta[r].data_ptr(),
+                                         R.table([t.data_ptr() for t in R.recv]), R.flags(1), R.done[r].data_ptr(), n[r], k,
+                                         h, 0, r, world, e, cap, seq, max_ctas, R.status[r].data_ptr(), st) == 0
+    for r in range(world):
+        assert lib.dice_ep_wait_flags(R.my_flags(r, 1), world, seq, 0, R.status[r].data_ptr(), st) == 0
+    for r in range(world):
+        assert lib.dice_ep_return_rows(R.recv[r].data_ptr(), R.meta[r].data_ptr(), R.table([t.data_ptr() for t in R.back]),
+                                       R.flags(2), R.done[r][1:].data_ptr(), h, 0, r, world, R.back_cap, cap, seq, max_ctas,
+                                       R.status[r].data_ptr(), st) == 0
+    for r in range(world):
+        assert lib.dice_ep_wait_flags(R.my_flags(r, 2), world, seq, 1, R.status[r].data_ptr(), st) == 0
+    torch.cuda.synchronize()
+    for r in range(world):
+        m = R.meta[r].cpu().tolist()
+        assert m[0] == 0 and m[1] == 1, f"rank {r}: meta head {m[:2]}"                  # no rows, state = overflow
+        assert all(v == 0 for v in m[2 + 3 * world + 1:]), "segments must be empty"
+        with pytest.raises(RuntimeError, match="more rows"):
+            ops.check_status(R.status[r])
+        assert bool((R.recv[r] == 3.0).all()) and bool((R.back[r] == 5.0).all()), f"rank {r}: a buffer was written"
+        assert int(R.done[r].sum()) == 0
+
+
+@pytest.mark.parametrize("max_ctas", [0, -1])
+def test_exchange_failure_reaches_the_peers(cuda_device, max_ctas):
+    """Failure detection without a fault: rank 1 of two never publishes its counts, so rank 0's count exchange
+    runs out of time (bounded wait).  Rank 0's dispatch then marks its push as failed before it raises the
+    flags, and the rank that waits for those rows records "a peer rank reported ..." instead of consuming
+    incomplete rows with a clean status."""
+    import time
+
+    from dice_b200 import _lib
+
+    ops = _ops()
+    lib = _lib.load()
+    world, e, h, k = 2, 8, 128, 2
+    n = [200, 200]
+    xs, poss, segs = _emulated_inputs(world, e, h, n, k, cuda_device, seed=22)
+    seg_host = [s.cpu().tolist() for s in segs]
+    R = _EmulatedRanks(world, e, h, 4 * max(n), k * max(n), cuda_device, lib)
+    st = torch.cuda.current_stream().cuda_stream
+    seq = 1
+    t0 = time.time()
+    assert lib.dice_ep_exchange_counts(segs[0].data_ptr(), R.table([c.data_ptr() for c in R.ctrl]), R.flags(0),
+                                       R.meta[0].data_ptr(), 0, world, e, R.cap, seq, R.status[0].data_ptr(), st) == 0
+    assert lib.dice_ep_dispatch_rows(xs[0].data_ptr(), poss[0].data_ptr(), segs[0].data_ptr(), R.meta[0].data_ptr(),
+                                     R.table([t.data_ptr() for t in R.recv]), R.flags(1), R.done[0].data_ptr(), n[0], k, h, 0,
+                                     0, world, e, R.cap, seq, max_ctas, R.status[0].data_ptr(), st) == 0
+    # rank 1's own push is played by hand: its dispatch flag on rank 1 is up, so that only rank 0's mark matters
+    R.ctrl[1][R.flag_base + 64 + 1] = seq
+    assert lib.dice_ep_wait_flags(R.my_flags(1, 1), world, seq, 0, R.status[1].data_ptr(), st) == 0
+    torch.cuda.synchronize()
+    assert 1.0 < time.time() - t0 < 15.0
+    assert R.meta[0].cpu().tolist()[:2] == [0, 2]  # no rows, state = the peers' counts never arrived
+    with pytest.raises(RuntimeError, match="row counts"):
+        ops.check_status(R.status[0])
+    with pytest.raises(RuntimeError, match="peer rank reported"):
+        ops.check_status(R.status[1])
+    assert bool((R.recv[0] == 3.0).all()) and bool((R.recv[1] == 3.0).all())
+    # the next exchange on the same buffers is clean again (marks carry the sequence number of the failure)
+    seq = 2
+    R.publish_counts(seg_host, seq)
+    for r in range(world):
+        assert lib.dice_ep_exchange_counts(segs[r].data_ptr(), R.table([c.data_ptr() for c in R.ctrl]), R.flags(0),
+                                           R.meta[r].data_ptr(), r, world, e, R.cap, seq, R.status[r].data_ptr(), st) == 0
+    for r in range(world):
+        assert lib.dice_ep_dispatch_rows(xs[r].data_ptr(), poss[r].data_ptr(), segs[r].data_ptr(), R.meta[r].data_ptr(),
+                                         R.table([t.data_ptr() for t in R.recv]), R.flags(1), R.done[r].data_ptr(), n[r], k,
+                                         h, 0, r, world, e, R.cap, seq, max_ctas, R.status[r].data_ptr(), st) == 0
+    for r in range(world):
+        assert lib.dice_ep_wait_flags(R.my_flags(r, 1), world, seq, 0, R.status[r].data_ptr(), st) == 0
+    torch.cuda.synchronize()
+    for r in range(world):
+        ops.check_status(R.status[r])
+
+
+def test_status_is_polled_without_a_synchronisation(cuda_device):
+    """ops.poll_status: a status a kernel left on the device surfaces as an exception one or two polls later,
+    with no host synchronisation in between (the word travels through a pinned mirror)."""
+    ops = _ops()
+    word = ops.device_status(cuda_device)
+    torch.cuda.synchronize()
+    word.zero_()
+    ops.poll_status(cuda_device)
+    torch.cuda.synchronize()
+    ops.poll_status(cuda_device)  # clean
+    # non-monotone segments make the grouped GEMM record a status on the shared word
+    a = torch.zeros(256, 64, dtype=torch.bfloat16, device=cuda_device)
+    w = torch.zeros(2, 32, 64, dtype=torch.bfloat16, device=cuda_device)
+    seg = torch.tensor([0, 200, 100], dtype=torch.int32, device=cuda_device)
+    ops.grouped_gemm(a, w, seg, ops.EPI_STORE, 32, word)
+    raised = False
+    for _ in range(3):
+        try:
+            ops.poll_status(cuda_device)
+        except RuntimeError as exc:
+            assert "segment offsets" in str(exc)
+            raised = True
+            break
+        torch.cuda.synchronize()  # only so that the test does not depend on timing; the poll itself never waits
+    assert raised
+    torch.cuda.synchronize()
+    assert int(word.item()) == 0
+    ops.poll_status(cuda_device)
+    torch.cuda.synchronize()
+    ops.poll_status(cuda_device)
+
+
 def test_ffn_with_fused_return_world_of_one(cuda_device):
     """dice_grouped_ffn_return on one GPU: the rows the second GEMM sends "home"
     land where the separate return kernel would put them and equal the plain
@@ -541,10 +729,10 @@ def test_ffn_with_fused_return_world_of_one(cuda_device):
         back.zero_()
         assert lib.dice_ep_exchange_counts(seg.data_ptr(), tab(ctrl.data_ptr()), tab(f_cnt), meta.data_ptr(), 0, 1, e,
                                            2 * n, seq, status.data_ptr(), st) == 0
-        seg_dev = meta[4:4 + e + 1]
+        seg_dev = meta[6:6 + e + 1]
         assert lib.dice_grouped_ffn_return(rows.data_ptr(), 2 * n, h, f, 0, w1.data_ptr(), w2.data_ptr(), e,
                                            seg_dev.data_ptr(), slab.data_ptr(), e, inter.data_ptr(), meta.data_ptr(),
-                                           tab(back.data_ptr()), tab(f_back), done[1:].data_ptr(), 0, 1, 2 * n, seq,
+                                           tab(back.data_ptr()), tab(f_back), done[1:].data_ptr(), 0, 1, 2 * n, seq, 0,
                                            status.data_ptr(), st) == 0
         assert lib.dice_ep_wait_flags(f_back, 1, seq, 1, status.data_ptr(), st) == 0
         torch.cuda.synchronize()

@@ -1,0 +1,207 @@
+"""Parity at the shapes the benchmark configurations name, on one GPU, through
+the C ABI against the CPU oracle:
+
+* the DiT-G/2 shapes (hidden 1792 as the benchmark states it, 1408 as the
+  reference builds it, ``models.py:769-770``; 16 experts, F = 4h) for the
+  grouped expert FFN in the single-device layout, in the expert-parallel
+  receive layout (``(source, slot)`` segments resolved through ``seg_slab``,
+  ``ep_fwd.py:199-211``) and for the whole block;
+* the full DiT-XL/2 block of the headline benchmark line (16384 tokens,
+  hidden 1152, 8 experts, both expert variants, bf16) against the oracle, not
+  only through size-independent properties;
+* the dtype flow the reference samples in (``sample_ddp.py:97-98, 228``:
+  half-precision parameters inside an autocast region).
+
+Tolerances: routing exact on the kernel's own logits, every disagreement with
+the oracle's own logits a one-ulp near-tie (< 2 % of tokens); activations
+2e-2 relative (bf16).
+"""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import moe_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+def _ops():
+    from dice_b200 import ops
+
+    return ops
+
+
+def _segments(counts, device):
+    return torch.tensor([0] + list(np.cumsum(counts)), dtype=torch.int32, device=device)
+
+
+def _rel(a, b):
+    return ((a - b).norm() / b.norm()).item()
+
+
+def _make_experts(n, h, f, act, gen, device):
+    """bf16 expert weights on the device (returned packed for the kernels) and as CPU bf16 tensors (oracle)."""
+    ops = _ops()
+    mk = lambda *shape: (torch.randn(*shape, generator=gen, device=device) / math.sqrt(shape[-1])).bfloat16()
+    if act == "swiglu":
+        experts = [(mk(f, h), mk(f, h), mk(h, f)) for _ in range(n)]
+        w1 = torch.stack([ops.pack_w13(e[0], e[1]) for e in experts])
+        w2 = torch.stack([e[2] for e in experts])
+    else:
+        experts = [(mk(f, h), mk(h, f)) for _ in range(n)]
+        w1 = torch.stack([e[0] for e in experts])
+        w2 = torch.stack([e[1] for e in experts])
+    return w1, w2, [[t.cpu() for t in e] for e in experts]
+
+
+def _check_ffn(cuda_device, h, f, act, n_slabs, counts, seg_slab):
+    ops = _ops()
+    gen = torch.Generator(device=cuda_device).manual_seed(h + f + len(counts))
+    w1, w2, experts = _make_experts(n_slabs, h, f, act, gen, cuda_device)
+    r = sum(counts)
+    x = torch.randn(r, h, generator=gen, device=cuda_device).bfloat16()
+    seg = _segments(counts, cuda_device)
+    slab_dev = None if seg_slab is None else torch.tensor(seg_slab, dtype=torch.int32, device=cuda_device)
+    status = torch.zeros(1, dtype=torch.int32, device=cuda_device)
+    out = torch.full((r + 2, h), 7.0, dtype=torch.bfloat16, device=cuda_device)  # canary rows
+    ops.grouped_ffn(x, w1, w2, seg, act, f, status, seg_slab=slab_dev, out=out)
+    torch.cuda.synchronize()
+    ops.check_status(status)
+    assert bool((out[r:] == 7.0).all())
+    xc, got = x.cpu().float(), out[:r].cpu().float()
+    offs = seg.cpu().tolist()
+    for s in range(len(counts)):
+        if counts[s] == 0:
+            continue
+        slab = s if seg_slab is None else seg_slab[s]
+        want = O.run_expert(xc[offs[s]:offs[s + 1]], [t.float() for t in experts[slab]], act)
+        err = _rel(got[offs[s]:offs[s + 1]], want)
+        assert err < 2e-2, f"segment {s} (slab {slab}, {counts[s]} rows): relative error {err}"
+
+
+@pytest.mark.parametrize("act", ["swiglu", "gelu_tanh"])
+@pytest.mark.parametrize("h", [1792, 1408])
+def test_grouped_ffn_g2_receive_layout(cuda_device, act, h):
+    """Expert-parallel receive layout of the G/2 configurations on 8 ranks: 16 experts -> 2 local slots, 8
+    sources -> 16 (source, slot) segments that alternate between the two weight slabs; ragged, one empty, one
+    longer than a 256-row tile pair, K = 28 (22) k-blocks, F = 28 (22) n-blocks."""
+    counts = [130, 257, 0, 64, 1, 300, 255, 256, 31, 129, 7, 513, 96, 128, 2, 77]
+    _check_ffn(cuda_device, h, 4 * h, act, 2, counts, [i for _ in range(8) for i in range(2)])
+
+
+@pytest.mark.parametrize("act", ["swiglu", "gelu_tanh"])
+def test_grouped_ffn_g2_sixteen_experts(cuda_device, act):
+    """Single-device layout of the G/2 block: 16 experts, one segment each (one empty)."""
+    counts = [97, 140, 0, 260, 33, 128, 129, 5, 256, 64, 200, 1, 90, 310, 17, 66]
+    _check_ffn(cuda_device, 1408, 5632, act, 16, counts, None)
+
+
+def test_grouped_ffn_many_small_segments(cuda_device):
+    """16 local slots x 8 sources = 128 segments of 0..40 rows each: every segment needs a tile of its own."""
+    g = torch.Generator().manual_seed(5)
+    counts = torch.randint(0, 41, (128,), generator=g).tolist()
+    counts[3] = counts[64] = 0
+    _check_ffn(cuda_device, 1408, 5632, "swiglu", 16, counts, [i for _ in range(8) for i in range(16)])
+
+
+def _near_tie_only(idx, idx_o, logits_o):
+    """Every token whose selection differs from the oracle's must owe that to logits one bf16 ulp apart."""
+    lo = logits_o.float()
+    ulp = torch.maximum(lo.abs(), torch.tensor(2.0 ** -126)).log2().floor().exp2() * 2.0 ** -7
+    mism = (idx != idx_o).any(-1)
+    for t in mism.nonzero().flatten().tolist():
+        a = set(idx[t].tolist()) ^ set(idx_o[t].tolist())
+        if not a:  # same two experts, slot order decided by a tie
+            a = set(idx[t].tolist())
+        vals = lo[t, sorted(a)]
+        assert (vals.max() - vals.min()).abs() <= 2 * ulp[t].max() + 4e-5, f"token {t}: {idx[t]} vs {idx_o[t]}"
+    return mism.float().mean().item()
+
+
+def _block_against_oracle(cuda_device, h, e, variant, batch, tokens):
+    from dice_b200.moe_block import ParaMode, SparseMoeBlock
+
+    ops = _ops()
+    torch.manual_seed(0)
+    with torch.device(cuda_device):
+        blk = SparseMoeBlock(h, 4, e, 2, 1, 0, 1, ParaMode(), expert_act=variant, shared_expert=(variant == "swiglu"))
+    blk = blk.to(torch.bfloat16).eval()
+    gen = torch.Generator(device=cuda_device).manual_seed(2)
+    for p in blk.parameters():
+        p.data.normal_(0.0, 0.02, generator=gen)
+    blk.gate.norm_topk_prob = variant == "gelu_tanh"
+    x = torch.randn(batch, tokens, h, generator=gen, device=cuda_device).bfloat16()
+    y = blk(x)
+    blk.check_status()
+    idx, w, hist, logits = ops.router_top2(x.view(-1, h), blk.gate.weight.detach(), renorm=blk.gate.norm_topk_prob,
+                                           want_logits=True)
+    assert int(hist.sum()) == 2 * batch * tokens
+    sd = {k: v.detach().cpu() for k, v in blk.state_dict().items()}
+    names = ("gate_proj", "up_proj", "down_proj") if variant == "swiglu" else ("fc1", "fc2")
+    ex = [[sd[f"experts.{i}.{p}.weight"].float() for p in names] for i in range(e)]
+    sh = [sd[f"shared_experts.{p}.weight"].float() for p in names] if variant == "swiglu" else None
+    xc = x.cpu().view(-1, h)
+    # routing: the oracle on its own logits; disagreements must be near-ties
+    idx_o, w_o, logits_o = O.gate_top2(xc, sd["gate.weight"], renorm=blk.gate.norm_topk_prob)
+    frac = _near_tie_only(idx.cpu(), idx_o, logits_o)
+    assert frac < 0.02, frac
+    # selection exact on the kernel's own logits
+    w_sel, idx_sel = O.top2_from_scores(logits.cpu().float().softmax(-1))
+    assert torch.equal(idx.cpu(), idx_sel)
+    # activations: the oracle with the kernel's routing, fp32 arithmetic on the bf16 values
+    want = O.moe_infer(xc.float(), idx.cpu().view(-1), w.cpu().view(-1), ex, variant)
+    if sh is not None:
+        want = want + O.run_expert(xc.float(), sh, variant)
+    got = y.cpu().float().view(-1, h)
+    err = _rel(got, want)
+    assert err < 2e-2, err
+    # and against the oracle end to end (fp32 logits, its own routing) on the tokens where both routings agree
+    full = O.moe_block_forward(xc.float(), sd["gate.weight"].float(), ex, sh, act=variant, renorm=blk.gate.norm_topk_prob)
+    agree = (full["topk_idx"] == idx.cpu()).all(-1)
+    assert agree.float().mean() > 0.95, agree.float().mean()
+    assert _rel(got[agree], full["out"][agree]) < 2e-2
+
+
+@pytest.mark.parametrize("variant", ["gelu_tanh", "swiglu"])
+def test_full_size_xl_block_against_oracle(cuda_device, variant):
+    """The block of the headline benchmark line: 64 x 256 tokens, hidden 1152, 8 experts, bf16."""
+    _block_against_oracle(cuda_device, 1152, 8, variant, 64, 256)
+
+
+@pytest.mark.parametrize("h,variant", [(1792, "gelu_tanh"), (1408, "swiglu")])
+def test_g2_block_against_oracle(cuda_device, h, variant):
+    """One G/2 block (16 experts, 2 x 1024 tokens): hidden 1792 in the benchmark's wording (GELU-tanh experts,
+    renormalised weights), hidden 1408 as the reference builds it (SwiGLU experts + shared expert)."""
+    _block_against_oracle(cuda_device, h, 16, variant, 2, 1024)
+
+
+def test_half_precision_parameters_under_autocast(cuda_device):
+    """The reference samples with ``model.half()`` inside ``torch.autocast('cuda')``; LayerNorm hands the block
+    fp32 activations there.  The block computes in bf16 (fp16 parameters are converted once), returns the input's
+    dtype, and stays within 2e-2 of the fp32 oracle on the fp16 parameter values."""
+    from dice_b200.moe_block import ParaMode, SparseMoeBlock
+
+    torch.manual_seed(4)
+    h, e = 256, 8
+    blk = SparseMoeBlock(h, 4, e, 2, 1, 0, 1, ParaMode()).half().to(cuda_device).eval()
+    x = torch.randn(2, 333, h, device=cuda_device)
+    with torch.autocast("cuda"):
+        y = blk(x)
+        idx, w, _ = blk.gate(x)
+    blk.check_status()
+    assert y.dtype == torch.float32 and y.shape == x.shape
+    sd = {k: v.detach().float().cpu() for k, v in blk.state_dict().items()}
+    ex = [[sd[f"experts.{i}.{p}.weight"] for p in ("gate_proj", "up_proj", "down_proj")] for i in range(e)]
+    sh = [sd[f"shared_experts.{p}.weight"] for p in ("gate_proj", "up_proj", "down_proj")]
+    xc = x.cpu().view(-1, h)
+    want = O.moe_infer(xc, idx.cpu().view(-1), w.cpu().view(-1), ex, "swiglu") + O.run_expert(xc, sh, "swiglu")
+    assert _rel(y.cpu().view(-1, h), want) < 2e-2
+    r = O.moe_block_forward(xc, sd["gate.weight"], ex, sh)
+    assert ((idx.cpu() != r["topk_idx"]).any(-1).float().mean()) < 0.06  # bf16 logits against fp32 logits
+    # fp16 activations (the reference's x after model.half()) take the same path and come back as fp16
+    with torch.autocast("cuda"):
+        y16 = blk(x.half())
+    assert y16.dtype == torch.float16
+    assert _rel(y16.float().cpu().view(-1, h), want) < 2e-2
