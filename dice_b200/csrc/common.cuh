@@ -89,8 +89,8 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
 
 // internal (not exported): bf16 router on the tensor cores, defined next to the grouped GEMM kernel
 int dice_internal_router_tc(const void* x, const void* w_gate, int64_t n_tokens, int hidden, int n_experts, int renorm,
-                            int64_t* out_idx, float* out_w, int32_t* out_hist, void* out_logits,
-                            uint32_t* status, cudaStream_t stream);
+                            int64_t* out_idx, float* out_w, int32_t* out_hist, int32_t* out_chunk_hist,
+                            void* out_logits, uint32_t* status, cudaStream_t stream);
 
 // internal (not exported): grouped GEMM on CTA pairs (cta_group::2); arguments as dice_grouped_gemm, validated by it
 // where the output rows of a grouped GEMM go when they leave the GPU (see GemmParams::ret_*)

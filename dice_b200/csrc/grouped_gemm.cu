@@ -53,7 +53,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   int* s_mprefix = s_seg_off + (kMaxSeg + 1);                     // [n_seg + 1] m-blocks before segment s
   const uint32_t tiles_smem = smem_u32(smem);
   const uint32_t stage_tx_bytes = kTileABytes + static_cast<uint32_t>(p.b_box_rows) * (BK * 2);
-  int* s_hist = s_mprefix + (kMaxSeg + 1);                        // [64] router histogram
+  int* s_hist = s_mprefix + (kMaxSeg + 1);                        // [64] router histogram of this CTA's tiles
+  int* s_tile_hist = s_hist + 64;                                 // [kAccStages][64] histogram of the tile in flight
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -61,6 +62,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   // tail of the kernel before this one in the stream.
   pdl_trigger();
   if (threadIdx.x < 64) s_hist[threadIdx.x] = 0;
+  if (threadIdx.x < 64 * kAccStages) s_tile_hist[threadIdx.x] = 0;
   if (threadIdx.x == 0) {
     for (int s = 0; s < n_stages; ++s) {
       mbar_init(full_bar + 8 * s, 1);
@@ -241,8 +243,17 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
           longlong2 iv; iv.x = i0; iv.y = i1;
           *reinterpret_cast<longlong2*>(p.out_idx + 2 * tok) = iv;
           *reinterpret_cast<float2*>(p.out_w + 2 * tok) = make_float2(p0, p1);
-          atomicAdd(&s_hist[i0], 1);
-          atomicAdd(&s_hist[i1], 1);
+          atomicAdd(&s_tile_hist[acc * 64 + i0], 1);
+          atomicAdd(&s_tile_hist[acc * 64 + i1], 1);
+        }
+        // the four selecting warps meet (named barrier 1), then one thread per expert files the tile's histogram
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        const int e = quad * 32 + lane;
+        if (e < p.n_experts) {
+          const int cnt = s_tile_hist[acc * 64 + e];
+          if (p.chunk_hist != nullptr) p.chunk_hist[t * p.n_experts + e] = cnt;
+          s_hist[e] += cnt;
+          s_tile_hist[acc * 64 + e] = 0;
         }
         }
       } else if (p.epilogue == DICE_EPI_SWIGLU) {
@@ -287,7 +298,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   // ---------------- teardown ----------------
   tc_fence_before_sync();
   __syncthreads();
-  if (p.epilogue == kEpiRouter && threadIdx.x < p.n_experts && s_hist[threadIdx.x] != 0)
+  if (p.epilogue == kEpiRouter && p.hist != nullptr && threadIdx.x < p.n_experts && s_hist[threadIdx.x] != 0)
     atomicAdd(&p.hist[threadIdx.x], s_hist[threadIdx.x]);
   if (*abort_flag != 0) {
     // a wait expired: give copies and MMAs still in flight time to land before the CTA's
@@ -437,6 +448,7 @@ extern "C" int dice_grouped_gemm(const void* a, int64_t n_rows, int k_dim, const
   p.out_idx = nullptr;
   p.out_w = nullptr;
   p.hist = nullptr;
+  p.chunk_hist = nullptr;
   p.logits_out = nullptr;
 
   const int64_t max_tiles = ((n_rows + BM - 1) / BM + n_seg) * p.n_nblk;
@@ -450,8 +462,8 @@ extern "C" int dice_grouped_gemm(const void* a, int64_t n_rows, int k_dim, const
 // Router on the tensor cores (bf16): logits = x * w_gate^T as one 128 x 16..64 accumulator tile per 128
 // tokens, then every epilogue thread selects the top-2 of its own token.
 int dice_internal_router_tc(const void* x, const void* w_gate, int64_t n_tokens, int hidden, int n_experts, int renorm,
-                            int64_t* out_idx, float* out_w, int32_t* out_hist, void* out_logits,
-                            uint32_t* status, cudaStream_t stream) {
+                            int64_t* out_idx, float* out_w, int32_t* out_hist, int32_t* out_chunk_hist,
+                            void* out_logits, uint32_t* status, cudaStream_t stream) {
   const int sms = sm_count();
   if (sms <= 0) return DICE_ERR_CUDA;
   if (n_tokens >= 0x7fffff00LL) return DICE_ERR_LIMIT;
@@ -482,6 +494,7 @@ int dice_internal_router_tc(const void* x, const void* w_gate, int64_t n_tokens,
   p.out_idx = out_idx;
   p.out_w = out_w;
   p.hist = out_hist;
+  p.chunk_hist = out_chunk_hist;
   p.logits_out = static_cast<__nv_bfloat16*>(out_logits);
   const int64_t tiles = (n_tokens + BM - 1) / BM;
   const int grid = static_cast<int>(tiles < sms ? tiles : sms);

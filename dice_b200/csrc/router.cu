@@ -315,7 +315,7 @@ extern "C" int dice_router_top2(const void* x, const void* w_gate, int64_t n_tok
   // bf16: the logits are a skinny GEMM on the tensor cores with the selection in its epilogue;
   // fp32 must not be rounded to tf32, so it takes the CUDA-core kernel of this file
   if (dtype == DICE_BF16)
-    return dice_internal_router_tc(x, w_gate, n_tokens, hidden, n_experts, renorm, out_idx, out_w, out_hist,
+    return dice_internal_router_tc(x, w_gate, n_tokens, hidden, n_experts, renorm, out_idx, out_w, out_hist, nullptr,
                                    out_logits, status, s);
   return dispatch_router<float>(x, w_gate, n_tokens, hidden, n_experts, renorm, out_idx, out_w, out_hist, out_logits,
                                 s);

@@ -47,7 +47,8 @@ struct GemmParams {
   int renorm;
   int64_t* out_idx;
   float* out_w;
-  int* hist;
+  int* hist;        // [n_experts] totals (may be null)
+  int* chunk_hist;  // [tiles][n_experts] per-128-token histograms (may be null)
   __nv_bfloat16* logits_out;
   // output rows leave the GPU (CTA-pair kernel only): row r of the receive order belongs to source rank s
   // with ret_src_off[s] <= r < ret_src_off[s+1] and is stored in that rank's buffer at row
