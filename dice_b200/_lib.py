@@ -20,13 +20,18 @@ SIGNATURES = {
     "dice_router_top2": (
         c_int,
         [c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-         c_void_p],
+         c_void_p, c_void_p],
     ),
     "dice_top2_from_logits": (c_int, [c_void_p, c_int64, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
     "dice_permute_scratch_bytes": (c_size_t, [c_int64, c_int]),
     "dice_permute_plan": (
         c_int,
         [c_void_p, c_int64, c_int, c_void_p, c_size_t, c_void_p, c_void_p, c_void_p, c_void_p],
+    ),
+    "dice_permute_plan_chunked": (
+        c_int,
+        [c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p,
+         c_void_p],
     ),
     "dice_permute_plan_static": (c_int, [c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
     "dice_permute_rows": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_void_p, c_void_p]),

@@ -569,7 +569,10 @@ int bulk_smem_ready(Kern kernel) {
              : DICE_ERR_CUDA;
 }
 
-// dependent launch, optionally as clusters of two CTAs (which fill whole SM pairs)
+// Launch of a push.  The form that owns the GPU is a dependent launch like the other kernels of the block.  The
+// form that runs beside the expert FFN is launched as clusters of two CTAs (which fill whole SM pairs) and in
+// plain stream order: with a dependent launch the next push of the side stream would become resident on a second
+// set of SMs while this one still runs, and the FFN's persistent CTAs would find fewer SMs than they were sized for.
 template <typename... KArgs, typename... Args>
 cudaError_t launch_push(void (*kernel)(KArgs...), unsigned grid, unsigned threads, size_t smem, cudaStream_t stream,
                         bool pairs, Args... args) {
@@ -587,7 +590,7 @@ cudaError_t launch_push(void (*kernel)(KArgs...), unsigned grid, unsigned thread
     attr[n].val.clusterDim.z = 1;
     ++n;
   }
-  if (dice_pdl_enabled()) {
+  if (dice_pdl_enabled() && !pairs) {
     attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[n].val.programmaticStreamSerializationAllowed = 1;
     ++n;

@@ -113,6 +113,97 @@ plan_rank_kernel(const int64_t* __restrict__ flat_idx, int64_t n_rows, int n_exp
   }
 }
 
+// ---- plan in one launch, from the router's per-chunk histograms -------------------
+// The bf16 router files one histogram per 128 tokens (= one chunk of 256 rows), so passes 1 and 2 are not
+// needed: every CTA adds up the (small) table itself.  Keys may be a permutation of the expert ids: with
+// `world` > 1 rows are ordered by (owner rank, local slot) of a round-robin expert placement, key(e) =
+// (e mod world) * (E / world) + e / world, which is the order the expert-parallel exchange sends them in.
+// With K > 0 the row gather is part of the same kernel: `split` CTAs share a chunk, each ranks the whole
+// chunk and moves its share of the chunk's tokens.
+constexpr int kMaxChunkTable = 16384;  // ints of the per-chunk table one CTA is willing to add up
+
+template <int K>
+__global__ void __launch_bounds__(kChunkRows)
+plan_chunked_kernel(const int64_t* __restrict__ flat_idx, const int* __restrict__ chunk_hist, int64_t n_rows,
+                    int n_experts, int world, int n_chunks, int split, int* __restrict__ pos, int* __restrict__ order,
+                    int* __restrict__ seg_offsets, const uint4* __restrict__ x, int row_vec, uint4* __restrict__ out_rows) {
+  constexpr int kWarps = kChunkRows / 32;
+  __shared__ int s_total[kMaxExperts];
+  __shared__ int s_before[kMaxExperts];
+  __shared__ int s_cbase[kMaxExperts];
+  __shared__ int s_warp_count[kWarps][kMaxExperts];
+  __shared__ int s_pos[kChunkRows];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int chunk = blockIdx.x / split, part = blockIdx.x - chunk * split;
+  pdl_trigger();
+  if (threadIdx.x < kMaxExperts) { s_total[threadIdx.x] = 0; s_before[threadIdx.x] = 0; }
+  for (int i = threadIdx.x; i < kWarps * kMaxExperts; i += kChunkRows) (&s_warp_count[0][0])[i] = 0;
+  __syncthreads();
+  pdl_wait();
+  for (int i = threadIdx.x; i < n_chunks * n_experts; i += kChunkRows) {
+    const int c = i / n_experts, e = i - c * n_experts;
+    const int v = chunk_hist[i];
+    if (v != 0) {
+      atomicAdd(&s_total[e], v);
+      if (c < chunk) atomicAdd(&s_before[e], v);
+    }
+  }
+  const int64_t r = static_cast<int64_t>(chunk) * kChunkRows + threadIdx.x;
+  int e = -1;
+  if (r < n_rows) {
+    const int64_t v = flat_idx[r];
+    if (v >= 0 && v < n_experts) e = static_cast<int>(v);
+  }
+  const unsigned peers = __match_any_sync(0xffffffffu, e);
+  const int rank_in_warp = __popc(peers & ((1u << lane) - 1u));
+  if (e >= 0 && rank_in_warp == 0) s_warp_count[warp][e] = __popc(peers);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int el = n_experts / world;
+    int run = 0;
+    for (int k = 0; k < n_experts; ++k) {
+      const int ek = (k % el) * world + k / el;  // the expert whose key is k
+      s_cbase[ek] = run + s_before[ek];
+      if (blockIdx.x == 0) seg_offsets[k] = run;
+      run += s_total[ek];
+    }
+    if (blockIdx.x == 0) seg_offsets[n_experts] = run;
+  }
+  __syncthreads();
+  int p = -1;
+  if (e >= 0) {
+    int before = 0;
+    for (int w = 0; w < warp; ++w) before += s_warp_count[w][e];
+    p = s_cbase[e] + before + rank_in_warp;
+  }
+  if (part == 0 && r < n_rows) {
+    pos[r] = p;
+    if (order != nullptr && p >= 0) order[p] = static_cast<int>(r);
+  }
+  if (K > 0) {
+    s_pos[threadIdx.x] = p;
+    __syncthreads();
+    const int tokens_per_part = kChunkRows / K / split;
+    const int64_t n_tokens = n_rows / K;
+    for (int i = warp; i < tokens_per_part; i += kWarps) {
+      const int tl = part * tokens_per_part + i;  // token inside the chunk
+      const int64_t t = static_cast<int64_t>(chunk) * (kChunkRows / K) + tl;
+      if (t >= n_tokens) break;
+      int64_t dst[K > 0 ? K : 1];
+#pragma unroll
+      for (int s = 0; s < K; ++s) dst[s] = static_cast<int64_t>(s_pos[tl * K + s]) * row_vec;
+      const uint4* src = x + t * row_vec;
+#pragma unroll 4
+      for (int c = lane; c < row_vec; c += 32) {
+        const uint4 v = ldg_stream16(src + c);
+#pragma unroll
+        for (int s = 0; s < K; ++s)
+          if (dst[s] >= 0) stg_stream16(out_rows + dst[s] + c, v);
+      }
+    }
+  }
+}
+
 // ---- row gather: out_rows[pos[t*k+s]] = x[t] ---------------------------------
 template <int K>
 __global__ void __launch_bounds__(256)
@@ -296,6 +387,46 @@ extern "C" int dice_permute_plan_static(const int64_t* flat_idx, int64_t n_rows,
                            out_seg_offsets));
   DICE_CUDA_OK(dice_launch(plan_rank_kernel, dim3(n_chunks), dim3(kChunkRows), 0, s, flat_idx, n_rows, n_experts,
                            chunk_hist, out_pos, out_order));
+  return DICE_OK;
+}
+
+extern "C" int dice_permute_plan_chunked(const int64_t* flat_idx, const int32_t* chunk_hist, int64_t n_rows,
+                                         int n_experts, int world, int32_t* out_pos, int32_t* out_order,
+                                         int32_t* out_seg_offsets, const void* x, int k, int hidden, int dtype,
+                                         void* out_rows, void* stream) {
+  DICE_CHECK_ARG(n_rows >= 0 && out_seg_offsets != nullptr, DICE_ERR_ARG);
+  DICE_CHECK_ARG(n_experts >= 1 && n_experts <= kMaxExperts && world >= 1 && n_experts % world == 0, DICE_ERR_SHAPE);
+  const int64_t chunks = (n_rows + kChunkRows - 1) / kChunkRows;
+  DICE_CHECK_ARG(chunks * n_experts <= kMaxChunkTable, DICE_ERR_LIMIT);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (n_rows == 0) {
+    DICE_CUDA_OK(cudaMemsetAsync(out_seg_offsets, 0, sizeof(int32_t) * (n_experts + 1), s));
+    return DICE_OK;
+  }
+  DICE_CHECK_ARG(flat_idx && chunk_hist && out_pos, DICE_ERR_ARG);
+  const int n_chunks = static_cast<int>(chunks);
+  if (x == nullptr) {
+    DICE_CUDA_OK(dice_launch(plan_chunked_kernel<0>, dim3(n_chunks), dim3(kChunkRows), 0, s, flat_idx, chunk_hist, n_rows,
+                             n_experts, world, n_chunks, 1, out_pos, out_order, out_seg_offsets,
+                             static_cast<const uint4*>(nullptr), 0, static_cast<uint4*>(nullptr)));
+    return DICE_OK;
+  }
+  DICE_CHECK_ARG(k == 1 || k == 2, DICE_ERR_SHAPE);
+  DICE_CHECK_ARG(n_rows % k == 0 && hidden > 0 && out_rows != nullptr, DICE_ERR_ARG);
+  const size_t es = dice_dtype_size(dtype);
+  DICE_CHECK_ARG(es != 0, DICE_ERR_DTYPE);
+  DICE_CHECK_ARG((hidden * es) % 16 == 0, DICE_ERR_SHAPE);
+  DICE_CHECK_ARG(dice_aligned16(x) && dice_aligned16(out_rows), DICE_ERR_ALIGN);
+  const int row_vec = static_cast<int>(hidden * es / 16);
+  const int split = 8;  // CTAs per chunk: 16 (k = 2) or 32 (k = 1) tokens each
+  if (k == 2)
+    DICE_CUDA_OK(dice_launch(plan_chunked_kernel<2>, dim3(n_chunks * split), dim3(kChunkRows), 0, s, flat_idx, chunk_hist,
+                             n_rows, n_experts, world, n_chunks, split, out_pos, out_order, out_seg_offsets,
+                             static_cast<const uint4*>(x), row_vec, static_cast<uint4*>(out_rows)));
+  else
+    DICE_CUDA_OK(dice_launch(plan_chunked_kernel<1>, dim3(n_chunks * split), dim3(kChunkRows), 0, s, flat_idx, chunk_hist,
+                             n_rows, n_experts, world, n_chunks, split, out_pos, out_order, out_seg_offsets,
+                             static_cast<const uint4*>(x), row_vec, static_cast<uint4*>(out_rows)));
   return DICE_OK;
 }
 

@@ -299,14 +299,16 @@ int dispatch_select(const void* logits, int64_t n, int e, int renorm, int64_t* i
 
 extern "C" int dice_router_top2(const void* x, const void* w_gate, int64_t n_tokens, int hidden, int n_experts,
                                 int dtype, int renorm, int64_t* out_idx, float* out_w, int32_t* out_hist,
-                                void* out_logits, uint32_t* status, void* stream) {
+                                int32_t* out_chunk_hist, void* out_logits, uint32_t* status, void* stream) {
   DICE_CHECK_ARG(n_tokens >= 0 && hidden > 0, DICE_ERR_ARG);
   DICE_CHECK_ARG(n_experts >= 2 && n_experts <= 64, DICE_ERR_SHAPE);
   DICE_CHECK_ARG(dtype == DICE_BF16 || dtype == DICE_F32, DICE_ERR_DTYPE);
   DICE_CHECK_ARG((hidden * dice_dtype_size(dtype)) % 16 == 0, DICE_ERR_SHAPE);
-  DICE_CHECK_ARG(out_hist != nullptr, DICE_ERR_ARG);
+  // per-chunk histograms come out of the tensor-core kernel's 128-token tiles; the fp32 kernel walks smaller tiles
+  DICE_CHECK_ARG(out_chunk_hist == nullptr || dtype == DICE_BF16, DICE_ERR_DTYPE);
+  DICE_CHECK_ARG(out_hist != nullptr || out_chunk_hist != nullptr, DICE_ERR_ARG);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  DICE_CUDA_OK(cudaMemsetAsync(out_hist, 0, sizeof(int32_t) * n_experts, s));
+  if (out_hist != nullptr) DICE_CUDA_OK(cudaMemsetAsync(out_hist, 0, sizeof(int32_t) * n_experts, s));
   if (n_tokens == 0) return DICE_OK;
   DICE_CHECK_ARG(x && w_gate && out_idx && out_w, DICE_ERR_ARG);
   DICE_CHECK_ARG(dice_aligned16(x) && dice_aligned16(w_gate) && dice_aligned16(out_idx) &&
@@ -315,8 +317,8 @@ extern "C" int dice_router_top2(const void* x, const void* w_gate, int64_t n_tok
   // bf16: the logits are a skinny GEMM on the tensor cores with the selection in its epilogue;
   // fp32 must not be rounded to tf32, so it takes the CUDA-core kernel of this file
   if (dtype == DICE_BF16)
-    return dice_internal_router_tc(x, w_gate, n_tokens, hidden, n_experts, renorm, out_idx, out_w, out_hist, nullptr,
-                                   out_logits, status, s);
+    return dice_internal_router_tc(x, w_gate, n_tokens, hidden, n_experts, renorm, out_idx, out_w, out_hist,
+                                   out_chunk_hist, out_logits, status, s);
   return dispatch_router<float>(x, w_gate, n_tokens, hidden, n_experts, renorm, out_idx, out_w, out_hist, out_logits,
                                 s);
 }

@@ -60,6 +60,13 @@ class CudaOps:
         pos, seg, _ = ops.permute_plan(keys, n_keys)
         return pos, seg
 
+    def plan_chunked(self, flat_idx: torch.Tensor, chunk_hist: torch.Tensor, n_experts: int, world: int):
+        """Plan by (owner rank, local slot) in one launch, from the router's per-chunk histograms."""
+        from .. import ops
+
+        pos, seg, _, _ = ops.permute_plan_chunked(flat_idx, chunk_hist, n_experts, world)
+        return pos, seg
+
     def permute_rows(self, x: torch.Tensor, pos: torch.Tensor, k: int) -> torch.Tensor:
         from .. import ops
 
@@ -226,7 +233,9 @@ def _peer_push(info, async_op, dispatch=None, rows_back=None):
             stream),
             "dice_ep_return_rows")
         out, which = x.back[slot][: info.rows_sent], 1
-    event = None
+    # a consumer on another stream must also see what THIS rank's side stream wrote (the meta block of the count
+    # exchange, the rows this rank pushed into its own buffers)
+    event = x.record_side_event(slot, which) if async_op else None
     handle = p2p.PeerHandle(info, which, event)
     with _scope("moe.wait"):
         if not async_op:
@@ -327,7 +336,8 @@ def _pick(pairs: torch.Tensor, const_slot: Optional[int], per_tok: Optional[torc
 
 @torch.no_grad()
 def moe_infer_ep(inp: torch.Tensor, experts: nn.ModuleList, flat_expert_indices, flat_expert_weights,
-                 num_experts_per_tok, async_op, skip_mask=None, skip_now=None, cache_key=None, _addend=None):
+                 num_experts_per_tok, async_op, skip_mask=None, skip_now=None, cache_key=None, _addend=None,
+                 _chunks=None):
     """Expert-parallel replacement of ``SparseMoeBlock.moe_infer``
     (ep_fwd.py:19-197; same arguments and result).
 
@@ -336,7 +346,9 @@ def moe_infer_ep(inp: torch.Tensor, experts: nn.ModuleList, flat_expert_indices,
     ``flat_expert_weights`` ``[N*k, 1]``; ``async_op`` selects the displaced /
     interweaved protocol of :mod:`diep`; ``skip_mask`` / ``skip_now`` drive
     conditional communication; ``cache_key`` is the layer index.  ``_addend``
-    (not in the reference) is added to the result inside the combine kernel."""
+    (not in the reference) is added to the result inside the combine kernel;
+    ``_chunks`` (not in the reference) is the router's per-128-token histogram
+    table, from which the plan is a single launch."""
     world_size, rank = dist.get_world_size(), dist.get_rank()
     num_total_experts = len(experts)
     num_local_experts = num_total_experts // world_size
@@ -361,8 +373,11 @@ def moe_infer_ep(inp: torch.Tensor, experts: nn.ModuleList, flat_expert_indices,
         flat_idx = flat_expert_indices
 
     # sort key = (owner rank, local slot): rows for one destination are contiguous
-    keys = (flat_idx % world_size) * num_local_experts + torch.div(flat_idx, world_size, rounding_mode="floor")
-    pos, seg_offsets = _ops.plan(keys, num_total_experts)
+    if _chunks is not None and k_eff == k_full and hasattr(_ops, "plan_chunked"):
+        pos, seg_offsets = _ops.plan_chunked(flat_idx, _chunks, num_total_experts, world_size)
+    else:
+        keys = (flat_idx % world_size) * num_local_experts + torch.div(flat_idx, world_size, rounding_mode="floor")
+        pos, seg_offsets = _ops.plan(keys, num_total_experts)
 
     xchg = None
     if inp.is_cuda and p2p.enabled():
@@ -375,10 +390,18 @@ def moe_infer_ep(inp: torch.Tensor, experts: nn.ModuleList, flat_expert_indices,
 
         inp = inp.contiguous()
         slot, seq, tab = xchg.begin(cache_key or 0)
+        # An exchange that nobody waits for in this layer (displaced / interweaved) keeps even its count exchange,
+        # a rendezvous of all ranks, off the main stream: it runs on the side stream in front of the dispatch.
+        # Whoever consumes the exchange later waits for the side stream's event and for the sources' flags.
+        side = async_op and not diep._forced_sync
         with _scope("exchange_token_counts"):
+            if side:
+                for t in (seg_offsets, pos, inp):
+                    t.record_stream(xchg._comm)
             _lib.check(xchg.lib.dice_ep_exchange_counts(
                 seg_offsets.data_ptr(), tab["matrix"], tab["f_cnt"], xchg._meta_ptrs[slot], xchg.rank, xchg.world,
-                xchg.n_experts, xchg.min_peer_cap, seq, xchg.status_ptr, _stream()), "dice_ep_exchange_counts")
+                xchg.n_experts, xchg.min_peer_cap, seq, xchg.status_ptr, xchg.fork_to_comm() if side else _stream()),
+                "dice_ep_exchange_counts")
         counts_local = None
         counts_global = p2p.SegInfo(xchg, slot, seq, tab, n_tokens * k_eff)
         grouped_dup_inp = p2p.PendingRows(inp, pos, seg_offsets, k_eff, counts_global)

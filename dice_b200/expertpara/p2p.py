@@ -151,6 +151,7 @@ class PeerExchange:
         self.seg_slab = [i for _ in range(self.world) for i in range(self.el)]
         self.seg_slab_dev = torch.tensor(self.seg_slab, dtype=torch.int32, device=self.device)
         self._fork = torch.cuda.Event()
+        self._side_events = [torch.cuda.Event() for _ in range(2 * n_slots)]
         self._comm = torch.cuda.Stream(device=self.device)
         self.comm_raw = self._comm.cuda_stream
         dist.barrier(group=group)
@@ -189,6 +190,12 @@ class PeerExchange:
         self._fork.record()
         self._comm.wait_event(self._fork)
         return self.comm_raw
+
+    def record_side_event(self, slot: int, which: int) -> torch.cuda.Event:
+        """Mark the side stream's position after a push of ``slot`` (0 dispatch, 1 return)."""
+        ev = self._side_events[2 * slot + which]
+        ev.record(self._comm)
+        return ev
 
     def my_flags_ptr(self, slot: int, which: int) -> int:
         return self.ctrl.data_ptr() + (slot * self.ctrl_stride + self.flag_base + which * _FLAG_PAD) * 4
@@ -352,7 +359,8 @@ class ReturnedRows:
 
 
 class PeerHandle:
-    """Work handle of one push: ``wait`` makes the current stream wait (bounded,
+    """Work handle of one push: ``wait`` makes the current stream wait for this
+    rank's own side-stream work on the exchange (an event) and then (bounded,
     on the device) until every source raised this exchange's flag;
     ``is_completed`` tells whether this rank's own push has left its buffers."""
 
@@ -363,6 +371,8 @@ class PeerHandle:
         from ..ops import _stream
 
         x = self.info.xchg
+        if self.event is not None:
+            torch.cuda.current_stream().wait_event(self.event)
         _lib.check(x.lib.dice_ep_wait_flags(x.my_flags_ptr(self.info.slot, 1 + self.which), x.world, self.info.seq,
                                             self.which, x.status.data_ptr(), _stream()), "dice_ep_wait_flags")
 

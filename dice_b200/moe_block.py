@@ -203,6 +203,7 @@ class ExpertPack:
     def __init__(self, experts: Sequence[nn.Module], tag: str = "routed"):
         self._experts = experts
         self._built = {}
+        self._calls = 0
         self.status = None
         self.tag = tag
         self._slab_tables = {}
@@ -218,12 +219,25 @@ class ExpertPack:
             return "gelu_tanh", (e.fc1.weight, e.fc2.weight)
         raise TypeError(f"cannot pack expert of type {type(e).__name__}")
 
+    def invalidate(self) -> None:
+        """Forget the packed weights (the block calls this when its parameters are replaced or reloaded)."""
+        self._built.clear()
+
+    def _signature(self, local):
+        return tuple((p.data_ptr(), p._version) for e in local for p in self._params(e)[1])
+
     def get(self, dtype: torch.dtype):
-        local = self._local()
-        sig = tuple((p.data_ptr(), p._version) for e in local for p in self._params(e)[1])
         hit = self._built.get(dtype)
-        if hit is not None and hit[0] == sig:
-            return hit[1]
+        if hit is not None:
+            # per call only the first parameter is looked at; module-level changes (``.to()``, ``.half()``,
+            # ``load_state_dict``) invalidate the pack through the block's hooks, and every 256th call
+            # compares all parameters
+            self._calls += 1
+            p0 = hit[2]
+            if p0.data_ptr() == hit[3] and p0._version == hit[4] and (self._calls & 255 or hit[0] == self._signature(self._local())):
+                return hit[1]
+        local = self._local()
+        sig = self._signature(local)
         act = self._params(local[0])[0]
         dev = self._params(local[0])[1][0].device
         if dev.type != "cuda":
@@ -240,7 +254,8 @@ class ExpertPack:
             if self.status is None:
                 self.status = ops.device_status(dev)
         built = (act, ffn, w1, w2)
-        self._built[dtype] = (sig, built)
+        p0 = self._params(local[0])[1][0]
+        self._built[dtype] = (sig, built, p0, p0.data_ptr(), p0._version)
         return built
 
     def run_offsets(self, rows: torch.Tensor, seg_offsets: torch.Tensor, seg_slab: Optional[torch.Tensor] = None,
@@ -340,6 +355,20 @@ class SparseMoeBlock(nn.Module):
         self._gate_cast = {}
         self._seg_cache = {}
         self._status = None
+        self.register_load_state_dict_post_hook(lambda module, incompatible: module._invalidate_packs())
+
+    def _invalidate_packs(self):
+        self.experts._dice_pack.invalidate()
+        if self._shared_pack is not None:
+            self._shared_pack.invalidate()
+        self._gate_cast.clear()
+
+    def _apply(self, fn, *args, **kwargs):
+        # .to() / .half() / .cuda() replace the parameters' storage: the packed copies must be rebuilt
+        out = super()._apply(fn, *args, **kwargs)
+        if hasattr(self, "_gate_cast"):
+            self._invalidate_packs()
+        return out
 
     # -- helpers ----------------------------------------------------------------
     def _gate_weight(self, dtype):
@@ -401,15 +430,18 @@ class SparseMoeBlock(nn.Module):
             from .expertpara import p2p
 
             reserve = p2p.reserve_sms()
+        # bf16: the router also files one histogram per 128 tokens, from which the permutation plan is one launch
+        chunked = cd == torch.bfloat16 and (2 * n_tokens + 255) // 256 * self.num_experts <= ops.PLAN_CHUNKED_MAX_INTS
         with _scope("moe.gate"):
             topk_idx, topk_weight, hist, _ = ops.router_top2(x, self._gate_weight(cd), renorm=self.gate.norm_topk_prob,
-                                                             status=self._router_status(x.device))
+                                                             status=self._router_status(x.device), want_chunks=chunked)
+        chunks = hist if chunked else None
         shared_out = None
         if self._shared_pack is not None:
             with _scope("moe.mlp_shared"):
                 shared_out = self._shared_pack.run_offsets(x, self._segment_all(n_tokens, x.device), reserve_sms=reserve)
         if not self.para_mode.ep:
-            y = self.moe_infer(x, topk_idx.view(-1), topk_weight.view(-1, 1), _addend=shared_out)
+            y = self.moe_infer(x, topk_idx.view(-1), topk_weight.view(-1, 1), _addend=shared_out, _chunks=chunks)
         else:
             from .expertpara.diep import ep_skip_enabled, ep_skip_mask, ep_skip_now
             from .expertpara.ep_fwd import moe_infer_ep
@@ -420,19 +452,24 @@ class SparseMoeBlock(nn.Module):
                 flat_expert_weights=topk_weight.view(-1, 1), num_experts_per_tok=self.num_experts_per_tok,
                 skip_mask=ep_skip_mask(topk_idx.numel()) if partial_skip else None,
                 skip_now=ep_skip_now(self.layer_idx) if partial_skip else None,
-                async_op=self._async_layer(), cache_key=self.layer_idx, _addend=shared_out)
+                async_op=self._async_layer(), cache_key=self.layer_idx, _addend=shared_out, _chunks=chunks)
         y = y.view(*orig_shape)
         return y if y.dtype == orig_dtype else y.to(orig_dtype)
 
     @torch.no_grad()
-    def moe_infer(self, x, flat_expert_indices, flat_expert_weights, _addend=None):
+    def moe_infer(self, x, flat_expert_indices, flat_expert_weights, _addend=None, _chunks=None):
         """Single-device dispatch -> experts -> weighted combine
-        (models.py:361-382), as four kernel launches and no host sync."""
+        (models.py:361-382), without a host sync: plan + row gather (one
+        launch when the router filed per-chunk histograms, else four), two
+        grouped GEMMs, combine."""
         assert not self.para_mode.ep
         n_tokens = x.shape[0]
         k = self.num_experts_per_tok
-        pos, seg, _ = ops.permute_plan(flat_expert_indices, self.num_experts)
-        rows = ops.permute_rows(x, pos, k)
+        if _chunks is not None:
+            pos, seg, _, rows = ops.permute_plan_chunked(flat_expert_indices, _chunks, self.num_experts, 1, x, k)
+        else:
+            pos, seg, _ = ops.permute_plan(flat_expert_indices, self.num_experts)
+            rows = ops.permute_rows(x, pos, k)
         with _scope("moe.mlp"):
             y_rows = self.experts._dice_pack.run_offsets(rows, seg)
         w = flat_expert_weights.view(n_tokens, k)

@@ -126,11 +126,15 @@ def poll_status(device=None) -> None:
 
 def router_top2(
     x2d: torch.Tensor, w_gate: torch.Tensor, renorm: bool = False, want_logits: bool = False,
-    status: Optional[torch.Tensor] = None,
+    status: Optional[torch.Tensor] = None, want_chunks: bool = False,
 ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, Optional[torch.Tensor]]:
     """Fused gate: returns ``(topk_idx int64 [N,2], topk_weight fp32 [N,2],
     hist int32 [E], logits or None)``; replaces ``MoEGate.forward``
-    (models.py:179-217) and the ``bincount`` of ep_fwd.py:70."""
+    (models.py:179-217) and the ``bincount`` of ep_fwd.py:70.
+
+    With ``want_chunks`` (bf16 only) the third result is instead the
+    per-128-token histogram table ``int32 [ceil(N/128), E]`` that
+    :func:`permute_plan_chunked` consumes."""
     _require_cuda(x2d, w_gate)
     assert x2d.dim() == 2 and w_gate.dim() == 2 and x2d.shape[1] == w_gate.shape[1]
     assert x2d.dtype == w_gate.dtype, "router weight must have the activation dtype"
@@ -140,17 +144,21 @@ def router_top2(
     e = w_gate.shape[0]
     idx = torch.empty((n, 2), dtype=torch.int64, device=x2d.device)
     w = torch.empty((n, 2), dtype=torch.float32, device=x2d.device)
-    hist = torch.empty((e,), dtype=torch.int32, device=x2d.device)
+    hist = chunks = None
+    if want_chunks:
+        chunks = torch.empty(((n + 127) // 128, e), dtype=torch.int32, device=x2d.device)
+    else:
+        hist = torch.empty((e,), dtype=torch.int32, device=x2d.device)
     logits = torch.empty((n, e), dtype=x2d.dtype, device=x2d.device) if want_logits else None
     lib = _lib.load()
     _lib.check(
         lib.dice_router_top2(
             _ptr(x2d), _ptr(w_gate), n, h, e, _dtype_code(x2d), int(renorm), _ptr(idx), _ptr(w), _ptr(hist),
-            _ptr(logits), _ptr(status), _stream(),
+            _ptr(chunks), _ptr(logits), _ptr(status), _stream(),
         ),
         "dice_router_top2",
     )
-    return idx, w, hist, logits
+    return idx, w, (chunks if want_chunks else hist), logits
 
 
 def top2_from_logits(logits: torch.Tensor, renorm: bool = False):
@@ -196,6 +204,40 @@ def permute_plan(flat_idx: torch.Tensor, n_experts: int, want_order: bool = Fals
         "dice_permute_plan",
     )
     return pos, seg, order
+
+
+def permute_plan_chunked(flat_idx: torch.Tensor, chunk_hist: torch.Tensor, n_experts: int, world: int = 1,
+                         x2d: Optional[torch.Tensor] = None, k: int = 2, want_order: bool = False):
+    """The plan in one launch from the router's per-128-token histograms
+    (``router_top2(..., want_chunks=True)``), ordered by expert id (``world``
+    1) or by ``(owner rank, local slot)`` of the round-robin placement
+    (``world`` > 1, etrim.py:23-24).  With ``x2d`` the row gather of
+    :func:`permute_rows` is part of the same kernel.  Returns ``(pos, seg_offsets,
+    order or None, rows or None)``."""
+    _require_cuda(flat_idx, chunk_hist, x2d)
+    assert flat_idx.dtype == torch.int64 and flat_idx.dim() == 1 and flat_idx.is_contiguous()
+    assert chunk_hist.dtype == torch.int32 and chunk_hist.is_contiguous()
+    r = flat_idx.shape[0]
+    assert chunk_hist.numel() == (r + 255) // 256 * n_experts
+    dev = flat_idx.device
+    pos = torch.empty((r,), dtype=torch.int32, device=dev)
+    order = torch.empty((r,), dtype=torch.int32, device=dev) if want_order else None
+    seg = torch.empty((n_experts + 1,), dtype=torch.int32, device=dev)
+    rows, h, code = None, 0, 0
+    if x2d is not None:
+        assert x2d.is_contiguous() and x2d.shape[0] * k == r
+        h, code = x2d.shape[1], _dtype_code(x2d)
+        rows = torch.empty((r, h), dtype=x2d.dtype, device=dev)
+    _lib.check(
+        _lib.load().dice_permute_plan_chunked(_ptr(flat_idx), _ptr(chunk_hist), r, n_experts, world, _ptr(pos), _ptr(order),
+                                              _ptr(seg), _ptr(x2d), k, h, code, _ptr(rows), _stream()),
+        "dice_permute_plan_chunked",
+    )
+    return pos, seg, order, rows
+
+
+# the chunked plan adds the whole per-chunk table up in every CTA: beyond this size use the three-pass plan
+PLAN_CHUNKED_MAX_INTS = 16384
 
 
 def permute_rows(x2d: torch.Tensor, pos: torch.Tensor, k: int, out: Optional[torch.Tensor] = None) -> torch.Tensor:

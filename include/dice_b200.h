@@ -82,7 +82,11 @@ DICE_API uint64_t dice_kernel_launches(void);
  *                                 expert index first
  *   out_w    [n_tokens, 2] fp32   softmax scores of the two (renormalised to
  *                                 sum 1 when renorm != 0)
- *   out_hist [n_experts]  int32   rows per expert (zeroed by the call)
+ *   out_hist [n_experts]  int32   rows per expert (zeroed by the call; NULL to
+ *                                 skip when out_chunk_hist is given)
+ *   out_chunk_hist  optional [ceil(n_tokens / 128), n_experts] int32, bf16
+ *                   only: rows per expert of every 128 tokens (every cell is
+ *                   written), the input of dice_permute_plan_chunked
  *   out_logits  optional [n_tokens, n_experts] dtype (NULL to skip)
  * Logits are accumulated in fp32 and rounded to dtype before the softmax,
  * which is evaluated in fp32.  hidden*sizeof(dtype) must be a multiple of 16,
@@ -94,7 +98,7 @@ DICE_API uint64_t dice_kernel_launches(void);
  */
 DICE_API int dice_router_top2(const void* x, const void* w_gate, int64_t n_tokens, int hidden, int n_experts,
                      int dtype, int renorm, int64_t* out_idx, float* out_w, int32_t* out_hist,
-                     void* out_logits, uint32_t* status, void* stream);
+                     int32_t* out_chunk_hist, void* out_logits, uint32_t* status, void* stream);
 
 /* The selection stage alone, on logits supplied by the caller (same outputs
  * as above).  Lets the selection be checked bit-exactly against
@@ -118,6 +122,26 @@ DICE_API size_t dice_permute_scratch_bytes(int64_t n_rows, int n_experts);
 DICE_API int dice_permute_plan(const int64_t* flat_idx, int64_t n_rows, int n_experts, void* scratch,
                       size_t scratch_bytes, int32_t* out_pos, int32_t* out_order,
                       int32_t* out_seg_offsets, void* stream);
+
+/* The same plan in ONE launch, from the per-128-token histograms the bf16
+ * router files (the two counting passes are already done), optionally with
+ * the row gather of dice_permute_rows fused in (ep_fwd.py:70-76, :100,
+ * :107-111; models.py:365-366, :374).
+ *   chunk_hist  [ceil(n_rows / 256), n_experts] int32 as written by
+ *               dice_router_top2 (a chunk = 128 tokens x 2 slots = 256 rows)
+ *   world       1: rows are ordered by expert id; > 1: by (owner rank, local
+ *               slot) of the round-robin placement of etrim.py:23-24, i.e. by
+ *               key(e) = (e mod world) * (n_experts / world) + e / world, the
+ *               order the expert-parallel exchange sends rows in;
+ *               out_seg_offsets is then indexed by key
+ *   x, k, hidden, dtype, out_rows   x == NULL: plan only; else also
+ *               out_rows[out_pos[t*k + s]] = x[t]
+ *   limit: ceil(n_rows / 256) * n_experts <= 16384 (DICE_ERR_LIMIT beyond; use
+ *   dice_permute_plan + dice_permute_rows there). */
+DICE_API int dice_permute_plan_chunked(const int64_t* flat_idx, const int32_t* chunk_hist, int64_t n_rows,
+                              int n_experts, int world, int32_t* out_pos, int32_t* out_order,
+                              int32_t* out_seg_offsets, const void* x, int k, int hidden, int dtype,
+                              void* out_rows, void* stream);
 
 /* Allocation-free variant of dice_permute_plan; it has no counterpart in the
  * reference.  It is for hosts that must not allocate device memory while they

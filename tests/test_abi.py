@@ -41,8 +41,8 @@ def test_version_and_messages():
 def test_argument_errors_are_reported_on_the_host():
     lib = _lib.load()
     # bad expert count / dtype / null pointers: rejected before any CUDA call
-    assert lib.dice_router_top2(None, None, 4, 64, 1, 0, 0, None, None, None, None, None, None) == -2
-    assert lib.dice_router_top2(None, None, 4, 64, 8, 7, 0, None, None, None, None, None, None) == -3
+    assert lib.dice_router_top2(None, None, 4, 64, 1, 0, 0, None, None, None, None, None, None, None) == -2
+    assert lib.dice_router_top2(None, None, 4, 64, 8, 7, 0, None, None, None, None, None, None, None) == -3
     assert lib.dice_permute_rows(None, None, 4, 3, 64, 0, None, None) == -2
     assert lib.dice_grouped_gemm(None, 4, 60, None, 1, 32, None, None, 1, 0, None, 32, 32, 0, None, None) == -2
     assert lib.dice_grouped_gemm(None, 4, 64, None, 1, 32, None, None, 300, 0, None, 32, 32, 0, None, None) == -7

@@ -123,6 +123,51 @@ def test_permute_plan_all_rows_one_expert_and_empty(cuda_device):
     assert seg.cpu().tolist() == [0] * 9 and pos.numel() == 0
 
 
+@pytest.mark.parametrize("n,h,e", [(1, 64, 8), (127, 64, 8), (128, 128, 8), (129, 64, 8), (1000, 256, 16), (16384, 1152, 8), (4096, 1792, 16)])
+def test_router_files_a_histogram_per_128_tokens(cuda_device, n, h, e):
+    """The bf16 router's per-chunk table equals a bincount of every 128 tokens' selections; routing is unchanged."""
+    ops = _ops()
+    g = torch.Generator(device="cuda").manual_seed(n + h)
+    x = torch.randn(n, h, generator=g, device=cuda_device).bfloat16()
+    wg = (torch.randn(e, h, generator=g, device=cuda_device) * 0.05).bfloat16()
+    idx, w, hist, _ = ops.router_top2(x, wg)
+    idx2, w2, chunks, _ = ops.router_top2(x, wg, want_chunks=True)
+    assert torch.equal(idx, idx2) and torch.equal(w, w2)
+    assert chunks.shape == ((n + 127) // 128, e)
+    ic = idx.cpu()
+    want = torch.stack([O.expert_histogram(ic[c * 128:(c + 1) * 128].reshape(-1), e) for c in range((n + 127) // 128)])
+    assert torch.equal(chunks.cpu().long(), want)
+    assert torch.equal(chunks.sum(0), hist)
+
+
+@pytest.mark.parametrize("n,e,world,k", [(1, 8, 1, 2), (127, 8, 1, 2), (129, 8, 2, 2), (1000, 8, 8, 2), (5000, 16, 8, 2),
+                                         (16384, 8, 1, 2), (3000, 16, 4, 2), (300, 64, 1, 2), (777, 8, 4, 1)])
+def test_chunked_plan_equals_three_pass_plan(cuda_device, n, e, world, k):
+    """dice_permute_plan_chunked (one launch, from per-256-row histograms, keys = (owner rank, local slot) of the
+    round-robin placement, optional fused row gather) gives exactly the plan and the rows of
+    dice_permute_plan on those keys + dice_permute_rows, which are checked against the oracle's stable argsort."""
+    ops = _ops()
+    h = 64
+    g = torch.Generator().manual_seed(n + e + world)
+    flat = torch.randint(0, e, (n * k,), generator=g)
+    if n >= 127:
+        flat[flat == 3] = 2  # an empty expert
+    x = torch.randn(n, h, generator=g).bfloat16().to(cuda_device)
+    chunks = torch.stack([O.expert_histogram(flat[c * 256:(c + 1) * 256], e) for c in range((n * k + 255) // 256)])
+    chunks = chunks.to(torch.int32).to(cuda_device)
+    el = e // world
+    keys = (flat % world) * el + flat // world
+    pos_w, seg_w, order_w = ops.permute_plan(keys.to(cuda_device), e, want_order=True)
+    rows_w = ops.permute_rows(x, pos_w, k)
+    order_o = O.stable_expert_order(keys)
+    assert torch.equal(order_w.cpu().long(), order_o)
+    pos, seg, order, rows = ops.permute_plan_chunked(flat.to(cuda_device), chunks, e, world, x, k, want_order=True)
+    assert torch.equal(pos, pos_w) and torch.equal(seg, seg_w) and torch.equal(order, order_w)
+    assert torch.equal(rows, rows_w)
+    pos2, seg2, _, none = ops.permute_plan_chunked(flat.to(cuda_device), chunks, e, world)
+    assert none is None and torch.equal(pos2, pos_w) and torch.equal(seg2, seg_w)
+
+
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
 @pytest.mark.parametrize("n,h,e", [(1, 64, 8), (129, 1152, 8), (512, 1792, 16)])
 def test_permute_rows_and_unpermute_combine(cuda_device, dtype, n, h, e):
