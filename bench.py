@@ -252,20 +252,29 @@ def full_model_step(blocks, tokens, device, begin_step, barrier, ep, steps=10):
         begin_step()
         return model.sampling_step(z, cond, null, t=1.0 - i / 50.0, dt=1.0 / 50.0)
 
-    for i in range(3):
-        step(i)
-    barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for i in range(steps):
-        step(i)
-    e1.record()
-    barrier()
-    ms = torch.tensor([e0.elapsed_time(e1) / steps], device=device)
-    if ep:
-        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-    return {"ms_per_step": round(float(ms.item()), 3), "images_per_gpu": images, "latent": latent,
-            "note": "MoE blocks: dice_b200 kernels; backbone (attention, adaLN, embeddings): PyTorch bf16 harness"}
+    def measure():
+        for i in range(3):
+            step(i)
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(steps):
+            step(i)
+        e1.record()
+        barrier()
+        ms = torch.tensor([e0.elapsed_time(e1) / steps], device=device)
+        if ep:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return round(float(ms.item()), 3)
+
+    model.set_fused_glue(False)
+    plain = measure()
+    model.set_fused_glue(True)
+    fused = measure()
+    return {"ms_per_step": fused, "ms_per_step_glue_in_torch": plain, "images_per_gpu": images, "latent": latent,
+            "note": "MoE blocks: dice_b200 kernels, with the LayerNorm + modulation in front of the block and the gated "
+                    "residual behind it inside them (ms_per_step) or as PyTorch element-wise kernels "
+                    "(ms_per_step_glue_in_torch); backbone (attention, adaLN, embeddings): PyTorch bf16 harness"}
 
 
 def phase_times(step_fn, layers, steps=3):

@@ -48,10 +48,13 @@ class _Block(nn.Module):
         self.norm2 = nn.LayerNorm(dim, elementwise_affine=False, eps=1e-6)
         self.moe = moe
         self.ada = nn.Sequential(nn.SiLU(), nn.Linear(dim, 6 * dim, bias=True))
+        self.fused_glue = True
 
     def forward(self, x, c):
         s1, c1, g1, s2, c2, g2 = self.ada(c).chunk(6, dim=1)
         x = x + g1.unsqueeze(1) * self.attn(_modulate(self.norm1(x), s1, c1))
+        if self.fused_glue:  # LayerNorm + modulation and the gated residual inside the MoE block's kernels
+            return self.moe.forward_with_glue(x, s2, c2, g2, eps=self.norm2.eps)
         return x + g2.unsqueeze(1) * self.moe(_modulate(self.norm2(x), s2, c2))
 
 
@@ -69,6 +72,10 @@ class DiTBackbone(nn.Module):
         self.final_norm = nn.LayerNorm(hidden, elementwise_affine=False, eps=1e-6)
         self.final_ada = nn.Sequential(nn.SiLU(), nn.Linear(hidden, 2 * hidden))
         self.final = nn.Linear(hidden, patch * patch * channels * 2)
+
+    def set_fused_glue(self, flag: bool) -> None:
+        for blk in self.blocks:
+            blk.fused_glue = flag
 
     def _t_embed(self, t):
         half = 128

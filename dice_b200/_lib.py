@@ -37,8 +37,12 @@ SIGNATURES = {
     "dice_permute_rows": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_void_p, c_void_p]),
     "dice_unpermute_combine": (
         c_int,
-        [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int64, c_int,
-         c_int, c_void_p, c_void_p],
+        [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+         c_int, c_int64, c_int, c_int, c_void_p, c_void_p],
+    ),
+    "dice_ln_modulate": (
+        c_int,
+        [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, ctypes.c_float, c_int, c_int, c_void_p, c_void_p],
     ),
     "dice_w13_rows": (c_int64, [c_int]),
     "dice_pack_w13": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]),

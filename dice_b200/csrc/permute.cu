@@ -257,7 +257,8 @@ __global__ void __launch_bounds__(256)
 unpermute_combine_kernel(const uint4* __restrict__ src0, const int* __restrict__ idx0, int idx0_stride,
                          const uint4* __restrict__ src1, const int* __restrict__ idx1, int idx1_stride,
                          const float* __restrict__ w0, const float* __restrict__ w1, int w_stride,
-                         const uint4* __restrict__ addend, int64_t n_tokens, int row_vec, uint4* __restrict__ out) {
+                         const uint4* __restrict__ addend, const uint4* __restrict__ resid, const uint4* __restrict__ gate,
+                         int tokens_per_sample, int64_t n_tokens, int row_vec, uint4* __restrict__ out) {
   constexpr int EL = Vec16<T>::kElems;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t t = static_cast<int64_t>(blockIdx.x) * 8 + warp;
@@ -271,6 +272,9 @@ unpermute_combine_kernel(const uint4* __restrict__ src0, const int* __restrict__
   const uint4* p0 = (i0 >= 0) ? src0 + i0 * row_vec : nullptr;
   const uint4* p1 = (i1 >= 0) ? src1 + i1 * row_vec : nullptr;
   const uint4* pa = addend ? addend + t * row_vec : nullptr;
+  // the gated residual of the DiT block: out = resid + gate[sample of t] * (the sum above)
+  const uint4* pr = resid ? resid + t * row_vec : nullptr;
+  const uint4* pg = gate ? gate + (t / tokens_per_sample) * row_vec : nullptr;
   uint4* po = out + t * row_vec;
 #pragma unroll 2
   for (int c = lane; c < row_vec; c += 32) {
@@ -292,6 +296,18 @@ unpermute_combine_kernel(const uint4* __restrict__ src0, const int* __restrict__
     if (pa) {
       float f[EL];
       Vec16<T>::to_float(ldg_stream16(pa + c), f);
+#pragma unroll
+      for (int j = 0; j < EL; ++j) acc[j] += f[j];
+    }
+    if (pg) {
+      float f[EL];
+      Vec16<T>::to_float(__ldg(pg + c), f);
+#pragma unroll
+      for (int j = 0; j < EL; ++j) acc[j] *= f[j];
+    }
+    if (pr) {
+      float f[EL];
+      Vec16<T>::to_float(ldg_stream16(pr + c), f);
 #pragma unroll
       for (int j = 0; j < EL; ++j) acc[j] += f[j];
     }
@@ -456,16 +472,20 @@ extern "C" int dice_permute_rows(const void* x, const int32_t* pos, int64_t n_to
 
 extern "C" int dice_unpermute_combine(const void* src0, const int32_t* idx0, int idx0_stride, const void* src1,
                                       const int32_t* idx1, int idx1_stride, const float* w0, const float* w1,
-                                      int w_stride, const void* addend, int64_t n_tokens, int hidden, int dtype,
-                                      void* out, void* stream) {
+                                      int w_stride, const void* addend, const void* resid, const void* gate,
+                                      int tokens_per_sample, int64_t n_tokens, int hidden, int dtype, void* out,
+                                      void* stream) {
   DICE_CHECK_ARG(n_tokens >= 0 && hidden > 0, DICE_ERR_ARG);
+  DICE_CHECK_ARG(gate == nullptr || tokens_per_sample > 0, DICE_ERR_ARG);
   const size_t es = dice_dtype_size(dtype);
   DICE_CHECK_ARG(es != 0, DICE_ERR_DTYPE);
   DICE_CHECK_ARG((hidden * es) % 16 == 0, DICE_ERR_SHAPE);
   if (n_tokens == 0) return DICE_OK;
   DICE_CHECK_ARG(src0 && out, DICE_ERR_ARG);
-  DICE_CHECK_ARG(dice_aligned16(src0) && dice_aligned16(out) && dice_aligned16(src1) && dice_aligned16(addend),
+  DICE_CHECK_ARG(dice_aligned16(src0) && dice_aligned16(out) && dice_aligned16(src1) && dice_aligned16(addend) &&
+                     dice_aligned16(resid) && dice_aligned16(gate),
                  DICE_ERR_ALIGN);
+  if (tokens_per_sample <= 0) tokens_per_sample = 1;
   const int row_vec = static_cast<int>(hidden * es / 16);
   const int64_t blocks = (n_tokens + 7) / 8;
   DICE_CHECK_ARG(blocks <= 0x7fffffffLL, DICE_ERR_LIMIT);
@@ -474,12 +494,14 @@ extern "C" int dice_unpermute_combine(const void* src0, const int32_t* idx0, int
   if (dtype == DICE_BF16)
     DICE_CUDA_OK(dice_launch(unpermute_combine_kernel<__nv_bfloat16>, grid, dim3(256), 0, s,
                              static_cast<const uint4*>(src0), idx0, idx0_stride, static_cast<const uint4*>(src1), idx1,
-                             idx1_stride, w0, w1, w_stride, static_cast<const uint4*>(addend), n_tokens, row_vec,
-                             static_cast<uint4*>(out)));
+                             idx1_stride, w0, w1, w_stride, static_cast<const uint4*>(addend),
+                             static_cast<const uint4*>(resid), static_cast<const uint4*>(gate), tokens_per_sample, n_tokens,
+                             row_vec, static_cast<uint4*>(out)));
   else
     DICE_CUDA_OK(dice_launch(unpermute_combine_kernel<float>, grid, dim3(256), 0, s, static_cast<const uint4*>(src0),
                              idx0, idx0_stride, static_cast<const uint4*>(src1), idx1, idx1_stride, w0, w1, w_stride,
-                             static_cast<const uint4*>(addend), n_tokens, row_vec, static_cast<uint4*>(out)));
+                             static_cast<const uint4*>(addend), static_cast<const uint4*>(resid),
+                             static_cast<const uint4*>(gate), tokens_per_sample, n_tokens, row_vec, static_cast<uint4*>(out)));
   return DICE_OK;
 }
 

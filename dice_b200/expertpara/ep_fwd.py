@@ -72,10 +72,10 @@ class CudaOps:
 
         return ops.permute_rows(x, pos, k)
 
-    def unpermute_combine(self, src0, idx0, src1, idx1, w0, w1, n_tokens, addend=None):
+    def unpermute_combine(self, src0, idx0, src1, idx1, w0, w1, n_tokens, addend=None, **glue):
         from .. import ops
 
-        return ops.unpermute_combine(src0, idx0, src1, idx1, w0, w1, n_tokens, addend=addend)
+        return ops.unpermute_combine(src0, idx0, src1, idx1, w0, w1, n_tokens, addend=addend, **glue)
 
     def run_packed_experts(self, rows, pack, seg_counts: Sequence[int], seg_slab: Sequence[int], seg_offsets_dev=None):
         if seg_offsets_dev is not None:
@@ -337,7 +337,7 @@ def _pick(pairs: torch.Tensor, const_slot: Optional[int], per_tok: Optional[torc
 @torch.no_grad()
 def moe_infer_ep(inp: torch.Tensor, experts: nn.ModuleList, flat_expert_indices, flat_expert_weights,
                  num_experts_per_tok, async_op, skip_mask=None, skip_now=None, cache_key=None, _addend=None,
-                 _chunks=None):
+                 _chunks=None, _glue=None):
     """Expert-parallel replacement of ``SparseMoeBlock.moe_infer``
     (ep_fwd.py:19-197; same arguments and result).
 
@@ -348,7 +348,9 @@ def moe_infer_ep(inp: torch.Tensor, experts: nn.ModuleList, flat_expert_indices,
     conditional communication; ``cache_key`` is the layer index.  ``_addend``
     (not in the reference) is added to the result inside the combine kernel;
     ``_chunks`` (not in the reference) is the router's per-128-token histogram
-    table, from which the plan is a single launch."""
+    table, from which the plan is a single launch; ``_glue`` (not in the
+    reference) is ``(residual [N, h], gate [B, h], tokens per sample)``: the
+    DiT block's gated residual, applied by the same combine kernel."""
     world_size, rank = dist.get_world_size(), dist.get_rank()
     num_total_experts = len(experts)
     num_local_experts = num_total_experts // world_size
@@ -434,13 +436,14 @@ def moe_infer_ep(inp: torch.Tensor, experts: nn.ModuleList, flat_expert_indices,
                 grouped_idx_dup=pos, flat_expert_weights=flat_expert_weights, cache_key=cache_key)
 
     return _finish(grouped_dup_outp, pos, latest_flat_expert_weights, flat_expert_weights, n_tokens, hidden, k_full,
-                   partial_skip, const_slot, per_tok, cache_key, _addend, inp)
+                   partial_skip, const_slot, per_tok, cache_key, _addend, inp, _glue)
 
 
 def _finish(grouped_dup_outp, pos, latest_flat_expert_weights, flat_expert_weights, n_tokens, hidden, k_full,
-            partial_skip, const_slot, per_tok, cache_key, _addend, inp):
+            partial_skip, const_slot, per_tok, cache_key, _addend, inp, _glue=None):
     """Un-permute, merge with the skip cache, scale by the gate weights and sum
     each token's pair (ep_fwd.py:172-195) in one kernel."""
+    glue = {} if _glue is None else dict(resid=_glue[0], gate=_glue[1], tokens_per_sample=_glue[2])
     weights = latest_flat_expert_weights if _use_latest_expert_weights else flat_expert_weights
     w_pairs = weights.reshape(n_tokens, k_full)
     if w_pairs.dtype != torch.float32:
@@ -457,7 +460,7 @@ def _finish(grouped_dup_outp, pos, latest_flat_expert_weights, flat_expert_weigh
             if per_tok is not None:
                 w_kept, w_drop = w_kept.contiguous(), w_drop.contiguous()
             expert_out = _ops.unpermute_combine(grouped_dup_outp, pos, dropped, None, w_kept, w_drop, n_tokens,
-                                                addend=_addend)
+                                                addend=_addend, **glue)
         else:
             assert got_rows == n_tokens * k_full
             pos_pairs = pos.view(n_tokens, k_full)
@@ -469,10 +472,10 @@ def _finish(grouped_dup_outp, pos, latest_flat_expert_weights, flat_expert_weigh
             if k_full == 2:
                 expert_out = _ops.unpermute_combine(grouped_dup_outp, pos_pairs[:, 0], grouped_dup_outp,
                                                     pos_pairs[:, 1], w_pairs[:, 0], w_pairs[:, 1], n_tokens,
-                                                    addend=_addend)
+                                                    addend=_addend, **glue)
             else:
                 assert k_full == 1, "num_experts_per_tok must be 1 or 2"
                 expert_out = _ops.unpermute_combine(grouped_dup_outp, pos_pairs[:, 0], None, None, w_pairs[:, 0],
-                                                    None, n_tokens, addend=_addend)
+                                                    None, n_tokens, addend=_addend, **glue)
     assert expert_out.shape == inp.shape, f"{expert_out.shape} != {inp.shape}"
     return expert_out

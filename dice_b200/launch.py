@@ -7,15 +7,36 @@
 ``expertpara.{ep_fwd,diep,ep_cache,etrim}`` (before anything imports names
 from them) and its ``SparseMoeBlock`` / ``MoEGate`` / ``MoeMLP`` in the place
 of the classes of the reference's ``models`` module, which ``DiTBlock`` looks
-up by name when it builds a block (models.py:498-507).  Everything else of the
-reference (DiT backbone, samplers, flags, state-dict loading) runs as is.
+up by name when it builds a block (models.py:498-507), and lets
+``DiTBlock.forward`` hand the LayerNorm + modulation in front of the MoE block
+and the gated residual behind it to the block's kernels.  Everything else of
+the reference (DiT backbone, attention, samplers, flags, state-dict loading)
+runs as is.
 """
 from __future__ import annotations
 
+import contextlib
 import importlib
 import os
 import runpy
 import sys
+
+
+def _ditblock_forward(self, x, c):
+    """``DiTBlock.forward`` (models.py:514-520) with its MoE half handed to
+    ``SparseMoeBlock.forward_with_glue``: the attention half is the
+    reference's, the LayerNorm + modulation in front of the MoE block and the
+    gated residual behind it run inside this package's kernels."""
+    from .expertpara import diep
+
+    prof = diep._profiler()
+    scope = prof.scope if prof is not None else (lambda name: contextlib.nullcontext())
+    shift_msa, scale_msa, gate_msa, shift_mlp, scale_mlp, gate_mlp = self.adaLN_modulation(c).chunk(6, dim=1)
+    with scope("attn"):
+        normed = self.norm1(x)
+        x = x + gate_msa.unsqueeze(1) * self.attn(normed * (1 + scale_msa.unsqueeze(1)) + shift_msa.unsqueeze(1))
+    with scope("moe"):
+        return self.moe.forward_with_glue(x, shift_mlp, scale_mlp, gate_mlp, eps=self.norm2.eps)
 
 
 def install(reference_root: str | None = None):
@@ -41,6 +62,9 @@ def install(reference_root: str | None = None):
     models.MoEGate = moe_block.MoEGate
     models.MoeMLP = moe_block.MoeMLP
     models.trim_module_list = etrim.trim_module_list
+    # the element-wise glue around the MoE block moves into its kernels unless DICE_FUSED_GLUE=0
+    if os.environ.get("DICE_FUSED_GLUE", "1") != "0":
+        models.DiTBlock.forward = _ditblock_forward
     # expert parallelism exchanges rows over NVLink peer memory unless DICE_EP_P2P=0 (NCCL is the fallback
     # when peer memory cannot be mapped)
     if os.environ.get("DICE_EP_P2P", "1") != "0":

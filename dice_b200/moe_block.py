@@ -415,7 +415,31 @@ class SparseMoeBlock(nn.Module):
         return self._forward_infer(hidden_states)
 
     @torch.no_grad()
-    def _forward_infer(self, hidden_states):
+    def forward_with_glue(self, x, shift, scale, gate, eps: float = 1e-6):
+        """The MoE half of ``DiTBlock.forward`` (models.py:518-519),
+
+            x + gate.unsqueeze(1) * self(modulate(LayerNorm(x), shift, scale)),
+
+        with the LayerNorm (no affine parameters, models.py:494) and the
+        modulation (models.py:75-76) in one kernel in front of the router and
+        the gated residual inside the combine kernel: two full passes over
+        ``[N, h]`` instead of six or seven.  ``x`` is ``[B, T, h]``; ``shift``,
+        ``scale`` and ``gate`` are ``[B, h]`` (views are fine).  Training, CPU
+        tensors and 16-bit floats other than bf16 take the plain formulation."""
+        fusable = (not self.training and x.is_cuda and x.dim() == 3 and x.dtype in (torch.bfloat16, torch.float32))
+        if not fusable:
+            normed = F.layer_norm(x, x.shape[-1:], None, None, eps)
+            return x + gate.unsqueeze(1) * self(normed * (1 + scale.unsqueeze(1)) + shift.unsqueeze(1))
+        cd = _compute_dtype(x)
+        x = x.contiguous()
+        x_in = ops.ln_modulate(x, shift.to(x.dtype), scale.to(x.dtype), eps, out_dtype=cd)
+        if x.dtype != cd:  # fp32 residual stream around a 16-bit block: the residual stays in torch
+            return x + gate.unsqueeze(1) * self._forward_infer(x_in).to(x.dtype)
+        glue = (x.view(-1, x.shape[-1]), gate.to(cd).contiguous(), x.shape[1])
+        return self._forward_infer(x_in, _glue=glue)
+
+    @torch.no_grad()
+    def _forward_infer(self, hidden_states, _glue=None):
         orig_shape, orig_dtype = hidden_states.shape, hidden_states.dtype
         h = orig_shape[-1]
         cd = _compute_dtype(hidden_states)
@@ -441,7 +465,8 @@ class SparseMoeBlock(nn.Module):
             with _scope("moe.mlp_shared"):
                 shared_out = self._shared_pack.run_offsets(x, self._segment_all(n_tokens, x.device), reserve_sms=reserve)
         if not self.para_mode.ep:
-            y = self.moe_infer(x, topk_idx.view(-1), topk_weight.view(-1, 1), _addend=shared_out, _chunks=chunks)
+            y = self.moe_infer(x, topk_idx.view(-1), topk_weight.view(-1, 1), _addend=shared_out, _chunks=chunks,
+                               _glue=_glue)
         else:
             from .expertpara.diep import ep_skip_enabled, ep_skip_mask, ep_skip_now
             from .expertpara.ep_fwd import moe_infer_ep
@@ -452,12 +477,12 @@ class SparseMoeBlock(nn.Module):
                 flat_expert_weights=topk_weight.view(-1, 1), num_experts_per_tok=self.num_experts_per_tok,
                 skip_mask=ep_skip_mask(topk_idx.numel()) if partial_skip else None,
                 skip_now=ep_skip_now(self.layer_idx) if partial_skip else None,
-                async_op=self._async_layer(), cache_key=self.layer_idx, _addend=shared_out, _chunks=chunks)
+                async_op=self._async_layer(), cache_key=self.layer_idx, _addend=shared_out, _chunks=chunks, _glue=_glue)
         y = y.view(*orig_shape)
         return y if y.dtype == orig_dtype else y.to(orig_dtype)
 
     @torch.no_grad()
-    def moe_infer(self, x, flat_expert_indices, flat_expert_weights, _addend=None, _chunks=None):
+    def moe_infer(self, x, flat_expert_indices, flat_expert_weights, _addend=None, _chunks=None, _glue=None):
         """Single-device dispatch -> experts -> weighted combine
         (models.py:361-382), without a host sync: plan + row gather (one
         launch when the router filed per-chunk histograms, else four), two
@@ -475,7 +500,9 @@ class SparseMoeBlock(nn.Module):
         w = flat_expert_weights.view(n_tokens, k)
         w = w if w.dtype == torch.float32 else w.float()
         pp = pos.view(n_tokens, k)
-        return ops.unpermute_combine(y_rows, pp[:, 0], y_rows, pp[:, 1], w[:, 0], w[:, 1], n_tokens, addend=_addend)
+        resid, gate, tps = _glue if _glue is not None else (None, None, 1)
+        return ops.unpermute_combine(y_rows, pp[:, 0], y_rows, pp[:, 1], w[:, 0], w[:, 1], n_tokens, addend=_addend,
+                                     resid=resid, gate=gate, tokens_per_sample=tps)
 
     def _forward_train(self, hidden_states):
         """models.py:313-320 with differentiable torch operations."""

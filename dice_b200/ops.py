@@ -266,12 +266,17 @@ def unpermute_combine(
     n_tokens: int,
     addend: Optional[torch.Tensor] = None,
     out: Optional[torch.Tensor] = None,
+    resid: Optional[torch.Tensor] = None,
+    gate: Optional[torch.Tensor] = None,
+    tokens_per_sample: int = 1,
 ) -> torch.Tensor:
-    """``out[t] = w0[t]*src0[idx0[t]] + w1[t]*src1[idx1[t]] + addend[t]``.
+    """``y[t] = w0[t]*src0[idx0[t]] + w1[t]*src1[idx1[t]] + addend[t]`` and
+    ``out[t] = resid[t] + gate[t // tokens_per_sample] * y[t]`` (residual and
+    gate optional: the DiT block's ``x + gate_mlp * moe(...)``, models.py:519).
 
     ``idx*`` and ``w*`` may be strided 1-D views (e.g. ``pos[0::2]``); the two
     weight views must share one stride.  Replaces ep_fwd.py:172-195."""
-    _require_cuda(src0, idx0, src1, idx1, w0, w1, addend, out)
+    _require_cuda(src0, idx0, src1, idx1, w0, w1, addend, out, resid, gate)
     h = src0.shape[1]
     assert src0.is_contiguous() and (src1 is None or (src1.is_contiguous() and src1.dtype == src0.dtype))
     for i in (idx0, idx1):
@@ -285,6 +290,11 @@ def unpermute_combine(
         assert w0.stride(0) == w1.stride(0)
     if addend is not None:
         assert addend.is_contiguous() and addend.shape == (n_tokens, h) and addend.dtype == src0.dtype
+    if resid is not None:
+        assert resid.is_contiguous() and resid.shape == (n_tokens, h) and resid.dtype == src0.dtype
+    if gate is not None:
+        assert gate.is_contiguous() and gate.dim() == 2 and gate.shape[1] == h and gate.dtype == src0.dtype
+        assert gate.shape[0] * tokens_per_sample >= n_tokens
     if out is None:
         out = torch.empty((n_tokens, h), dtype=src0.dtype, device=src0.device)
     assert out.is_contiguous() and out.shape == (n_tokens, h) and out.dtype == src0.dtype
@@ -293,9 +303,32 @@ def unpermute_combine(
     _lib.check(
         _lib.load().dice_unpermute_combine(
             _ptr(src0), _ptr(idx0), s0, _ptr(src1), _ptr(idx1), s1, _ptr(w0), _ptr(w1), w_stride, _ptr(addend),
-            n_tokens, h, _dtype_code(src0), _ptr(out), _stream(),
+            _ptr(resid), _ptr(gate), tokens_per_sample, n_tokens, h, _dtype_code(src0), _ptr(out), _stream(),
         ),
         "dice_unpermute_combine",
+    )
+    return out
+
+
+def ln_modulate(x: torch.Tensor, shift: torch.Tensor, scale: torch.Tensor, eps: float = 1e-6,
+                out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """``LayerNorm(x) * (1 + scale[:, None]) + shift[:, None]`` in one pass
+    (``modulate(self.norm2(x), shift_mlp, scale_mlp)``, models.py:75-76, :494,
+    :519).  ``x`` is ``[B, T, h]``, ``shift`` / ``scale`` are ``[B, h]`` of
+    the same dtype (bf16 or fp32); statistics in fp32."""
+    _require_cuda(x, shift, scale)
+    assert x.dim() == 3 and shift.shape == (x.shape[0], x.shape[2]) and scale.shape == shift.shape
+    assert shift.dtype == x.dtype and scale.dtype == x.dtype
+    x, shift, scale = x.contiguous(), shift.contiguous(), scale.contiguous()
+    b, t, h = x.shape
+    out_dtype = out_dtype or x.dtype
+    out = torch.empty((b, t, h), dtype=out_dtype, device=x.device)
+    code_out = DICE_BF16 if out_dtype == torch.bfloat16 else DICE_F32
+    assert out_dtype in (torch.bfloat16, torch.float32)
+    _lib.check(
+        _lib.load().dice_ln_modulate(_ptr(x), _ptr(shift), _ptr(scale), b * t, h, t, float(eps), _dtype_code(x), code_out,
+                                     _ptr(out), _stream()),
+        "dice_ln_modulate",
     )
     return out
 

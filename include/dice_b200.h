@@ -181,15 +181,32 @@ DICE_API int dice_permute_rows(const void* x, const int32_t* pos, int64_t n_toke
  * merge (ep_fwd.py:177-187), mul_ by the gate weights (:190-193) and the
  * pair sum (:195); on one device the mul_/scatter_reduce_ of
  * models.py:377-381 and the shared-expert add of models.py:357.
- *   out[t] = w0[t*w_stride] * src0[i0] + w1[t*w_stride] * src1[i1] + addend[t]
+ *   y[t]   = w0[t*w_stride] * src0[i0] + w1[t*w_stride] * src1[i1] + addend[t]
+ *   out[t] = resid[t] + gate[t / tokens_per_sample] * y[t]
  * with i0 = idx0 ? idx0[t*idx0_stride] : t (same for i1).  src1 == NULL drops
  * the second term, w0/w1 == NULL mean weight 1, addend == NULL means 0.
  * A negative index contributes 0.  Sums are formed in fp32.
+ * resid [n_tokens, hidden] and gate [n_samples, hidden] (either may be NULL:
+ * no residual / gate 1) fold the DiT block's gated residual around the MoE
+ * block, x + gate_mlp.unsqueeze(1) * moe(...) (models.py:519), into the same
+ * pass.
  */
 DICE_API int dice_unpermute_combine(const void* src0, const int32_t* idx0, int idx0_stride, const void* src1,
                            const int32_t* idx1, int idx1_stride, const float* w0, const float* w1,
-                           int w_stride, const void* addend, int64_t n_tokens, int hidden, int dtype,
-                           void* out, void* stream);
+                           int w_stride, const void* addend, const void* resid, const void* gate,
+                           int tokens_per_sample, int64_t n_tokens, int hidden, int dtype, void* out,
+                           void* stream);
+
+/* ---------------------------------------------------------------------------
+ * The DiT block's input glue in one pass (models.py:75-76, :494, :519):
+ *   out[t] = LayerNorm(x[t]) * (1 + scale[b]) + shift[b],  b = t / tokens_per_sample
+ * LayerNorm over `hidden` without affine parameters, statistics in fp32 (two
+ * passes over the row, which stays in registers); x, shift [n_samples, hidden]
+ * and scale have element type `dtype`, out has `out_dtype` (bf16 -> bf16,
+ * fp32 -> fp32 or fp32 -> bf16).  hidden <= 2048.
+ */
+DICE_API int dice_ln_modulate(const void* x, const void* shift, const void* scale, int64_t n_tokens, int hidden,
+                     int tokens_per_sample, float eps, int dtype, int out_dtype, void* out, void* stream);
 
 /* ---------------------------------------------------------------------------
  * Expert weights.  SwiGLU experts (models.py:246-247) are packed once at load

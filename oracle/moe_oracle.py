@@ -167,6 +167,20 @@ def moe_block_forward(
     }
 
 
+def modulate(x: torch.Tensor, shift: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
+    """models.py:75-76."""
+    return x * (1 + scale.unsqueeze(1)) + shift.unsqueeze(1)
+
+
+def dit_block_moe_half(x, shift_mlp, scale_mlp, gate_mlp, moe_fn, eps: float = 1e-6) -> torch.Tensor:
+    """The MoE half of DiTBlock.forward (models.py:518-519) around any block
+    function: ``x + gate_mlp.unsqueeze(1) * moe(modulate(norm2(x), shift_mlp,
+    scale_mlp))`` with ``norm2 = LayerNorm(hidden, elementwise_affine=False,
+    eps=1e-6)`` (models.py:494)."""
+    normed = F.layer_norm(x, x.shape[-1:], None, None, eps)
+    return x + gate_mlp.unsqueeze(1) * moe_fn(modulate(normed, shift_mlp, scale_mlp))
+
+
 # ----------------------------------------------------------------------------
 # Expert-parallel building blocks (per-rank restatement; the collectives are
 # the caller's)
