@@ -318,7 +318,7 @@ def ffn_flops(tokens, variant):
     return rows * per_row
 
 
-def hbm_rooflines(blocks, xs, peak_gbs, reps=3):
+def hbm_rooflines(blocks, xs, peak_gbs, reps=10):
     """The HBM-bound kernels of the block, each timed alone with CUDA events over all layers' inputs (one
     distinct 37.7 MB input per layer: the working set between two uses of a buffer exceeds the 126 MB L2),
     against their algorithmic bytes: router N*h*2 + E*h*2 + 24 N + 4 E; row gather and combine N*h*2 + R*h*2 +
@@ -335,7 +335,8 @@ def hbm_rooflines(blocks, xs, peak_gbs, reps=3):
     outs = [torch.empty((n, h), dtype=torch.bfloat16, device=xs[0].device) for _ in range(min(len(xs), 4))]
 
     def timed(fn):
-        fn()
+        for _ in range(3):
+            fn()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         torch.cuda.synchronize()
         e0.record()

@@ -30,6 +30,7 @@ from __future__ import annotations
 
 import torch
 
+from ..ops import no_grad as _no_grad
 from .ep_cache import All2AllCache, EPSkipCache
 
 _CACHE_DISPATCH_VAL_LEN = 8  # (handles, recv, counts_local, counts_global, pos, weights, experts, send)
@@ -212,6 +213,20 @@ def ep_skip_put(key, tensor):
 # ---- the two protocols (diep.py:178-310) ------------------------------------------
 
 
+_ep_fwd_module = None
+
+
+def _ep_fwd():
+    """``expertpara.ep_fwd`` (imported late: that module imports this one); looked up through
+    ``sys.modules`` semantics once, then cached, but re-read when someone replaced the module attribute."""
+    global _ep_fwd_module
+    if _ep_fwd_module is None:
+        from . import ep_fwd
+
+        _ep_fwd_module = ep_fwd
+    return _ep_fwd_module
+
+
 def _wait(handles):
     if handles is not None:
         for handle in handles:
@@ -234,14 +249,13 @@ def _past_layer_key(key):
     raise ValueError(f"Unknown selective async strategy: {_selective_async_strategy}")
 
 
-@torch.no_grad()
+@_no_grad
 def global_dispatch_async(grouped_dup_inp, token_counts_local, token_counts_global, grouped_idx_dup,
                           flat_expert_weights, experts, cache_key):
     """Launch this call's dispatch and hand back an earlier one to compute on
     (diep.py:196-259).  Returns ``(recv_rows, counts_local, counts_global,
     pos, weights, experts)`` of the exchange being consumed."""
-    from .ep_fwd import global_dispatch
-
+    global_dispatch = _ep_fwd().global_dispatch
     assert cache_key is not None
     if _forced_sync:
         buf, _ = global_dispatch(grouped_dup_inp, token_counts_local, token_counts_global, async_op=False)
@@ -270,14 +284,13 @@ def global_dispatch_async(grouped_dup_inp, token_counts_local, token_counts_glob
     return prev_buf, prev_counts_local, prev_counts_global, prev_pos, prev_weights, prev_experts
 
 
-@torch.no_grad()
+@_no_grad
 def global_combine_async(grouped_dup_outp, token_counts_local, token_counts_global, grouped_idx_dup,
                          flat_expert_weights, cache_key):
     """Launch the combine of the rows just computed and hand back the combine
     stored for this layer (diep.py:261-310).  Returns ``(rows, pos, weights)``
     of the exchange being consumed."""
-    from .ep_fwd import global_combine
-
+    global_combine = _ep_fwd().global_combine
     assert cache_key is not None
     if _forced_sync:
         buf, _ = global_combine(grouped_dup_outp, token_counts_local, token_counts_global, async_op=False)

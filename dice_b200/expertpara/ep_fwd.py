@@ -30,6 +30,8 @@ import torch
 import torch.distributed as dist
 import torch.nn as nn
 
+from .. import _lib, ops as _dops
+from ..ops import _dtype_code, _stream, no_grad
 from . import diep, p2p
 from .diep import ep_skip_get, ep_skip_put, global_combine_async, global_dispatch_async  # noqa: F401
 
@@ -55,27 +57,19 @@ class CudaOps:
     kernels and refuses CPU tensors."""
 
     def plan(self, keys: torch.Tensor, n_keys: int):
-        from .. import ops
-
-        pos, seg, _ = ops.permute_plan(keys, n_keys)
+        pos, seg, _ = _dops.permute_plan(keys, n_keys)
         return pos, seg
 
     def plan_chunked(self, flat_idx: torch.Tensor, chunk_hist: torch.Tensor, n_experts: int, world: int):
         """Plan by (owner rank, local slot) in one launch, from the router's per-chunk histograms."""
-        from .. import ops
-
-        pos, seg, _, _ = ops.permute_plan_chunked(flat_idx, chunk_hist, n_experts, world)
+        pos, seg, _, _ = _dops.permute_plan_chunked(flat_idx, chunk_hist, n_experts, world)
         return pos, seg
 
     def permute_rows(self, x: torch.Tensor, pos: torch.Tensor, k: int) -> torch.Tensor:
-        from .. import ops
-
-        return ops.permute_rows(x, pos, k)
+        return _dops.permute_rows(x, pos, k)
 
     def unpermute_combine(self, src0, idx0, src1, idx1, w0, w1, n_tokens, addend=None, **glue):
-        from .. import ops
-
-        return ops.unpermute_combine(src0, idx0, src1, idx1, w0, w1, n_tokens, addend=addend, **glue)
+        return _dops.unpermute_combine(src0, idx0, src1, idx1, w0, w1, n_tokens, addend=addend, **glue)
 
     def run_packed_experts(self, rows, pack, seg_counts: Sequence[int], seg_slab: Sequence[int], seg_offsets_dev=None):
         if seg_offsets_dev is not None:
@@ -111,7 +105,7 @@ def _scope(name: str):
 # --------------------------------------------------------------------------- #
 
 
-@torch.no_grad()
+@no_grad
 def exchange_token_counts(token_counts_local: torch.Tensor) -> torch.Tensor:
     """ep_fwd.py:214-245: all-gather the per-expert row counts (expert-id
     order, length E) and return the ``[world_size, E/W]`` counts of rows each
@@ -166,7 +160,7 @@ def _all_to_all_rows(send: torch.Tensor, in_counts: torch.Tensor, out_counts: to
     return buf, [handle]
 
 
-@torch.no_grad()
+@no_grad
 def global_dispatch(grouped_dup_inp, token_counts_local, token_counts_global, async_op=False):
     """Send owner-sorted rows to the expert owners (ep_fwd.py:247-293).
 
@@ -183,7 +177,7 @@ def global_dispatch(grouped_dup_inp, token_counts_local, token_counts_global, as
     return _all_to_all_rows(grouped_dup_inp, token_counts_local, token_counts_global, async_op)
 
 
-@torch.no_grad()
+@no_grad
 def global_combine(grouped_dup_outp, token_counts_local, token_counts_global, async_op=False):
     """Return expert outputs to the token owners; the mirror image of
     :func:`global_dispatch` (ep_fwd.py:295-342).  With the peer-memory exchange
@@ -203,9 +197,6 @@ def global_combine(grouped_dup_outp, token_counts_local, token_counts_global, as
 def _peer_push(info, async_op, dispatch=None, rows_back=None):
     """Launch one push of the peer-memory exchange (csrc/p2p_exchange.cu) and
     return ``(buffer the peers fill for this rank, [handle])``."""
-    from .. import _lib
-    from ..ops import _dtype_code, _stream
-
     x = info.xchg
     lib, tab, slot = x.lib, info.tab, info.slot
     # 0: the push owns the GPU (one copy-unit warp per SM); an asynchronous push runs next to the expert FFN on
@@ -248,7 +239,7 @@ def _peer_push(info, async_op, dispatch=None, rows_back=None):
 # --------------------------------------------------------------------------- #
 
 
-@torch.no_grad()
+@no_grad
 def proc_experts(inp, experts, token_counts_global, num_local_experts):
     """Run this rank's experts over the received rows (ep_fwd.py:199-211).
 
@@ -257,9 +248,7 @@ def proc_experts(inp, experts, token_counts_global, num_local_experts):
     ``rank + i * world_size``).  Expert lists built by ``SparseMoeBlock`` carry
     packed weights and run as one grouped-FFN launch pair; any other list of
     row-wise modules is called segment by segment, as the reference does."""
-    world_size, rank = dist.get_world_size(), dist.get_rank()
     if isinstance(token_counts_global, p2p.SegInfo):
-        seg_slab = [i for _ in range(world_size) for i in range(num_local_experts)]
         pack = getattr(experts, "_dice_pack", None)
         if pack is not None:
             if inp.dtype == torch.bfloat16 and p2p.fused_return():
@@ -267,12 +256,15 @@ def proc_experts(inp, experts, token_counts_global, num_local_experts):
                 return p2p.ReturnedRows(token_counts_global)
             return pack.run_offsets(inp, token_counts_global.seg_dev, token_counts_global.xchg.seg_slab_dev,
                                     reserve_sms=p2p.reserve_sms())
+        world_size, rank = token_counts_global.xchg.world, token_counts_global.xchg.rank
+        seg_slab = token_counts_global.xchg.seg_slab
         offs = token_counts_global.seg_dev.tolist()  # arbitrary expert modules need the bounds on the host
         outp = torch.empty_like(inp)
         for j, slot in enumerate(seg_slab):
             if offs[j + 1] > offs[j]:
                 outp[offs[j]:offs[j + 1]] = experts[rank + slot * world_size](inp[offs[j]:offs[j + 1]])
         return outp
+    world_size, rank = dist.get_world_size(), dist.get_rank()
     counts = token_counts_global.tolist()  # CPU tensor: no device sync
     seg_counts = [counts[s][i] for s in range(world_size) for i in range(num_local_experts)]
     seg_slab = [i for _ in range(world_size) for i in range(num_local_experts)]
@@ -334,7 +326,7 @@ def _pick(pairs: torch.Tensor, const_slot: Optional[int], per_tok: Optional[torc
     return pairs.gather(1, sel.view(-1, 1)).view(-1)
 
 
-@torch.no_grad()
+@no_grad
 def moe_infer_ep(inp: torch.Tensor, experts: nn.ModuleList, flat_expert_indices, flat_expert_weights,
                  num_experts_per_tok, async_op, skip_mask=None, skip_now=None, cache_key=None, _addend=None,
                  _chunks=None, _glue=None):
@@ -351,7 +343,8 @@ def moe_infer_ep(inp: torch.Tensor, experts: nn.ModuleList, flat_expert_indices,
     table, from which the plan is a single launch; ``_glue`` (not in the
     reference) is ``(residual [N, h], gate [B, h], tokens per sample)``: the
     DiT block's gated residual, applied by the same combine kernel."""
-    world_size, rank = dist.get_world_size(), dist.get_rank()
+    live = p2p._exchange if p2p.enabled() else None  # knows this rank's place without asking c10d per layer
+    world_size, rank = (live.world, live.rank) if live is not None else (dist.get_world_size(), dist.get_rank())
     num_total_experts = len(experts)
     num_local_experts = num_total_experts // world_size
     assert num_total_experts % world_size == 0, "Number of experts must be divisible by world size"
@@ -387,9 +380,6 @@ def moe_infer_ep(inp: torch.Tensor, experts: nn.ModuleList, flat_expert_indices,
         cached_layers = diep._diep_cache_dispatch.capacity if diep._diep_cache_dispatch is not None else 0
         xchg = p2p.get_exchange(num_total_experts, hidden, inp.dtype, n_tokens * k_full, max(1, cached_layers))
     if xchg is not None:
-        from .. import _lib
-        from ..ops import _stream
-
         inp = inp.contiguous()
         slot, seq, tab = xchg.begin(cache_key or 0)
         # An exchange that nobody waits for in this layer (displaced / interweaved) keeps even its count exchange,

@@ -187,7 +187,9 @@ class PeerExchange:
         """Order the side stream (on which asynchronous pushes run next to the
         expert FFN) after everything enqueued so far on the current stream;
         returns its raw handle."""
-        self._fork.record()
+        from ..ops import current_stream_object
+
+        self._fork.record(current_stream_object())
         self._comm.wait_event(self._fork)
         return self.comm_raw
 
@@ -240,7 +242,10 @@ def side_push_ctas() -> int:
     number of SMs free, so the two never compete for an SM: the push moves its
     rows with the copy unit through shared memory, the GEMM keeps its own SMs
     to itself."""
-    return int(os.environ.get("DICE_EP_P2P_SIDE_CTAS", "8"))
+    return _side_ctas
+
+
+_side_ctas = int(os.environ.get("DICE_EP_P2P_SIDE_CTAS", "8"))  # read once: this is on the per-layer path
 
 
 _side_pushes = False
@@ -372,7 +377,9 @@ class PeerHandle:
 
         x = self.info.xchg
         if self.event is not None:
-            torch.cuda.current_stream().wait_event(self.event)
+            from ..ops import current_stream_object
+
+            current_stream_object().wait_event(self.event)
         _lib.check(x.lib.dice_ep_wait_flags(x.my_flags_ptr(self.info.slot, 1 + self.which), x.world, self.info.seq,
                                             self.which, x.status.data_ptr(), _stream()), "dice_ep_wait_flags")
 

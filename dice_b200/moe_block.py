@@ -468,11 +468,11 @@ class SparseMoeBlock(nn.Module):
             y = self.moe_infer(x, topk_idx.view(-1), topk_weight.view(-1, 1), _addend=shared_out, _chunks=chunks,
                                _glue=_glue)
         else:
-            from .expertpara.diep import ep_skip_enabled, ep_skip_mask, ep_skip_now
-            from .expertpara.ep_fwd import moe_infer_ep
+            from .expertpara import diep as _diep, ep_fwd as _ep_fwd
 
-            partial_skip = ep_skip_enabled()
-            y = moe_infer_ep(
+            ep_skip_mask, ep_skip_now = _diep.ep_skip_mask, _diep.ep_skip_now
+            partial_skip = _diep.ep_skip_enabled()
+            y = _ep_fwd.moe_infer_ep(
                 inp=x, experts=self.experts, flat_expert_indices=topk_idx.view(-1),
                 flat_expert_weights=topk_weight.view(-1, 1), num_experts_per_tok=self.num_experts_per_tok,
                 skip_mask=ep_skip_mask(topk_idx.numel()) if partial_skip else None,
@@ -481,7 +481,7 @@ class SparseMoeBlock(nn.Module):
         y = y.view(*orig_shape)
         return y if y.dtype == orig_dtype else y.to(orig_dtype)
 
-    @torch.no_grad()
+    @ops.no_grad
     def moe_infer(self, x, flat_expert_indices, flat_expert_weights, _addend=None, _chunks=None, _glue=None):
         """Single-device dispatch -> experts -> weighted combine
         (models.py:361-382), without a host sync: plan + row gather (one

@@ -50,6 +50,41 @@ def _stream() -> int:
     return torch.cuda.current_stream().cuda_stream
 
 
+_stream_objects = {}
+
+
+def current_stream_object() -> "torch.cuda.Stream":
+    """torch's current stream as a Stream object, looked up by its raw handle
+    (``torch.cuda.current_stream()`` itself costs several microseconds per call,
+    which adds up on the per-layer path of the asynchronous exchange)."""
+    if _raw_stream is None:
+        return torch.cuda.current_stream()
+    dev = torch.cuda.current_device()
+    key = (dev, _raw_stream(dev))
+    obj = _stream_objects.get(key)
+    if obj is None:
+        if len(_stream_objects) > 64:
+            _stream_objects.clear()
+        obj = _stream_objects[key] = torch.cuda.current_stream()
+    return obj
+
+
+def no_grad(fn):
+    """``@torch.no_grad()`` that costs nothing when gradients are already off
+    (the block's forward enters the no-grad region once; the functions below
+    it keep the reference's decorators without paying for them again)."""
+    import functools
+
+    @functools.wraps(fn)
+    def wrapper(*args, **kwargs):
+        if torch.is_grad_enabled():
+            with torch.no_grad():
+                return fn(*args, **kwargs)
+        return fn(*args, **kwargs)
+
+    return wrapper
+
+
 def check_status(status: torch.Tensor, what: str = "dice_b200 kernel") -> None:
     """Read a device status word (synchronises) and raise if a kernel's bounded
     wait expired."""
