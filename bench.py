@@ -312,10 +312,12 @@ def phase_times(step_fn, layers, steps=3):
 
 
 def ffn_flops(tokens, variant):
-    """Algorithmic FLOPs of one grouped-GEMM launch pair (routed experts only): 2 rows per token."""
+    """Algorithmic FLOPs of one grouped-GEMM launch pair: the routed experts (2 rows per token) and, in the
+    SwiGLU variant, the shared expert of width 2h that rides in the same launches (every token once)."""
     rows = 2 * tokens
     per_row = (6 if variant == "swiglu" else 4) * HIDDEN * MLP_RATIO * HIDDEN
-    return rows * per_row
+    shared = tokens * 6 * HIDDEN * 2 * HIDDEN if variant == "swiglu" else 0
+    return rows * per_row + shared
 
 
 def hbm_rooflines(blocks, xs, peak_gbs, reps=10):
@@ -591,7 +593,7 @@ def run_ours(args):
     ffn_events = ExpertPack.timing
     ExpertPack.timing = None
     torch.cuda.synchronize()
-    routed = [s.elapsed_time(e) for tag, s, e in ffn_events if tag == "routed"]
+    routed = [s.elapsed_time(e) for tag, s, e in ffn_events if tag.startswith("routed")]
     for blk in blocks:
         blk.check_status()
     exchange = "nccl"
@@ -631,7 +633,8 @@ def run_ours(args):
     gemm_ms = sum(routed) / max(gemm_launches, 1)
     flops_per_launch = ffn_flops(tokens, args.variant) / 2
     achieved = flops_per_launch / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else 0.0
-    roofline = {"kernel": "grouped_gemm_pair_kernel (tcgen05 cta_group::2, fc1+fc2 of the routed experts)", "bound": "tensor",
+    roofline = {"kernel": "grouped_gemm_pair_kernel (tcgen05 cta_group::2, fc1+fc2 of the routed experts"
+                          + (" and the shared expert" if args.variant == "swiglu" else "") + ")", "bound": "tensor",
                 "achieved": round(achieved, 1), "peak": peak_tf, "unit": "TFLOP/s", "frac": round(achieved / peak_tf, 4),
                 "peak_source": f"bf16_tflops_sustained of {pk_src}", "frac_of_burst": round(
                     achieved / pk.get("bf16_tflops", FALLBACK_PEAKS["bf16_tflops"]), 4), "avg_launch_ms": round(gemm_ms, 4),

@@ -102,7 +102,18 @@ struct DiceReturnSpec {
   uint32_t* done_counter;
   uint32_t seq;
 };
+// a dense problem (one segment, one weight slab) appended to the tile list of a grouped GEMM launch
+struct DiceDenseSpec {
+  const void* a;   // [n_rows, k_dim]
+  int64_t n_rows;
+  int k_dim;
+  const void* w;   // [w_rows, k_dim]
+  int64_t w_rows;
+  void* out;       // [n_rows, ld_out]
+  int64_t ld_out;
+  int n_out;
+};
 int dice_internal_gemm_pair(const void* a, int64_t n_rows, int k_dim, const void* w, int n_slabs, int64_t w_rows,
                             const int32_t* seg_offsets, const int32_t* seg_slab, int n_seg, int epilogue, void* out,
                             int64_t ld_out, int n_out, int reserve_sms, uint32_t* status, cudaStream_t stream,
-                            const DiceReturnSpec* ret = nullptr);
+                            const DiceReturnSpec* ret = nullptr, const DiceDenseSpec* extra = nullptr);

@@ -505,20 +505,51 @@ int dice_internal_router_tc(const void* x, const void* w_gate, int64_t n_tokens,
 
 extern "C" int dice_grouped_ffn(const void* rows_in, int64_t n_rows, int hidden, int ffn, int act, const void* w1,
                                 const void* w2, int n_slabs, const int32_t* seg_offsets, const int32_t* seg_slab,
-                                int n_seg, void* inter, void* rows_out, int reserve_sms, uint32_t* status, void* stream) {
+                                int n_seg, void* inter, void* rows_out, const void* shared_in, int64_t n_shared,
+                                int shared_ffn, const void* shared_w1, const void* shared_w2, void* shared_inter,
+                                void* shared_out, int reserve_sms, uint32_t* status, void* stream) {
   DICE_CHECK_ARG(act == DICE_ACT_SWIGLU || act == DICE_ACT_GELU_TANH, DICE_ERR_ARG);
-  DICE_CHECK_ARG(hidden > 0 && ffn > 0, DICE_ERR_ARG);
+  DICE_CHECK_ARG(hidden > 0 && ffn > 0 && reserve_sms >= 0, DICE_ERR_ARG);
   if (n_rows > 0 && n_seg > 0) DICE_CHECK_ARG(inter != nullptr, DICE_ERR_ARG);
-  int rc;
-  if (act == DICE_ACT_SWIGLU)
-    rc = dice_grouped_gemm(rows_in, n_rows, hidden, w1, n_slabs, dice_w13_rows(ffn), seg_offsets, seg_slab, n_seg,
-                           DICE_EPI_SWIGLU, inter, ffn, ffn, reserve_sms, status, stream);
-  else
-    rc = dice_grouped_gemm(rows_in, n_rows, hidden, w1, n_slabs, ffn, seg_offsets, seg_slab, n_seg, DICE_EPI_GELU_TANH,
-                           inter, ffn, ffn, reserve_sms, status, stream);
+  const int epi1 = act == DICE_ACT_SWIGLU ? DICE_EPI_SWIGLU : DICE_EPI_GELU_TANH;
+  const int64_t w1_rows = act == DICE_ACT_SWIGLU ? dice_w13_rows(ffn) : ffn;
+  if (shared_in == nullptr || n_shared == 0) {
+    int rc = dice_grouped_gemm(rows_in, n_rows, hidden, w1, n_slabs, w1_rows, seg_offsets, seg_slab, n_seg, epi1, inter,
+                               ffn, ffn, reserve_sms, status, stream);
+    if (rc != DICE_OK) return rc;
+    return dice_grouped_gemm(inter, n_rows, ffn, w2, n_slabs, hidden, seg_offsets, seg_slab, n_seg, DICE_EPI_STORE,
+                             rows_out, hidden, hidden, reserve_sms, status, stream);
+  }
+  // The always-on shared expert rides in the same two launches as one more problem of the tile list
+  // (models.py:355-357 runs it as three more linear layers after the routed experts).
+  DICE_CHECK_ARG(n_shared > 0 && shared_ffn > 0 && shared_w1 && shared_w2 && shared_inter && shared_out, DICE_ERR_ARG);
+  DICE_CHECK_ARG(use_cta_pairs(), DICE_ERR_ARG);  // the one-CTA-per-tile kernel has no second problem
+  DICE_CHECK_ARG(hidden % 8 == 0 && ffn % 8 == 0 && shared_ffn % 8 == 0, DICE_ERR_SHAPE);
+  DICE_CHECK_ARG(n_seg <= kMaxSeg && n_shared < 0x7fffff00LL && n_rows < 0x7fffff00LL, DICE_ERR_LIMIT);
+  DICE_CHECK_ARG(dice_aligned16(shared_in) && dice_aligned16(shared_w1) && dice_aligned16(shared_w2) &&
+                     dice_aligned16(shared_inter) && dice_aligned16(shared_out),
+                 DICE_ERR_ALIGN);
+  const int64_t sw1_rows = act == DICE_ACT_SWIGLU ? dice_w13_rows(shared_ffn) : shared_ffn;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (n_rows == 0 || n_seg == 0) {
+    // no routed rows on this rank: the shared expert alone, as one segment over all tokens
+    int rc = dice_internal_gemm_pair(shared_in, n_shared, hidden, shared_w1, 1, sw1_rows, nullptr, nullptr, 1, epi1,
+                                     shared_inter, shared_ffn, shared_ffn, reserve_sms, status, s);
+    if (rc != DICE_OK) return rc;
+    return dice_internal_gemm_pair(shared_inter, n_shared, shared_ffn, shared_w2, 1, hidden, nullptr, nullptr, 1,
+                                   DICE_EPI_STORE, shared_out, hidden, hidden, reserve_sms, status, s);
+  }
+  DICE_CHECK_ARG(rows_in && w1 && w2 && seg_offsets && rows_out, DICE_ERR_ARG);
+  DICE_CHECK_ARG(dice_aligned16(rows_in) && dice_aligned16(w1) && dice_aligned16(w2) && dice_aligned16(inter) &&
+                     dice_aligned16(rows_out),
+                 DICE_ERR_ALIGN);
+  DiceDenseSpec x1 = {shared_in, n_shared, hidden, shared_w1, sw1_rows, shared_inter, shared_ffn, shared_ffn};
+  int rc = dice_internal_gemm_pair(rows_in, n_rows, hidden, w1, n_slabs, w1_rows, seg_offsets, seg_slab, n_seg, epi1, inter,
+                                   ffn, ffn, reserve_sms, status, s, nullptr, &x1);
   if (rc != DICE_OK) return rc;
-  return dice_grouped_gemm(inter, n_rows, ffn, w2, n_slabs, hidden, seg_offsets, seg_slab, n_seg, DICE_EPI_STORE,
-                           rows_out, hidden, hidden, reserve_sms, status, stream);
+  DiceDenseSpec x2 = {shared_inter, n_shared, shared_ffn, shared_w2, hidden, shared_out, hidden, hidden};
+  return dice_internal_gemm_pair(inter, n_rows, ffn, w2, n_slabs, hidden, seg_offsets, seg_slab, n_seg, DICE_EPI_STORE,
+                                 rows_out, hidden, hidden, reserve_sms, status, s, nullptr, &x2);
 }
 
 // The expert FFN whose second GEMM writes its rows straight into the token owners' combine buffers

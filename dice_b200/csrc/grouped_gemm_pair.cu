@@ -92,7 +92,9 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
 // short enough to keep the tensor pipe fed (a single-lane loop under `lane == 0` was 15 % slower).
 __global__ void __launch_bounds__(kThreads, 1)
 grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
-                         const __grid_constant__ CUtensorMap tm_b_narrow, const GemmParams p) {
+                         const __grid_constant__ CUtensorMap tm_b_narrow, const __grid_constant__ CUtensorMap tm_xa,
+                         const __grid_constant__ CUtensorMap tm_xb, const __grid_constant__ CUtensorMap tm_xb_narrow,
+                         const GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* aux = smem + kPairStages * kPairStageBytes;
@@ -162,7 +164,32 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
   tc_fence_after_sync();
 
   const uint32_t tmem_base = *tmem_slot;
-  const int64_t total_tiles = static_cast<int64_t>(s_mprefix[p.n_seg]) * p.n_nblk;
+  // tile list: the segmented problem's tiles, then the tiles of the appended dense problem (if any)
+  const int64_t tiles0 = static_cast<int64_t>(s_mprefix[p.n_seg]) * p.n_nblk;
+  const int64_t total_tiles = tiles0 + static_cast<int64_t>((p.x_rows + PM - 1) / PM) * p.x_nblk;
+  // tile t -> problem (0 / 1), n-block, first row of this CTA's half and the rows that belong to the tile's segment
+  struct Tile { int g, nb, row0, rows_valid, slab; };
+  auto decode = [&](int64_t t, int& seg) {
+    Tile ti;
+    if (t < tiles0) {
+      const int mb = static_cast<int>(t / p.n_nblk);
+      ti.g = 0;
+      ti.nb = static_cast<int>(t - static_cast<int64_t>(mb) * p.n_nblk);
+      while (mb >= s_mprefix[seg + 1]) ++seg;
+      ti.row0 = s_seg_off[seg] + (mb - s_mprefix[seg]) * PM + static_cast<int>(cta_rank) * BM;
+      ti.rows_valid = s_seg_off[seg + 1] - ti.row0;  // <= 0 when this CTA's half lies past the segment
+      ti.slab = p.seg_slab != nullptr ? p.seg_slab[seg] : seg;
+    } else {
+      const int64_t t1 = t - tiles0;
+      const int mb = static_cast<int>(t1 / p.x_nblk);
+      ti.g = 1;
+      ti.nb = static_cast<int>(t1 - static_cast<int64_t>(mb) * p.x_nblk);
+      ti.row0 = mb * PM + static_cast<int>(cta_rank) * BM;
+      ti.rows_valid = p.x_rows - ti.row0;
+      ti.slab = 0;
+    }
+    return ti;
+  };
 
   if (warp == 0) {
     // ---------------- loader (both CTAs) ----------------
@@ -171,21 +198,21 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
       uint32_t phase = 0;
       bool alive = true;
       for (int64_t t = pair_id; alive && t < total_tiles; t += n_pairs) {
-        const int mb = static_cast<int>(t / p.n_nblk);
-        const int nb = static_cast<int>(t - static_cast<int64_t>(mb) * p.n_nblk);
-        while (mb >= s_mprefix[seg + 1]) ++seg;
-        const int row0 = s_seg_off[seg] + (mb - s_mprefix[seg]) * PM + static_cast<int>(cta_rank) * BM;
-        const int slab = p.seg_slab != nullptr ? p.seg_slab[seg] : seg;
-        int n_valid = p.w_rows - nb * BN;
+        const Tile ti = decode(t, seg);
+        const int w_rows = ti.g == 0 ? p.w_rows : p.x_w_rows;
+        const int n_kblk = ti.g == 0 ? p.n_kblk : p.x_kblk;
+        const CUtensorMap* map_a = ti.g == 0 ? &tm_a : &tm_xa;
+        const int row0 = ti.row0;
+        int n_valid = w_rows - ti.nb * BN;
         if (n_valid > BN) n_valid = BN;
         const int n_mma = (n_valid + 15) & ~15;
         // the MMA takes the first n_mma/2 weight rows of the tile from the leader and the rest from the peer
-        const int wrow0 = slab * p.w_rows + nb * BN + static_cast<int>(cta_rank) * (n_mma / 2);
+        const int wrow0 = ti.slab * w_rows + ti.nb * BN + static_cast<int>(cta_rank) * (n_mma / 2);
         // a tile of at most 128 weight rows needs 64 of them per CTA: the narrow box moves half the bytes
         const bool narrow = n_mma <= 128;
-        const CUtensorMap* map_b = narrow ? &tm_b_narrow : &tm_b;
+        const CUtensorMap* map_b = ti.g == 0 ? (narrow ? &tm_b_narrow : &tm_b) : (narrow ? &tm_xb_narrow : &tm_xb);
         const uint32_t pair_bytes = 2u * (kTileABytes + (narrow ? kPairTileBBytes / 2 : kPairTileBBytes));
-        for (int kb = 0; kb < p.n_kblk; ++kb) {
+        for (int kb = 0; kb < n_kblk; ++kb) {
           if (!mbar_wait(empty_bar + 8 * stage, phase ^ 1u, abort_flag, p.status, DICE_STATUS_WAIT_SMEM_EMPTY)) {
             alive = false;
             break;
@@ -194,7 +221,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
           const uint32_t leader_full = map_to_cta(full_bar + 8 * stage, 0);
           if (elect_one()) {
             if (leader) mbar_expect_tx(full_bar + 8 * stage, pair_bytes);
-            tma_load_2d_pair(a_dst, &tm_a, kb * BK, row0, leader_full);
+            tma_load_2d_pair(a_dst, map_a, kb * BK, row0, leader_full);
             tma_load_2d_pair(a_dst + kTileABytes, map_b, kb * BK, wrow0, leader_full);
           }
           __syncwarp();
@@ -209,14 +236,16 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
       uint32_t phase = 0, acc_phase = 0;
       bool alive = true;
       for (int64_t t = pair_id; alive && t < total_tiles; t += n_pairs) {
-        const int nb = static_cast<int>(t % p.n_nblk);
-        int n_valid = p.w_rows - nb * BN;
+        const bool first = t < tiles0;
+        const int nb = static_cast<int>(first ? t % p.n_nblk : (t - tiles0) % p.x_nblk);
+        const int n_kblk = first ? p.n_kblk : p.x_kblk;
+        int n_valid = (first ? p.w_rows : p.x_w_rows) - nb * BN;
         if (n_valid > BN) n_valid = BN;
         const uint32_t idesc = make_instr_desc(PM, (n_valid + 15) & ~15);
         if (!mbar_wait(acc_empty_bar + 8 * acc, acc_phase ^ 1u, abort_flag, p.status, DICE_STATUS_WAIT_ACC_EMPTY)) break;
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
-        for (int kb = 0; kb < p.n_kblk; ++kb) {
+        for (int kb = 0; kb < n_kblk; ++kb) {
           if (!mbar_wait(full_bar + 8 * stage, phase, abort_flag, p.status, DICE_STATUS_WAIT_SMEM_FULL)) {
             alive = false;
             break;
@@ -248,11 +277,11 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
     int acc = 0, seg = 0;
     uint32_t acc_phase = 0;
     for (int64_t t = pair_id; t < total_tiles; t += n_pairs) {
-      const int mb = static_cast<int>(t / p.n_nblk);
-      const int nb = static_cast<int>(t - static_cast<int64_t>(mb) * p.n_nblk);
-      while (mb >= s_mprefix[seg + 1]) ++seg;
-      const int row0 = s_seg_off[seg] + (mb - s_mprefix[seg]) * PM + static_cast<int>(cta_rank) * BM;
-      const int rows_valid = s_seg_off[seg + 1] - row0;  // <= 0 when this CTA's half lies past the segment
+      const Tile ti = decode(t, seg);
+      const int nb = ti.nb, row0 = ti.row0, rows_valid = ti.rows_valid;
+      __nv_bfloat16* const out = ti.g == 0 ? p.out : p.x_out;
+      const int64_t ld_out = ti.g == 0 ? p.ld_out : p.x_ld_out;
+      const int n_out = ti.g == 0 ? p.n_out : p.x_n_out;
       if (!mbar_wait(acc_full_bar + 8 * acc, acc_phase, abort_flag, p.status, DICE_STATUS_WAIT_ACC_FULL)) break;
       tc_fence_after_sync();
       const int r = quad * 32 + lane;
@@ -269,17 +298,17 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
         const int gr = row0 + rr;
         dst_rows[i] = nullptr;
         if (rr < rows_valid) {
-          if (p.ret_world > 0) {
+          if (p.ret_world > 0 && ti.g == 0) {
             // the row goes straight into the buffer of the rank whose token it is, over NVLink
             int src = 0;
             while (src + 1 < p.ret_world && gr >= s_ret_src[src + 1]) ++src;
             const int dst_row = s_ret_base[src] + (gr - s_ret_src[src]);
             if (dst_row < p.ret_capacity_rows)
-              dst_rows[i] = static_cast<__nv_bfloat16*>(p.ret_bufs[src]) + static_cast<int64_t>(dst_row) * p.ld_out;
+              dst_rows[i] = static_cast<__nv_bfloat16*>(p.ret_bufs[src]) + static_cast<int64_t>(dst_row) * ld_out;
             else if (p.status != nullptr)
               atomicCAS(p.status, 0u, DICE_STATUS_EXCHANGE_OVERFLOW);
           } else {
-            dst_rows[i] = p.out + static_cast<int64_t>(gr) * p.ld_out;
+            dst_rows[i] = out + static_cast<int64_t>(gr) * ld_out;
           }
         }
       }
@@ -303,7 +332,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
       };
       if (p.epilogue == DICE_EPI_SWIGLU) {
         const int col0 = nb * (BN / 2);
-        int n_valid = p.n_out - col0;
+        int n_valid = n_out - col0;
         if (n_valid > BN / 2) n_valid = BN / 2;
         for (int c = half * 32; c < n_valid; c += 64) {
           uint32_t g[32], u[32];
@@ -317,7 +346,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
         }
       } else {
         const int col0 = nb * BN;
-        int n_valid = p.n_out - col0;
+        int n_valid = n_out - col0;
         if (n_valid > BN) n_valid = BN;
         const bool gelu = p.epilogue == DICE_EPI_GELU_TANH;
         for (int c = half * 32; c < n_valid; c += 64) {
@@ -406,7 +435,7 @@ int resident_pairs() {
 int dice_internal_gemm_pair(const void* a, int64_t n_rows, int k_dim, const void* w, int n_slabs, int64_t w_rows,
                             const int32_t* seg_offsets, const int32_t* seg_slab, int n_seg, int epilogue, void* out,
                             int64_t ld_out, int n_out, int reserve_sms, uint32_t* status, cudaStream_t stream,
-                            const DiceReturnSpec* ret) {
+                            const DiceReturnSpec* ret, const DiceDenseSpec* extra) {
   int pairs = resident_pairs();
   if (pairs <= 0) return DICE_ERR_CUDA;
   // SM pairs left to kernels of other streams (the side-stream pushes of the asynchronous exchange)
@@ -421,7 +450,23 @@ int dice_internal_gemm_pair(const void* a, int64_t n_rows, int k_dim, const void
   rc = encode_map(&tm_b_narrow, w, static_cast<uint64_t>(n_slabs) * static_cast<uint64_t>(w_rows),
                   static_cast<uint64_t>(k_dim), 64);
   if (rc != DICE_OK) return rc;
+  CUtensorMap tm_xa = tm_a, tm_xb = tm_b, tm_xb_narrow = tm_b_narrow;
   GemmParams p = {};
+  if (extra != nullptr && extra->n_rows > 0) {
+    rc = encode_map(&tm_xa, extra->a, static_cast<uint64_t>(extra->n_rows), static_cast<uint64_t>(extra->k_dim), BM);
+    if (rc != DICE_OK) return rc;
+    rc = encode_map(&tm_xb, extra->w, static_cast<uint64_t>(extra->w_rows), static_cast<uint64_t>(extra->k_dim), 128);
+    if (rc != DICE_OK) return rc;
+    rc = encode_map(&tm_xb_narrow, extra->w, static_cast<uint64_t>(extra->w_rows), static_cast<uint64_t>(extra->k_dim), 64);
+    if (rc != DICE_OK) return rc;
+    p.x_rows = static_cast<int>(extra->n_rows);
+    p.x_kblk = (extra->k_dim + BK - 1) / BK;
+    p.x_nblk = static_cast<int>((extra->w_rows + BN - 1) / BN);
+    p.x_w_rows = static_cast<int>(extra->w_rows);
+    p.x_n_out = extra->n_out;
+    p.x_out = static_cast<__nv_bfloat16*>(extra->out);
+    p.x_ld_out = extra->ld_out;
+  }
   p.seg_offsets = seg_offsets;
   p.seg_slab = seg_slab;
   p.n_seg = n_seg;
@@ -451,7 +496,7 @@ int dice_internal_gemm_pair(const void* a, int64_t n_rows, int k_dim, const void
     }
   }
 
-  const int64_t max_tiles = ((n_rows + PM - 1) / PM + n_seg) * p.n_nblk;
+  const int64_t max_tiles = ((n_rows + PM - 1) / PM + n_seg) * p.n_nblk + static_cast<int64_t>((p.x_rows + PM - 1) / PM) * p.x_nblk;
   const int use_pairs = static_cast<int>(max_tiles < pairs ? max_tiles : pairs);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(2 * use_pairs), 1, 1);
@@ -468,6 +513,7 @@ int dice_internal_gemm_pair(const void* a, int64_t n_rows, int k_dim, const void
   cfg.attrs = attr;
   cfg.numAttrs = dice_pdl_enabled() ? 2 : 1;
   dice_count_launch();
-  if (cudaLaunchKernelEx(&cfg, grouped_gemm_pair_kernel, tm_a, tm_b, tm_b_narrow, p) != cudaSuccess) return DICE_ERR_CUDA;
+  if (cudaLaunchKernelEx(&cfg, grouped_gemm_pair_kernel, tm_a, tm_b, tm_b_narrow, tm_xa, tm_xb, tm_xb_narrow, p) != cudaSuccess)
+    return DICE_ERR_CUDA;
   return DICE_OK;
 }

@@ -50,6 +50,12 @@ struct GemmParams {
   int* hist;        // [n_experts] totals (may be null)
   int* chunk_hist;  // [tiles][n_experts] per-128-token histograms (may be null)
   __nv_bfloat16* logits_out;
+  // A second, dense problem (one segment, one weight slab) whose tiles follow the first problem's in the tile list
+  // of the same launch (CTA-pair kernel only; x_rows == 0: none).  It has its own operands (separate tensor maps)
+  // and its own reduction depth and output; the epilogue kind is the launch's.
+  int x_rows, x_kblk, x_nblk, x_w_rows, x_n_out;
+  __nv_bfloat16* x_out;
+  int64_t x_ld_out;
   // output rows leave the GPU (CTA-pair kernel only): row r of the receive order belongs to source rank s
   // with ret_src_off[s] <= r < ret_src_off[s+1] and is stored in that rank's buffer at row
   // ret_back_base[s] + r - ret_src_off[s]; ret_world == 0 means a plain local store to `out`

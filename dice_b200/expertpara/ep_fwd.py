@@ -36,6 +36,7 @@ from . import diep, p2p
 from .diep import ep_skip_get, ep_skip_put, global_combine_async, global_dispatch_async  # noqa: F401
 
 _use_latest_expert_weights = None
+_shared_job = None  # the shared-expert job of the moe_infer_ep call in progress (see proc_experts)
 
 
 def use_latest_expert_weights(val):
@@ -254,6 +255,11 @@ def proc_experts(inp, experts, token_counts_global, num_local_experts):
             if inp.dtype == torch.bfloat16 and p2p.fused_return():
                 pack.run_offsets_return(inp, token_counts_global)
                 return p2p.ReturnedRows(token_counts_global)
+            job = _shared_job
+            if job is not None and inp.dtype == torch.bfloat16:
+                outp, job.out = pack.run_offsets(inp, token_counts_global.seg_dev, token_counts_global.xchg.seg_slab_dev,
+                                                 reserve_sms=p2p.reserve_sms(), shared=(job.x, job.pack))
+                return outp
             return pack.run_offsets(inp, token_counts_global.seg_dev, token_counts_global.xchg.seg_slab_dev,
                                     reserve_sms=p2p.reserve_sms())
         world_size, rank = token_counts_global.xchg.world, token_counts_global.xchg.rank
@@ -329,7 +335,7 @@ def _pick(pairs: torch.Tensor, const_slot: Optional[int], per_tok: Optional[torc
 @no_grad
 def moe_infer_ep(inp: torch.Tensor, experts: nn.ModuleList, flat_expert_indices, flat_expert_weights,
                  num_experts_per_tok, async_op, skip_mask=None, skip_now=None, cache_key=None, _addend=None,
-                 _chunks=None, _glue=None):
+                 _chunks=None, _glue=None, _shared=None):
     """Expert-parallel replacement of ``SparseMoeBlock.moe_infer``
     (ep_fwd.py:19-197; same arguments and result).
 
@@ -342,7 +348,10 @@ def moe_infer_ep(inp: torch.Tensor, experts: nn.ModuleList, flat_expert_indices,
     ``_chunks`` (not in the reference) is the router's per-128-token histogram
     table, from which the plan is a single launch; ``_glue`` (not in the
     reference) is ``(residual [N, h], gate [B, h], tokens per sample)``: the
-    DiT block's gated residual, applied by the same combine kernel."""
+    DiT block's gated residual, applied by the same combine kernel;
+    ``_shared`` (not in the reference) is the block's shared-expert job, which
+    rides in this call's grouped-FFN launches and whose output is added in the
+    combine kernel."""
     live = p2p._exchange if p2p.enabled() else None  # knows this rank's place without asking c10d per layer
     world_size, rank = (live.world, live.rank) if live is not None else (dist.get_world_size(), dist.get_rank())
     num_total_experts = len(experts)
@@ -414,8 +423,13 @@ def moe_infer_ep(inp: torch.Tensor, experts: nn.ModuleList, flat_expert_indices,
                 grouped_dup_inp=grouped_dup_inp, token_counts_local=counts_local, token_counts_global=counts_global,
                 grouped_idx_dup=pos, flat_expert_weights=flat_expert_weights, experts=experts, cache_key=cache_key)
 
+    global _shared_job
+    _shared_job = _shared
     with _scope("moe.mlp"):
         mlp_outp = proc_experts(mlp_inp, experts_to_calc, counts_global, num_local_experts)
+    _shared_job = None
+    if _shared is not None:  # added by the combine kernel; computed on its own if no launch could carry it
+        _addend = _shared.out if _shared.out is not None else _shared.run_alone()
 
     with _scope("global_combine"):
         if not async_op:

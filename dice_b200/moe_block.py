@@ -259,17 +259,25 @@ class ExpertPack:
         return built
 
     def run_offsets(self, rows: torch.Tensor, seg_offsets: torch.Tensor, seg_slab: Optional[torch.Tensor] = None,
-                    reserve_sms: int = 0):
+                    reserve_sms: int = 0, shared=None):
+        """The grouped FFN over ``rows``.  ``shared = (tokens, pack of the shared expert)`` lets the shared expert
+        ride in the same launches (bf16); the result is then ``(rows_out, shared_out)``."""
         act, ffn, w1, w2 = self.get(rows.dtype)
+        extra = None
+        if shared is not None:
+            sx, spack = shared
+            s_act, s_ffn, sw1, sw2 = spack.get(rows.dtype)
+            assert s_act == act
+            extra = (sx, sw1, sw2, s_ffn)
         if not ExpertPack._want_timing():
             return ops.grouped_ffn(rows, w1, w2, seg_offsets, act, ffn, status=self.status, seg_slab=seg_slab,
-                                   reserve_sms=reserve_sms)
+                                   reserve_sms=reserve_sms, shared=extra)
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         start.record()
         out = ops.grouped_ffn(rows, w1, w2, seg_offsets, act, ffn, status=self.status, seg_slab=seg_slab,
-                              reserve_sms=reserve_sms)
+                              reserve_sms=reserve_sms, shared=extra)
         end.record()
-        ExpertPack.timing.append((self.tag, start, end))
+        ExpertPack.timing.append((self.tag if shared is None else self.tag + "+shared", start, end))
         return out
 
     def run_offsets_return(self, rows: torch.Tensor, info):
@@ -315,6 +323,30 @@ class ExpertPack:
     def check(self):
         if self.status is not None:
             ops.check_status(self.status, "grouped expert FFN")
+
+
+_fold_cached = None
+
+
+def _fold_shared() -> bool:
+    global _fold_cached
+    if _fold_cached is None:
+        _fold_cached = ops.shared_expert_can_ride()
+    return _fold_cached
+
+
+class SharedJob:
+    """The shared expert's work of one block call, waiting for a grouped-FFN launch to ride in: the tokens, the
+    shared expert's pack and what is needed to run it on its own if no suitable launch comes by."""
+
+    def __init__(self, x, pack, seg_all, reserve_sms):
+        self.x, self.pack, self.seg_all, self.reserve_sms = x, pack, seg_all, reserve_sms
+        self.out = None
+
+    def run_alone(self):
+        with _scope("moe.mlp_shared"):
+            self.out = self.pack.run_offsets(self.x, self.seg_all, reserve_sms=self.reserve_sms)
+        return self.out
 
 
 class SparseMoeBlock(nn.Module):
@@ -460,13 +492,18 @@ class SparseMoeBlock(nn.Module):
             topk_idx, topk_weight, hist, _ = ops.router_top2(x, self._gate_weight(cd), renorm=self.gate.norm_topk_prob,
                                                              status=self._router_status(x.device), want_chunks=chunked)
         chunks = hist if chunked else None
-        shared_out = None
+        # The always-on shared expert (models.py:355-357).  In bf16 it rides in the routed experts' two launches as
+        # one more problem of their tile list; otherwise it is a launch pair of its own, added inside the combine.
+        shared_out = shared_job = None
         if self._shared_pack is not None:
-            with _scope("moe.mlp_shared"):
-                shared_out = self._shared_pack.run_offsets(x, self._segment_all(n_tokens, x.device), reserve_sms=reserve)
+            if cd == torch.bfloat16 and _fold_shared():
+                shared_job = SharedJob(x, self._shared_pack, self._segment_all(n_tokens, x.device), reserve)
+            else:
+                with _scope("moe.mlp_shared"):
+                    shared_out = self._shared_pack.run_offsets(x, self._segment_all(n_tokens, x.device), reserve_sms=reserve)
         if not self.para_mode.ep:
             y = self.moe_infer(x, topk_idx.view(-1), topk_weight.view(-1, 1), _addend=shared_out, _chunks=chunks,
-                               _glue=_glue)
+                               _glue=_glue, _shared=shared_job)
         else:
             from .expertpara import diep as _diep, ep_fwd as _ep_fwd
 
@@ -477,12 +514,14 @@ class SparseMoeBlock(nn.Module):
                 flat_expert_weights=topk_weight.view(-1, 1), num_experts_per_tok=self.num_experts_per_tok,
                 skip_mask=ep_skip_mask(topk_idx.numel()) if partial_skip else None,
                 skip_now=ep_skip_now(self.layer_idx) if partial_skip else None,
-                async_op=self._async_layer(), cache_key=self.layer_idx, _addend=shared_out, _chunks=chunks, _glue=_glue)
+                async_op=self._async_layer(), cache_key=self.layer_idx, _addend=shared_out, _chunks=chunks, _glue=_glue,
+                _shared=shared_job)
         y = y.view(*orig_shape)
         return y if y.dtype == orig_dtype else y.to(orig_dtype)
 
     @ops.no_grad
-    def moe_infer(self, x, flat_expert_indices, flat_expert_weights, _addend=None, _chunks=None, _glue=None):
+    def moe_infer(self, x, flat_expert_indices, flat_expert_weights, _addend=None, _chunks=None, _glue=None,
+                  _shared=None):
         """Single-device dispatch -> experts -> weighted combine
         (models.py:361-382), without a host sync: plan + row gather (one
         launch when the router filed per-chunk histograms, else four), two
@@ -496,7 +535,10 @@ class SparseMoeBlock(nn.Module):
             pos, seg, _ = ops.permute_plan(flat_expert_indices, self.num_experts)
             rows = ops.permute_rows(x, pos, k)
         with _scope("moe.mlp"):
-            y_rows = self.experts._dice_pack.run_offsets(rows, seg)
+            if _shared is not None:
+                y_rows, _addend = self.experts._dice_pack.run_offsets(rows, seg, shared=(_shared.x, _shared.pack))
+            else:
+                y_rows = self.experts._dice_pack.run_offsets(rows, seg)
         w = flat_expert_weights.view(n_tokens, k)
         w = w if w.dtype == torch.float32 else w.float()
         pp = pos.view(n_tokens, k)

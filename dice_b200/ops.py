@@ -440,13 +440,18 @@ def grouped_ffn(
     inter: Optional[torch.Tensor] = None,
     out: Optional[torch.Tensor] = None,
     reserve_sms: int = 0,
-) -> torch.Tensor:
+    shared=None,
+):
     """Expert FFN over expert-sorted rows (ep_fwd.py:199-211; models.py:368-376).
 
     ``w1``: packed gate/up ``[S, w13_rows(F), h]`` (swiglu) or fc1 ``[S, F, h]``
     (gelu_tanh); ``w2``: ``[S, h, F]``.  bf16 runs on the tensor cores, fp32 on
     the CUDA cores.  ``reserve_sms`` SMs are left to kernels of other streams
-    (the side-stream pushes of the asynchronous exchange)."""
+    (the side-stream pushes of the asynchronous exchange).
+
+    ``shared = (tokens [N, h], w1 [1, ..., h], w2 [1, h, Fs], Fs)`` (bf16 only)
+    runs the block's shared expert over all tokens inside the same two
+    launches; the result is then ``(rows_out, shared_out)``."""
     _require_cuda(rows, w1, w2, seg_offsets, status, seg_slab, inter, out)
     assert rows.is_contiguous() and w1.is_contiguous() and w2.is_contiguous()
     assert seg_offsets.dtype == torch.int32
@@ -462,14 +467,27 @@ def grouped_ffn(
     lib = _lib.load()
     if rows.dtype == torch.bfloat16:
         assert status is not None and status.dtype == torch.int32
+        sx = sw1 = sw2 = s_inter = s_out = None
+        n_shared = s_ffn = 0
+        if shared is not None:
+            sx, sw1, sw2, s_ffn = shared
+            _require_cuda(sx, sw1, sw2)
+            assert sx.is_contiguous() and sx.dtype == rows.dtype and sx.shape[1] == h
+            assert sw1.is_contiguous() and sw2.is_contiguous() and sw2.shape == (1, h, s_ffn) and sw1.shape[0] == 1
+            n_shared = sx.shape[0]
+            s_inter = torch.empty((max(n_shared, 1), s_ffn), dtype=rows.dtype, device=rows.device)
+            s_out = torch.empty((n_shared, h), dtype=rows.dtype, device=rows.device)
         _lib.check(
             lib.dice_grouped_ffn(
                 _ptr(rows), n_rows, h, ffn, ACT_CODES[act], _ptr(w1), _ptr(w2), n_slabs, _ptr(seg_offsets),
-                _ptr(seg_slab), n_seg, _ptr(inter), _ptr(out), reserve_sms, _ptr(status), _stream(),
+                _ptr(seg_slab), n_seg, _ptr(inter), _ptr(out), _ptr(sx), n_shared, s_ffn, _ptr(sw1), _ptr(sw2),
+                _ptr(s_inter), _ptr(s_out), reserve_sms, _ptr(status), _stream(),
             ),
             "dice_grouped_ffn",
         )
-    elif rows.dtype == torch.float32:
+        return (out, s_out) if shared is not None else out
+    assert shared is None, "the shared expert rides along in the bf16 kernel only"
+    if rows.dtype == torch.float32:
         _lib.check(
             lib.dice_grouped_ffn_f32(
                 _ptr(rows), n_rows, h, ffn, ACT_CODES[act], _ptr(w1), _ptr(w2), n_slabs, _ptr(seg_offsets),
@@ -480,3 +498,12 @@ def grouped_ffn(
     else:
         raise TypeError(f"unsupported dtype {rows.dtype}")
     return out
+
+
+def shared_expert_can_ride() -> bool:
+    """Whether the grouped-FFN launches can carry the shared expert as an extra
+    problem (the CTA-pair kernel can; ``DICE_GEMM_PAIR=0`` selects the
+    one-CTA-per-tile kernel, which cannot)."""
+    import os
+
+    return os.environ.get("DICE_GEMM_PAIR", "1") != "0"

@@ -251,11 +251,19 @@ DICE_API int dice_grouped_gemm(const void* a, int64_t n_rows, int k_dim, const v
  *   act = DICE_ACT_SWIGLU   : w1 = packed gate/up [n_slabs, dice_w13_rows(ffn), hidden]
  *   act = DICE_ACT_GELU_TANH: w1 = fc1 [n_slabs, ffn, hidden]
  *   w2  [n_slabs, hidden, ffn];  inter = caller's scratch [n_rows, ffn] bf16.
+ * The block's always-on shared expert (models.py:292-296, :355-357: one more
+ * expert of width shared_ffn applied to EVERY token) can ride in the same two
+ * launches as an extra problem at the end of the tile list, where its tiles
+ * fill the routed experts' partly empty last wave:
+ *   shared_in  [n_shared, hidden] the tokens (NULL: no shared expert),
+ *   shared_w1 / shared_w2 as w1 / w2 for one slab of width shared_ffn,
+ *   shared_inter [n_shared, shared_ffn] scratch, shared_out [n_shared, hidden].
  */
 DICE_API int dice_grouped_ffn(const void* rows_in, int64_t n_rows, int hidden, int ffn, int act, const void* w1,
                      const void* w2, int n_slabs, const int32_t* seg_offsets, const int32_t* seg_slab,
-                     int n_seg, void* inter, void* rows_out, int reserve_sms, uint32_t* status,
-                     void* stream);
+                     int n_seg, void* inter, void* rows_out, const void* shared_in, int64_t n_shared,
+                     int shared_ffn, const void* shared_w1, const void* shared_w2, void* shared_inter,
+                     void* shared_out, int reserve_sms, uint32_t* status, void* stream);
 
 /* fp32 variant of the expert FFN on the CUDA cores (no tensor-core rounding;
  * used where fp32 parity at 1e-5 is asked for).  Same arguments as

@@ -106,6 +106,32 @@ def test_grouped_ffn_many_small_segments(cuda_device):
     _check_ffn(cuda_device, 1408, 5632, "swiglu", 16, counts, [i for _ in range(8) for i in range(16)])
 
 
+@pytest.mark.parametrize("act", ["swiglu", "gelu_tanh"])
+@pytest.mark.parametrize("counts,n_tok,h,f", [([130, 126, 257, 0, 3, 64, 64, 380], 512, 1152, 4608), ([0, 0, 0, 0], 300, 128, 512),
+                                             ([5, 300], 1, 256, 1024), ([77] * 16, 2048, 1408, 5632)])
+def test_shared_expert_rides_in_the_routed_launches(cuda_device, act, counts, n_tok, h, f):
+    """The shared expert (models.py:355-357: width 2h, every token) as an extra problem at the end of the routed
+    experts' tile list: both outputs equal the two separate launch pairs bit for bit, and the oracle within 2e-2."""
+    ops = _ops()
+    gen = torch.Generator(device=cuda_device).manual_seed(h + n_tok)
+    w1, w2, experts = _make_experts(len(counts), h, f, act, gen, cuda_device)
+    sw1, sw2, shared = _make_experts(1, h, 2 * h, act, gen, cuda_device)
+    r = sum(counts)
+    rows = torch.randn(max(r, 1), h, generator=gen, device=cuda_device).bfloat16()[:r]
+    x = torch.randn(n_tok, h, generator=gen, device=cuda_device).bfloat16()
+    seg = _segments(counts, cuda_device)
+    seg_all = _segments([n_tok], cuda_device)
+    status = torch.zeros(1, dtype=torch.int32, device=cuda_device)
+    want_rows = ops.grouped_ffn(rows, w1, w2, seg, act, f, status)
+    want_shared = ops.grouped_ffn(x, sw1, sw2, seg_all, act, 2 * h, status)
+    got_rows, got_shared = ops.grouped_ffn(rows, w1, w2, seg, act, f, status, shared=(x, sw1, sw2, 2 * h))
+    torch.cuda.synchronize()
+    ops.check_status(status)
+    assert torch.equal(got_rows, want_rows) and torch.equal(got_shared, want_shared)
+    want = O.run_expert(x.cpu().float(), [t.float() for t in shared[0]], act)
+    assert _rel(got_shared.cpu().float(), want) < 2e-2
+
+
 def _near_tie_only(idx, idx_o, logits_o):
     """Every token whose selection differs from the oracle's must owe that to logits one bf16 ulp apart."""
     lo = logits_o.float()
