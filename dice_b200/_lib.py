@@ -56,6 +56,11 @@ SIGNATURES = {
         [c_void_p, c_int64, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p,
          c_void_p, c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p],
     ),
+    "dice_grouped_ffn_combine": (
+        c_int,
+        [c_void_p, c_int64, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p,
+         c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p],
+    ),
     "dice_grouped_ffn_f32": (
         c_int,
         [c_void_p, c_int64, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p,

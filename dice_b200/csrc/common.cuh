@@ -113,7 +113,13 @@ struct DiceDenseSpec {
   int64_t ld_out;
   int n_out;
 };
+// the weighted scatter-add of a grouped GEMM's rows into token rows (see dice_grouped_ffn_combine)
+struct DiceCombineSpec {
+  const int32_t* order;   // sorted position -> flat (token, slot) row
+  const float* weights;   // gate weight of every flat row
+};
 int dice_internal_gemm_pair(const void* a, int64_t n_rows, int k_dim, const void* w, int n_slabs, int64_t w_rows,
                             const int32_t* seg_offsets, const int32_t* seg_slab, int n_seg, int epilogue, void* out,
                             int64_t ld_out, int n_out, int reserve_sms, uint32_t* status, cudaStream_t stream,
-                            const DiceReturnSpec* ret = nullptr, const DiceDenseSpec* extra = nullptr);
+                            const DiceReturnSpec* ret = nullptr, const DiceDenseSpec* extra = nullptr,
+                            const DiceCombineSpec* combine = nullptr);

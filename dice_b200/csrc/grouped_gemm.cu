@@ -552,6 +552,37 @@ extern "C" int dice_grouped_ffn(const void* rows_in, int64_t n_rows, int hidden,
                                  rows_out, hidden, hidden, reserve_sms, status, s, nullptr, &x2);
 }
 
+// The expert FFN whose second GEMM scales every row by its gate weight and adds it to its token's row
+// (models.py:377-381) with 16-byte bf16 reductions: no sorted output, no combine kernel.
+extern "C" int dice_grouped_ffn_combine(const void* rows_in, int64_t n_rows, int hidden, int ffn, int act,
+                                        const void* w1, const void* w2, int n_slabs, const int32_t* seg_offsets,
+                                        const int32_t* seg_slab, int n_seg, void* inter, const int32_t* order,
+                                        const float* row_weights, int k, void* out_tokens, int reserve_sms,
+                                        uint32_t* status, void* stream) {
+  DICE_CHECK_ARG(act == DICE_ACT_SWIGLU || act == DICE_ACT_GELU_TANH, DICE_ERR_ARG);
+  DICE_CHECK_ARG(n_rows >= 0 && hidden > 0 && ffn > 0 && n_slabs > 0 && n_seg >= 0 && reserve_sms >= 0, DICE_ERR_ARG);
+  DICE_CHECK_ARG(k == 2 && n_rows % 2 == 0, DICE_ERR_SHAPE);  // two addends per token: the sum is order-independent
+  DICE_CHECK_ARG(hidden % 8 == 0 && ffn % 8 == 0, DICE_ERR_SHAPE);
+  DICE_CHECK_ARG(n_seg <= kMaxSeg && n_rows < 0x7fffff00LL, DICE_ERR_LIMIT);
+  DICE_CHECK_ARG(use_cta_pairs(), DICE_ERR_ARG);
+  if (n_rows == 0) return DICE_OK;
+  DICE_CHECK_ARG(rows_in && w1 && w2 && seg_offsets && inter && order && row_weights && out_tokens, DICE_ERR_ARG);
+  DICE_CHECK_ARG(dice_aligned16(rows_in) && dice_aligned16(w1) && dice_aligned16(w2) && dice_aligned16(inter) &&
+                     dice_aligned16(out_tokens),
+                 DICE_ERR_ALIGN);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int epi1 = act == DICE_ACT_SWIGLU ? DICE_EPI_SWIGLU : DICE_EPI_GELU_TANH;
+  const int64_t w1_rows = act == DICE_ACT_SWIGLU ? dice_w13_rows(ffn) : ffn;
+  DICE_CUDA_OK(cudaMemsetAsync(out_tokens, 0, static_cast<size_t>(n_rows / 2) * hidden * 2, s));
+  int rc = dice_grouped_gemm(rows_in, n_rows, hidden, w1, n_slabs, w1_rows, seg_offsets, seg_slab, n_seg, epi1, inter, ffn,
+                             ffn, reserve_sms, status, stream);
+  if (rc != DICE_OK) return rc;
+  if (n_seg == 0) return DICE_OK;
+  DiceCombineSpec c = {order, row_weights};
+  return dice_internal_gemm_pair(inter, n_rows, ffn, w2, n_slabs, hidden, seg_offsets, seg_slab, n_seg, DICE_EPI_STORE,
+                                 out_tokens, hidden, hidden, reserve_sms, status, s, nullptr, nullptr, &c);
+}
+
 // The expert FFN whose second GEMM writes its rows straight into the token owners' combine buffers
 // (peer memory) and raises their flags when the whole grid is done: FFN + return of the exchange in
 // one launch pair.  `out` rows are not stored locally.

@@ -87,6 +87,13 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
                : "memory");
 }
 
+// 16 bytes of bf16 added to global memory (no return value): the combine epilogue's store
+__device__ __forceinline__ void red_add_bf16x8(void* dst, const uint4& v) {
+  asm volatile("red.relaxed.gpu.global.add.noftz.v4.bf16x2 [%0], {%1, %2, %3, %4};" ::"l"(dst), "r"(v.x), "r"(v.y),
+               "r"(v.z), "r"(v.w)
+               : "memory");
+}
+
 // The loader and the tensor-core warp run their loops with all 32 lanes (the waits are warp-wide) and elect one
 // lane for the TMA / MMA instructions: loop state stays warp-uniform for the compiler, and the issue loop is
 // short enough to keep the tensor pipe fed (a single-lane loop under `lane == 0` was 15 % slower).
@@ -290,7 +297,6 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
       // Stores go through a small per-warp transpose in shared memory: a lane holds 32 columns of ONE row,
       // but a store instruction should cover whole 64-byte row pieces.  After the transpose lane l writes
       // piece (l & 3) of rows (l >> 2) + 8 i, i < 4, whose destinations are resolved once per tile.
-      (void)row_ok;
       __nv_bfloat16* dst_rows[4];
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
@@ -298,7 +304,10 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
         const int gr = row0 + rr;
         dst_rows[i] = nullptr;
         if (rr < rows_valid) {
-          if (p.ret_world > 0 && ti.g == 0) {
+          if (p.epilogue == kEpiCombine) {
+            // the row is added to the row of the token it belongs to (two rows per token)
+            dst_rows[i] = out + static_cast<int64_t>(p.cmb_order[gr] >> 1) * ld_out;
+          } else if (p.ret_world > 0 && ti.g == 0) {
             // the row goes straight into the buffer of the rank whose token it is, over NVLink
             int src = 0;
             while (src + 1 < p.ret_world && gr >= s_ret_src[src + 1]) ++src;
@@ -312,6 +321,10 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
           }
         }
       }
+      // combine epilogue: this lane's own row is scaled by its gate weight before the transpose
+      const bool combine = p.epilogue == kEpiCombine;
+      float row_weight = 1.f;
+      if (combine && row_ok) row_weight = p.cmb_weights[p.cmb_order[row0 + r]];
       uint4* stage = reinterpret_cast<uint4*>(aux + kAuxBytes + (warp - 2) * kStoreStageBytes);
       auto staged_store = [&](const float (&v)[32], int col, int n_left) {
         const int swz = (lane >> 1) & 3;
@@ -326,7 +339,10 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
         for (int i = 0; i < 4; ++i) {
           const int rr = i * 8 + (lane >> 2);
           const uint4 val = stage[rr * 4 + (piece ^ ((rr >> 1) & 3))];
-          if (dst_rows[i] != nullptr && piece * 8 < n_left) *reinterpret_cast<uint4*>(dst_rows[i] + col + piece * 8) = val;
+          if (dst_rows[i] != nullptr && piece * 8 < n_left) {
+            if (combine) red_add_bf16x8(dst_rows[i] + col + piece * 8, val);
+            else *reinterpret_cast<uint4*>(dst_rows[i] + col + piece * 8) = val;
+          }
         }
         __syncwarp();
       };
@@ -357,7 +373,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
             const float f = __uint_as_float(a[j]);
-            v[j] = gelu ? gelu_tanh_f(f) : f;
+            v[j] = gelu ? gelu_tanh_f(f) : f * row_weight;
           }
           staged_store(v, col0 + c, n_valid - c);
         }
@@ -435,7 +451,7 @@ int resident_pairs() {
 int dice_internal_gemm_pair(const void* a, int64_t n_rows, int k_dim, const void* w, int n_slabs, int64_t w_rows,
                             const int32_t* seg_offsets, const int32_t* seg_slab, int n_seg, int epilogue, void* out,
                             int64_t ld_out, int n_out, int reserve_sms, uint32_t* status, cudaStream_t stream,
-                            const DiceReturnSpec* ret, const DiceDenseSpec* extra) {
+                            const DiceReturnSpec* ret, const DiceDenseSpec* extra, const DiceCombineSpec* combine) {
   int pairs = resident_pairs();
   if (pairs <= 0) return DICE_ERR_CUDA;
   // SM pairs left to kernels of other streams (the side-stream pushes of the asynchronous exchange)
@@ -481,6 +497,13 @@ int dice_internal_gemm_pair(const void* a, int64_t n_rows, int k_dim, const void
   p.status = status;
   p.b_box_rows = 128;
   p.n_stages = kPairStages;
+  if (combine != nullptr) {
+    if (epilogue != DICE_EPI_STORE || ret != nullptr || extra != nullptr || !combine->order || !combine->weights)
+      return DICE_ERR_ARG;
+    p.epilogue = kEpiCombine;
+    p.cmb_order = combine->order;
+    p.cmb_weights = combine->weights;
+  }
   if (ret != nullptr) {
     if (ret->world < 1 || ret->world > kMaxPeerRanks || epilogue != DICE_EPI_STORE) return DICE_ERR_ARG;
     p.ret_world = ret->world;

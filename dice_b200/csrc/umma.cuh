@@ -56,6 +56,9 @@ struct GemmParams {
   int x_rows, x_kblk, x_nblk, x_w_rows, x_n_out;
   __nv_bfloat16* x_out;
   int64_t x_ld_out;
+  // combine epilogue (CTA-pair kernel only): sorted position -> flat (token, slot) row, and the flat rows' gate weights
+  const int* cmb_order;
+  const float* cmb_weights;
   // output rows leave the GPU (CTA-pair kernel only): row r of the receive order belongs to source rank s
   // with ret_src_off[s] <= r < ret_src_off[s+1] and is stored in that rank's buffer at row
   // ret_back_base[s] + r - ret_src_off[s]; ret_world == 0 means a plain local store to `out`
@@ -69,7 +72,8 @@ struct GemmParams {
   uint32_t ret_seq;
 };
 
-constexpr int kEpiRouter = 100;  // internal epilogue: logits -> top-2 (see launch_router_tc)
+constexpr int kEpiRouter = 100;   // internal epilogue: logits -> top-2 (see launch_router_tc)
+constexpr int kEpiCombine = 101;  // internal epilogue (CTA-pair kernel): out[token(r)] += weight(r) * row r
 
 // ---- PTX wrappers ---------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }

@@ -280,6 +280,19 @@ class ExpertPack:
         ExpertPack.timing.append((self.tag if shared is None else self.tag + "+shared", start, end))
         return out
 
+    def run_offsets_combine(self, rows: torch.Tensor, seg_offsets: torch.Tensor, order: torch.Tensor, flat_weights):
+        """The grouped FFN with the gate-weighted combine in the second GEMM's epilogue: returns token rows."""
+        act, ffn, w1, w2 = self.get(rows.dtype)
+        timing = ExpertPack.timing if ExpertPack._want_timing() else None
+        if timing is not None:
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+        out = ops.grouped_ffn_combine(rows, w1, w2, seg_offsets, act, ffn, order, flat_weights, self.status)
+        if timing is not None:
+            end.record()
+            timing.append((self.tag + "+combine", start, end))
+        return out
+
     def run_offsets_return(self, rows: torch.Tensor, info):
         """FFN over the receive buffer of a peer-memory exchange with the
         return fused into the second GEMM (bf16 only): the outputs land in the
@@ -529,6 +542,16 @@ class SparseMoeBlock(nn.Module):
         assert not self.para_mode.ep
         n_tokens = x.shape[0]
         k = self.num_experts_per_tok
+        if (_chunks is not None and _addend is None and _shared is None and _glue is None and k == 2 and n_tokens > 0
+                and _fold_shared()):
+            # nothing but the two expert rows goes into a token's output: the second GEMM adds them itself
+            # (models.py:377-381 inside its epilogue), three launches and a memset for the whole dispatch -> combine
+            pos, seg, order, rows = ops.permute_plan_chunked(flat_expert_indices, _chunks, self.num_experts, 1, x, k,
+                                                             want_order=True)
+            w_flat = flat_expert_weights.reshape(-1)
+            w_flat = w_flat if w_flat.dtype == torch.float32 else w_flat.float()
+            with _scope("moe.mlp"):
+                return self.experts._dice_pack.run_offsets_combine(rows, seg, order, w_flat.contiguous())
         if _chunks is not None:
             pos, seg, _, rows = ops.permute_plan_chunked(flat_expert_indices, _chunks, self.num_experts, 1, x, k)
         else:

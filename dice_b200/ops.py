@@ -500,6 +500,33 @@ def grouped_ffn(
     return out
 
 
+def grouped_ffn_combine(rows: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor, seg_offsets: torch.Tensor, act: str,
+                        ffn: int, order: torch.Tensor, flat_weights: torch.Tensor, status: torch.Tensor,
+                        reserve_sms: int = 0) -> torch.Tensor:
+    """Expert FFN over expert-sorted rows with the gate-weighted combine
+    (models.py:377-381) inside the second GEMM's epilogue: returns ``[N, h]``
+    token rows, ``out[t] = sum_s w[t, s] * ffn(row(t, s))``.  bf16, two rows
+    per token; ``order`` is the plan's sorted-position -> flat-row map,
+    ``flat_weights`` the fp32 top-2 weights viewed flat."""
+    _require_cuda(rows, w1, w2, seg_offsets, order, flat_weights, status)
+    assert rows.dtype == torch.bfloat16 and rows.is_contiguous() and w1.is_contiguous() and w2.is_contiguous()
+    n_rows, h = rows.shape
+    assert n_rows % 2 == 0 and order.dtype == torch.int32 and order.numel() == n_rows
+    assert flat_weights.dtype == torch.float32 and flat_weights.is_contiguous() and flat_weights.numel() == n_rows
+    n_slabs = w1.shape[0]
+    inter = torch.empty((max(n_rows, 1), ffn), dtype=rows.dtype, device=rows.device)
+    out = torch.empty((n_rows // 2, h), dtype=rows.dtype, device=rows.device)
+    _lib.check(
+        _lib.load().dice_grouped_ffn_combine(
+            _ptr(rows), n_rows, h, ffn, ACT_CODES[act], _ptr(w1), _ptr(w2), n_slabs, _ptr(seg_offsets), None,
+            seg_offsets.numel() - 1, _ptr(inter), _ptr(order), _ptr(flat_weights), 2, _ptr(out), reserve_sms, _ptr(status),
+            _stream(),
+        ),
+        "dice_grouped_ffn_combine",
+    )
+    return out
+
+
 def shared_expert_can_ride() -> bool:
     """Whether the grouped-FFN launches can carry the shared expert as an extra
     problem (the CTA-pair kernel can; ``DICE_GEMM_PAIR=0`` selects the

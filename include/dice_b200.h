@@ -52,6 +52,8 @@ extern "C" {
 #define DICE_EPI_GELU_TANH 1 /* out = gelu_tanh(A * W^T)                        */
 #define DICE_EPI_SWIGLU 2    /* W holds 128-row gate/up blocks interleaved;
                                 out[:, j] = silu(gate_j) * up_j                 */
+/* (a fourth epilogue, the gate-weighted scatter-add into token rows, is reached
+ *  through dice_grouped_ffn_combine only) */
 
 /* error codes (negative) */
 #define DICE_OK 0
@@ -163,6 +165,8 @@ DICE_API int dice_permute_plan_chunked(const int64_t* flat_idx, const int32_t* c
  *   every cell that is read is rewritten first by the same call, so nothing
  *   needs clearing, but two calls that overlap on the GPU (different streams,
  *   or host threads without ordering between them) race on it: serialise them.
+ *   The address is remembered per device for the life of the process: do not
+ *   use the entry point across a cudaDeviceReset.
  * Outputs are identical to dice_permute_plan's. */
 #define DICE_PLAN_STATIC_MAX_INTS 65536
 DICE_API int dice_permute_plan_static(const int64_t* flat_idx, int64_t n_rows, int n_experts,
@@ -264,6 +268,28 @@ DICE_API int dice_grouped_ffn(const void* rows_in, int64_t n_rows, int hidden, i
                      int n_seg, void* inter, void* rows_out, const void* shared_in, int64_t n_shared,
                      int shared_ffn, const void* shared_w1, const void* shared_w2, void* shared_inter,
                      void* shared_out, int reserve_sms, uint32_t* status, void* stream);
+
+/* The expert FFN whose second GEMM also does the weighted combine
+ * (models.py:377-381: mul_ by the gate weights, scatter_reduce_ into the token
+ * rows): every output row is scaled by its gate weight in the epilogue and
+ * added to its token's row of out_tokens with 16-byte bf16 reductions, so the
+ * expert outputs are never stored in sorted order and no combine kernel runs.
+ *   order        [n_rows] int32   sorted position -> flat (token, slot) row, as
+ *                                 written by the plan entry points
+ *   row_weights  [n_rows] fp32    gate weight of every flat row (topk_weight
+ *                                 viewed flat)
+ *   out_tokens   [n_rows / k, hidden] bf16; zeroed by the call
+ * k must be 2: a token's row then receives exactly two addends on top of zero,
+ * and since that sum does not depend on which arrives first the result is the
+ * same bits in every run (each addend is rounded to bf16 before the add).  With
+ * a third addend (the shared expert, a residual) it would not be; those blocks
+ * keep dice_unpermute_combine.  bf16 only, on one GPU (the expert-parallel
+ * path returns rows to other ranks instead). */
+DICE_API int dice_grouped_ffn_combine(const void* rows_in, int64_t n_rows, int hidden, int ffn, int act,
+                             const void* w1, const void* w2, int n_slabs, const int32_t* seg_offsets,
+                             const int32_t* seg_slab, int n_seg, void* inter, const int32_t* order,
+                             const float* row_weights, int k, void* out_tokens, int reserve_sms,
+                             uint32_t* status, void* stream);
 
 /* fp32 variant of the expert FFN on the CUDA cores (no tensor-core rounding;
  * used where fp32 parity at 1e-5 is asked for).  Same arguments as

@@ -132,6 +132,34 @@ def test_shared_expert_rides_in_the_routed_launches(cuda_device, act, counts, n_
     assert _rel(got_shared.cpu().float(), want) < 2e-2
 
 
+@pytest.mark.parametrize("act", ["gelu_tanh", "swiglu"])
+@pytest.mark.parametrize("n,h,f,e", [(1, 64, 128, 4), (300, 128, 512, 8), (4096, 1152, 4608, 8), (1000, 1408, 5632, 16)])
+def test_combine_in_the_second_gemm_epilogue(cuda_device, act, n, h, f, e):
+    """dice_grouped_ffn_combine: the gate-weighted combine (models.py:377-381) inside the fc2 epilogue.  Against
+    the oracle's moe_infer within 2e-2, against the separate combine kernel within bf16 rounding, and the same
+    bits on every run (two addends per token on a zeroed row commute)."""
+    ops = _ops()
+    gen = torch.Generator(device=cuda_device).manual_seed(n + h)
+    w1, w2, experts = _make_experts(e, h, f, act, gen, cuda_device)
+    x = torch.randn(n, h, generator=gen, device=cuda_device).bfloat16()
+    idx = torch.stack([torch.randperm(e, generator=gen, device=cuda_device)[:2] for _ in range(min(n, 64))])
+    idx = idx.repeat((n + 63) // 64, 1)[:n].contiguous()  # two different experts per token
+    wts = torch.rand(n, 2, generator=gen, device=cuda_device)
+    status = torch.zeros(1, dtype=torch.int32, device=cuda_device)
+    pos, seg, order = ops.permute_plan(idx.view(-1), e, want_order=True)
+    rows = ops.permute_rows(x, pos, 2)
+    got = ops.grouped_ffn_combine(rows, w1, w2, seg, act, f, order, wts.view(-1).contiguous(), status)
+    again = ops.grouped_ffn_combine(rows, w1, w2, seg, act, f, order, wts.view(-1).contiguous(), status)
+    y_rows = ops.grouped_ffn(rows, w1, w2, seg, act, f, status)
+    sep = ops.unpermute_combine(y_rows, pos[0::2], y_rows, pos[1::2], wts[:, 0], wts[:, 1], n)
+    torch.cuda.synchronize()
+    ops.check_status(status)
+    assert got.shape == (n, h) and torch.equal(got, again)
+    want = O.moe_infer(x.cpu().float(), idx.cpu().view(-1), wts.cpu().view(-1), [[t.float() for t in ex] for ex in experts], act)
+    assert _rel(got.cpu().float(), want) < 2e-2
+    assert _rel(got.float(), sep.float()) < 1e-2
+
+
 def _near_tie_only(idx, idx_o, logits_o):
     """Every token whose selection differs from the oracle's must owe that to logits one bf16 ulp apart."""
     lo = logits_o.float()

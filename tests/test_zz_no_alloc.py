@@ -81,3 +81,28 @@ def test_static_plan_rejects_sizes_beyond_its_array(cuda_device):
     assert rc == 0
     torch.cuda.synchronize()
     assert int(seg[-1]) == ok_rows
+
+
+def test_static_plan_allocates_nothing(cuda_device):
+    """A warm call leaves the device's free memory and torch's allocator untouched: the scratch is the
+    library's own fixed array, not something obtained per call."""
+    from dice_b200 import _lib
+
+    lib = _lib.load()
+    n_rows, n_experts = 5000, 8
+    flat = torch.randint(0, n_experts, (n_rows,), device=cuda_device)
+    pos = torch.empty(n_rows, dtype=torch.int32, device=cuda_device)
+    seg = torch.empty(n_experts + 1, dtype=torch.int32, device=cuda_device)
+    stream = torch.cuda.current_stream().cuda_stream
+    call = lambda: lib.dice_permute_plan_static(flat.data_ptr(), n_rows, n_experts, pos.data_ptr(), None, seg.data_ptr(), stream)
+    assert call() == 0  # the first call on a device looks the array's address up
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info(cuda_device)
+    torch_before = (torch.cuda.memory_allocated(cuda_device), torch.cuda.memory_reserved(cuda_device))
+    for _ in range(3):
+        assert call() == 0
+    torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info(cuda_device)
+    assert free_after >= free_before  # nothing was taken from the device
+    assert (torch.cuda.memory_allocated(cuda_device), torch.cuda.memory_reserved(cuda_device)) == torch_before
+    assert int(seg[-1]) == n_rows
