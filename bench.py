@@ -277,6 +277,44 @@ def full_model_step(blocks, tokens, device, begin_step, barrier, ep, steps=10):
                     "(ms_per_step_glue_in_torch); backbone (attention, adaLN, embeddings): PyTorch bf16 harness"}
 
 
+def small_batch_serving(blocks, device, images=2, steps=20):
+    """One sampling step of the full model at a serving-size batch (2 images x2 CFG), where the step is bounded by
+    the host: eager against the same step captured once into a CUDA graph (dice_b200.serving.GraphedStep)."""
+    from bench_dit_model import DiTBackbone
+    from dice_b200.serving import GraphedStep
+
+    latent = int(round((TOKENS_PER_IMAGE) ** 0.5)) * 2
+    model = DiTBackbone(blocks, HIDDEN, latent=latent).to(device=device, dtype=torch.bfloat16).eval()
+    g = torch.Generator(device=device).manual_seed(6)
+    z = torch.randn(images, 4, latent, latent, generator=g, device=device).bfloat16()
+    cond = torch.randint(0, 1000, (images,), generator=g, device=device)
+    null = torch.full((images,), 1000, device=device)
+
+    def step(zz):
+        return model.sampling_step(zz, cond, null, t=0.5, dt=1.0 / 50.0)
+
+    def timed(fn):
+        for _ in range(3):
+            fn(z)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn(z)
+        e1.record()
+        torch.cuda.synchronize()
+        return round(e0.elapsed_time(e1) / steps, 3)
+
+    eager = timed(step)
+    try:
+        graphed = timed(GraphedStep(step, z, modules=[model]))
+    except Exception as exc:  # a capture that the installed driver refuses is reported, not fatal
+        return {"images": images, "eager_ms_per_step": eager, "graphed_ms_per_step": None, "error": str(exc)[:200]}
+    return {"images": images, "tokens": 2 * images * TOKENS_PER_IMAGE, "eager_ms_per_step": eager,
+            "graphed_ms_per_step": graphed,
+            "note": "full DiT-MoE sampling step (PyTorch backbone + dice_b200 MoE blocks), one CUDA graph per step"}
+
+
 def phase_times(step_fn, layers, steps=3):
     """GPU time of each named phase of the block (the section names the reference's profiler uses,
     ep_fwd.py:88-172, models.py:305-375), per layer, on this rank: CUDA events around every phase."""
@@ -672,6 +710,8 @@ def run_ours(args):
         line["phases_us_per_layer"] = phases
     if dit is not None:
         line["dit_sampling_step"] = dit
+    if world == 1 and dit is not None:
+        line["small_batch_serving"] = small_batch_serving(blocks, device)
     if not args.no_gpu_reference:
         t_ref, n_ref = gpu_reference(blocks, xs, ep)
         ref_ms = torch.tensor([t_ref], device=device)

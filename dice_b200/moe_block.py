@@ -15,6 +15,7 @@ from __future__ import annotations
 
 import contextlib
 import math
+import os
 from typing import List, Optional, Sequence
 
 import torch
@@ -338,6 +339,12 @@ class ExpertPack:
             ops.check_status(self.status, "grouped expert FFN")
 
 
+# DICE_FFN_COMBINE=1: blocks without a third addend let the second GEMM's epilogue do the gate-weighted combine
+# (dice_grouped_ffn_combine).  Off by default: the 16-byte bf16 reductions cost the GEMM more (about 40 us per layer
+# at 16384 tokens, hidden 1152) than the separate combine kernel they replace (about 22 us), and the rounding
+# differs from the combine kernel's fp32 sum, so the single-device and expert-parallel paths would stop agreeing
+# bit for bit.
+epilogue_combine = os.environ.get("DICE_FFN_COMBINE", "0") == "1"
 _fold_cached = None
 
 
@@ -542,9 +549,9 @@ class SparseMoeBlock(nn.Module):
         assert not self.para_mode.ep
         n_tokens = x.shape[0]
         k = self.num_experts_per_tok
-        if (_chunks is not None and _addend is None and _shared is None and _glue is None and k == 2 and n_tokens > 0
-                and _fold_shared()):
-            # nothing but the two expert rows goes into a token's output: the second GEMM adds them itself
+        if (epilogue_combine and _chunks is not None and _addend is None and _shared is None and _glue is None and k == 2
+                and n_tokens > 0 and _fold_shared()):
+            # nothing but the two expert rows goes into a token's output: the second GEMM can add them itself
             # (models.py:377-381 inside its epilogue), three launches and a memset for the whole dispatch -> combine
             pos, seg, order, rows = ops.permute_plan_chunked(flat_expert_indices, _chunks, self.num_experts, 1, x, k,
                                                              want_order=True)

@@ -108,6 +108,31 @@ def test_gelu_variant_against_oracle(cuda_device, dtype):
         assert torch.equal(idx.cpu(), r["topk_idx"])
 
 
+def test_gelu_block_with_the_combine_in_the_gemm_epilogue(cuda_device, monkeypatch):
+    """The opt-in path (DICE_FFN_COMBINE=1) where the second GEMM adds the gate-weighted rows to the token rows
+    itself: same routing, output within 2e-2 of the oracle and within bf16 rounding of the default path."""
+    from dice_b200 import moe_block
+    from dice_b200.moe_block import ParaMode, SparseMoeBlock
+
+    torch.manual_seed(5)
+    h, e = 128, 8
+    blk = SparseMoeBlock(h, 4, e, 2, 1, 0, 1, ParaMode(), expert_act="gelu_tanh", shared_expert=False)
+    blk.gate.norm_topk_prob = True
+    blk = blk.to(device=cuda_device, dtype=torch.bfloat16).eval()
+    x = torch.randn(2, 301, h, device=cuda_device, dtype=torch.bfloat16)
+    default = blk(x)
+    monkeypatch.setattr(moe_block, "epilogue_combine", True)
+    y = blk(x)
+    blk.check_status()
+    assert not torch.equal(y, default)  # the other path did run
+    sd = {k: v.detach().float().cpu() for k, v in blk.state_dict().items()}
+    ex = [(sd[f"experts.{i}.fc1.weight"], sd[f"experts.{i}.fc2.weight"]) for i in range(e)]
+    idx, w, _ = blk.gate(x)
+    want = O.moe_infer(x.float().cpu().view(-1, h), idx.cpu().view(-1), w.cpu().view(-1), ex, "gelu_tanh")
+    assert ((y.float().cpu().view(-1, h) - want).norm() / want.norm()).item() < 2e-2
+    assert ((y.float() - default.float()).norm() / default.float().norm()).item() < 1e-2
+
+
 def test_empty_and_single_token_batches(cuda_device):
     g, sd = _small()
     blk = _block(32, 8, sd, cuda_device)
