@@ -128,6 +128,7 @@ plan_chunked_kernel(const int64_t* __restrict__ flat_idx, const int* __restrict_
                     int n_experts, int world, int n_chunks, int split, int* __restrict__ pos, int* __restrict__ order,
                     int* __restrict__ seg_offsets, const uint4* __restrict__ x, int row_vec, uint4* __restrict__ out_rows) {
   constexpr int kWarps = kChunkRows / 32;
+  constexpr int KK = K > 0 ? K : 1;  // rows per token where the gather is compiled in
   __shared__ int s_total[kMaxExperts];
   __shared__ int s_before[kMaxExperts];
   __shared__ int s_cbase[kMaxExperts];
@@ -140,6 +141,20 @@ plan_chunked_kernel(const int64_t* __restrict__ flat_idx, const int* __restrict_
   for (int i = threadIdx.x; i < kWarps * kMaxExperts; i += kChunkRows) (&s_warp_count[0][0])[i] = 0;
   __syncthreads();
   pdl_wait();
+  // The first token row of this warp is requested before the plan's loads and barriers, which then run under
+  // the row's memory latency (up to kPrefetch 16-byte chunks per lane; longer rows fetch the rest later).
+  constexpr int kPrefetch = 5;
+  uint4 pre[kPrefetch];
+  if (K > 0) {
+    const int tokens_per_part = kChunkRows / KK / split;
+    const int64_t t = static_cast<int64_t>(chunk) * (kChunkRows / KK) + part * tokens_per_part + warp;
+    if (warp < tokens_per_part && t < n_rows / KK) {
+      const uint4* src = x + t * row_vec;
+#pragma unroll
+      for (int j = 0; j < kPrefetch; ++j)
+        if (lane + 32 * j < row_vec) pre[j] = ldg_stream16(src + lane + 32 * j);
+    }
+  }
   for (int i = threadIdx.x; i < n_chunks * n_experts; i += kChunkRows) {
     const int c = i / n_experts, e = i - c * n_experts;
     const int v = chunk_hist[i];
@@ -183,18 +198,31 @@ plan_chunked_kernel(const int64_t* __restrict__ flat_idx, const int* __restrict_
   if (K > 0) {
     s_pos[threadIdx.x] = p;
     __syncthreads();
-    const int tokens_per_part = kChunkRows / K / split;
-    const int64_t n_tokens = n_rows / K;
+    const int tokens_per_part = kChunkRows / KK / split;
+    const int64_t n_tokens = n_rows / KK;
     for (int i = warp; i < tokens_per_part; i += kWarps) {
       const int tl = part * tokens_per_part + i;  // token inside the chunk
-      const int64_t t = static_cast<int64_t>(chunk) * (kChunkRows / K) + tl;
+      const int64_t t = static_cast<int64_t>(chunk) * (kChunkRows / KK) + tl;
       if (t >= n_tokens) break;
-      int64_t dst[K > 0 ? K : 1];
+      int64_t dst[KK];
 #pragma unroll
       for (int s = 0; s < K; ++s) dst[s] = static_cast<int64_t>(s_pos[tl * K + s]) * row_vec;
       const uint4* src = x + t * row_vec;
+      int c0 = lane;
+      if (i == warp) {  // this warp's first token: its head is already in registers
+#pragma unroll
+        for (int j = 0; j < kPrefetch; ++j) {
+          const int c = lane + 32 * j;
+          if (c < row_vec) {
+#pragma unroll
+            for (int s = 0; s < K; ++s)
+              if (dst[s] >= 0) stg_stream16(out_rows + dst[s] + c, pre[j]);
+          }
+        }
+        c0 = lane + 32 * kPrefetch;
+      }
 #pragma unroll 4
-      for (int c = lane; c < row_vec; c += 32) {
+      for (int c = c0; c < row_vec; c += 32) {
         const uint4 v = ldg_stream16(src + c);
 #pragma unroll
         for (int s = 0; s < K; ++s)
@@ -252,8 +280,8 @@ struct Vec16<float> {
   }
 };
 
-template <typename T>
-__global__ void __launch_bounds__(256)
+template <typename T, bool kGlue>
+__global__ void __launch_bounds__(256, kGlue ? 4 : 6)
 unpermute_combine_kernel(const uint4* __restrict__ src0, const int* __restrict__ idx0, int idx0_stride,
                          const uint4* __restrict__ src1, const int* __restrict__ idx1, int idx1_stride,
                          const float* __restrict__ w0, const float* __restrict__ w1, int w_stride,
@@ -273,8 +301,8 @@ unpermute_combine_kernel(const uint4* __restrict__ src0, const int* __restrict__
   const uint4* p1 = (i1 >= 0) ? src1 + i1 * row_vec : nullptr;
   const uint4* pa = addend ? addend + t * row_vec : nullptr;
   // the gated residual of the DiT block: out = resid + gate[sample of t] * (the sum above)
-  const uint4* pr = resid ? resid + t * row_vec : nullptr;
-  const uint4* pg = gate ? gate + (t / tokens_per_sample) * row_vec : nullptr;
+  const uint4* pr = (kGlue && resid) ? resid + t * row_vec : nullptr;
+  const uint4* pg = (kGlue && gate) ? gate + (t / tokens_per_sample) * row_vec : nullptr;
   uint4* po = out + t * row_vec;
 #pragma unroll 2
   for (int c = lane; c < row_vec; c += 32) {
@@ -299,13 +327,13 @@ unpermute_combine_kernel(const uint4* __restrict__ src0, const int* __restrict__
 #pragma unroll
       for (int j = 0; j < EL; ++j) acc[j] += f[j];
     }
-    if (pg) {
+    if (kGlue && pg) {
       float f[EL];
       Vec16<T>::to_float(__ldg(pg + c), f);
 #pragma unroll
       for (int j = 0; j < EL; ++j) acc[j] *= f[j];
     }
-    if (pr) {
+    if (kGlue && pr) {
       float f[EL];
       Vec16<T>::to_float(ldg_stream16(pr + c), f);
 #pragma unroll
@@ -434,7 +462,7 @@ extern "C" int dice_permute_plan_chunked(const int64_t* flat_idx, const int32_t*
   DICE_CHECK_ARG((hidden * es) % 16 == 0, DICE_ERR_SHAPE);
   DICE_CHECK_ARG(dice_aligned16(x) && dice_aligned16(out_rows), DICE_ERR_ALIGN);
   const int row_vec = static_cast<int>(hidden * es / 16);
-  const int split = 8;  // CTAs per chunk: 16 (k = 2) or 32 (k = 1) tokens each
+  const int split = 16;  // CTAs per chunk: 8 (k = 2) or 16 (k = 1) tokens each, one or two per warp
   if (k == 2)
     DICE_CUDA_OK(dice_launch(plan_chunked_kernel<2>, dim3(n_chunks * split), dim3(kChunkRows), 0, s, flat_idx, chunk_hist,
                              n_rows, n_experts, world, n_chunks, split, out_pos, out_order, out_seg_offsets,
@@ -491,17 +519,20 @@ extern "C" int dice_unpermute_combine(const void* src0, const int32_t* idx0, int
   DICE_CHECK_ARG(blocks <= 0x7fffffffLL, DICE_ERR_LIMIT);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const dim3 grid(static_cast<unsigned>(blocks));
-  if (dtype == DICE_BF16)
-    DICE_CUDA_OK(dice_launch(unpermute_combine_kernel<__nv_bfloat16>, grid, dim3(256), 0, s,
-                             static_cast<const uint4*>(src0), idx0, idx0_stride, static_cast<const uint4*>(src1), idx1,
-                             idx1_stride, w0, w1, w_stride, static_cast<const uint4*>(addend),
-                             static_cast<const uint4*>(resid), static_cast<const uint4*>(gate), tokens_per_sample, n_tokens,
-                             row_vec, static_cast<uint4*>(out)));
-  else
-    DICE_CUDA_OK(dice_launch(unpermute_combine_kernel<float>, grid, dim3(256), 0, s, static_cast<const uint4*>(src0),
-                             idx0, idx0_stride, static_cast<const uint4*>(src1), idx1, idx1_stride, w0, w1, w_stride,
-                             static_cast<const uint4*>(addend), static_cast<const uint4*>(resid),
-                             static_cast<const uint4*>(gate), tokens_per_sample, n_tokens, row_vec, static_cast<uint4*>(out)));
+  const bool glue = resid != nullptr || gate != nullptr;
+#define DICE_LAUNCH_COMBINE(T, G)                                                                                        \
+  DICE_CUDA_OK(dice_launch(unpermute_combine_kernel<T, G>, grid, dim3(256), 0, s, static_cast<const uint4*>(src0), idx0,  \
+                           idx0_stride, static_cast<const uint4*>(src1), idx1, idx1_stride, w0, w1, w_stride,            \
+                           static_cast<const uint4*>(addend), static_cast<const uint4*>(resid),                          \
+                           static_cast<const uint4*>(gate), tokens_per_sample, n_tokens, row_vec, static_cast<uint4*>(out)))
+  if (dtype == DICE_BF16) {
+    if (glue) DICE_LAUNCH_COMBINE(__nv_bfloat16, true);
+    else DICE_LAUNCH_COMBINE(__nv_bfloat16, false);
+  } else {
+    if (glue) DICE_LAUNCH_COMBINE(float, true);
+    else DICE_LAUNCH_COMBINE(float, false);
+  }
+#undef DICE_LAUNCH_COMBINE
   return DICE_OK;
 }
 
