@@ -204,7 +204,9 @@ def _peer_push(info, async_op, dispatch=None, rows_back=None):
     # the few SMs that the FFN leaves free (p2p.reserve_sms)
     side_ctas = (p2p.side_push_ctas() or -1) if async_op else 0
     p2p.note_push(async_op)
-    if async_op:
+    if async_op and dispatch is not None and dispatch.on_side:
+        stream = x.comm_raw  # the count exchange in front already moved this exchange to the side stream
+    elif async_op:
         stream = x.fork_to_comm()  # the push runs on the side stream, after what the current stream has produced
         # the caching allocator must not hand these to someone else before the side stream has read them
         for t in ((dispatch.inp, dispatch.pos, dispatch.seg_offsets) if dispatch is not None else (rows_back,)):
@@ -224,6 +226,8 @@ def _peer_push(info, async_op, dispatch=None, rows_back=None):
             _dtype_code(rows_back), x.rank, x.world, x.min_peer_rows, x.capacity_rows, info.seq, side_ctas, x.status_ptr,
             stream),
             "dice_ep_return_rows")
+        if async_op:
+            x.note_output_read_on_side(rows_back)
         out, which = x.back[slot][: info.rows_sent], 1
     # a consumer on another stream must also see what THIS rank's side stream wrote (the meta block of the count
     # exchange, the rows this rank pushed into its own buffers)
@@ -256,12 +260,14 @@ def proc_experts(inp, experts, token_counts_global, num_local_experts):
                 pack.run_offsets_return(inp, token_counts_global)
                 return p2p.ReturnedRows(token_counts_global)
             job = _shared_job
+            xchg = token_counts_global.xchg
+            inter, out = xchg.ffn_buffers(pack.ffn_width(inp.dtype)) if inp.shape[0] == xchg.capacity_rows else (None, None)
             if job is not None and inp.dtype == torch.bfloat16:
-                outp, job.out = pack.run_offsets(inp, token_counts_global.seg_dev, token_counts_global.xchg.seg_slab_dev,
-                                                 reserve_sms=p2p.reserve_sms(), shared=(job.x, job.pack))
+                outp, job.out = pack.run_offsets(inp, token_counts_global.seg_dev, xchg.seg_slab_dev,
+                                                 reserve_sms=p2p.reserve_sms(), shared=(job.x, job.pack), inter=inter, out=out)
                 return outp
-            return pack.run_offsets(inp, token_counts_global.seg_dev, token_counts_global.xchg.seg_slab_dev,
-                                    reserve_sms=p2p.reserve_sms())
+            return pack.run_offsets(inp, token_counts_global.seg_dev, xchg.seg_slab_dev, reserve_sms=p2p.reserve_sms(),
+                                    inter=inter, out=out)
         world_size, rank = token_counts_global.xchg.world, token_counts_global.xchg.rank
         seg_slab = token_counts_global.xchg.seg_slab
         offs = token_counts_global.seg_dev.tolist()  # arbitrary expert modules need the bounds on the host
@@ -405,7 +411,7 @@ def moe_infer_ep(inp: torch.Tensor, experts: nn.ModuleList, flat_expert_indices,
                 "dice_ep_exchange_counts")
         counts_local = None
         counts_global = p2p.SegInfo(xchg, slot, seq, tab, n_tokens * k_eff)
-        grouped_dup_inp = p2p.PendingRows(inp, pos, seg_offsets, k_eff, counts_global)
+        grouped_dup_inp = p2p.PendingRows(inp, pos, seg_offsets, k_eff, counts_global, on_side=side)
     else:
         with _scope("exchange_token_counts"):
             counts_local, counts_global = _exchange_counts_by_owner(seg_offsets[1:] - seg_offsets[:-1], world_size, rank)

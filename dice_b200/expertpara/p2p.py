@@ -152,6 +152,8 @@ class PeerExchange:
         self.seg_slab_dev = torch.tensor(self.seg_slab, dtype=torch.int32, device=self.device)
         self._fork = torch.cuda.Event()
         self._side_events = [torch.cuda.Event() for _ in range(2 * n_slots)]
+        self._ring_events = [torch.cuda.Event() for _ in range(self.FFN_OUT_RING)]
+        self._ffn_inter, self._ffn_out, self._ffn_out_event, self._ffn_out_index, self._ffn_next = {}, [], [], {}, 0
         self._comm = torch.cuda.Stream(device=self.device)
         self.comm_raw = self._comm.cuda_stream
         dist.barrier(group=group)
@@ -192,6 +194,46 @@ class PeerExchange:
         self._fork.record(current_stream_object())
         self._comm.wait_event(self._fork)
         return self.comm_raw
+
+    # -- scratch of the expert FFN over a receive buffer -----------------------------
+    # The receive buffer holds `capacity_rows` rows (W x the largest sender when memory allows), of which a
+    # routing fills about 1/W.  Allocating the FFN's intermediate and output per call at that size and keeping
+    # the outputs alive in the asynchronous caches (two steps x all layers) made the caching allocator thrash on
+    # the G/2 shapes.  The exchange therefore owns one intermediate per FFN width and a small ring of output
+    # buffers: an output is read by the return push that follows its FFN and is free again long before the ring
+    # comes round (the event of that push is waited for all the same).
+    FFN_OUT_RING = 4
+
+    def ffn_buffers(self, ffn: int):
+        """(intermediate [capacity, ffn], output [capacity, hidden]) for the next expert FFN over a receive buffer."""
+        from ..ops import current_stream_object
+
+        inter = self._ffn_inter.get(ffn)
+        if inter is None:
+            inter = self._ffn_inter[ffn] = torch.empty((self.capacity_rows, ffn), dtype=self.dtype, device=self.device)
+        if not self._ffn_out:
+            self._ffn_out = [torch.empty((self.capacity_rows, self.hidden), dtype=self.dtype, device=self.device)
+                             for _ in range(self.FFN_OUT_RING)]
+            self._ffn_out_event = [None] * self.FFN_OUT_RING
+            self._ffn_out_index = {t.data_ptr(): i for i, t in enumerate(self._ffn_out)}
+            for t in self._ffn_out:
+                t.keepalive = None  # the asynchronous caches need not (and must not) count or pin ring buffers
+        i = self._ffn_next
+        self._ffn_next = (i + 1) % self.FFN_OUT_RING
+        ev = self._ffn_out_event[i]
+        if ev is not None:  # the side-stream push that last read this buffer
+            current_stream_object().wait_event(ev)
+            self._ffn_out_event[i] = None
+        return inter, self._ffn_out[i]
+
+    def note_output_read_on_side(self, rows_back: torch.Tensor) -> None:
+        """A return push on the side stream reads ``rows_back``: if it is a ring buffer, remember where the side
+        stream is, so that the buffer's next use waits for this push."""
+        i = self._ffn_out_index.get(rows_back.data_ptr()) if self._ffn_out else None
+        if i is not None:
+            ev = self._ring_events[i]
+            ev.record(self._comm)
+            self._ffn_out_event[i] = ev
 
     def record_side_event(self, slot: int, which: int) -> torch.cuda.Event:
         """Mark the side stream's position after a push of ``slot`` (0 dispatch, 1 return)."""
@@ -344,8 +386,11 @@ class PendingRows:
     send buffer; the dispatch kernel reads ``inp`` through ``pos`` and writes
     each row into its expert owner's receive buffer."""
 
-    def __init__(self, inp: torch.Tensor, pos: torch.Tensor, seg_offsets: torch.Tensor, k_eff: int, info: SegInfo):
+    def __init__(self, inp: torch.Tensor, pos: torch.Tensor, seg_offsets: torch.Tensor, k_eff: int, info: SegInfo,
+                 on_side: bool = False):
         self.inp, self.pos, self.seg_offsets, self.k_eff, self.info = inp, pos, seg_offsets, k_eff, info
+        # the side stream was already ordered after these tensors' producers (by the count exchange in front)
+        self.on_side = on_side
 
     @property
     def keepalive(self) -> torch.Tensor:

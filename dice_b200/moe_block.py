@@ -259,10 +259,14 @@ class ExpertPack:
         self._built[dtype] = (sig, built, p0, p0.data_ptr(), p0._version)
         return built
 
+    def ffn_width(self, dtype: torch.dtype) -> int:
+        return self.get(dtype)[1]
+
     def run_offsets(self, rows: torch.Tensor, seg_offsets: torch.Tensor, seg_slab: Optional[torch.Tensor] = None,
-                    reserve_sms: int = 0, shared=None):
+                    reserve_sms: int = 0, shared=None, inter=None, out=None):
         """The grouped FFN over ``rows``.  ``shared = (tokens, pack of the shared expert)`` lets the shared expert
-        ride in the same launches (bf16); the result is then ``(rows_out, shared_out)``."""
+        ride in the same launches (bf16); the result is then ``(rows_out, shared_out)``.  ``inter`` / ``out`` are
+        caller-owned buffers for the intermediate and the result (allocated per call when None)."""
         act, ffn, w1, w2 = self.get(rows.dtype)
         extra = None
         if shared is not None:
@@ -272,14 +276,14 @@ class ExpertPack:
             extra = (sx, sw1, sw2, s_ffn)
         if not ExpertPack._want_timing():
             return ops.grouped_ffn(rows, w1, w2, seg_offsets, act, ffn, status=self.status, seg_slab=seg_slab,
-                                   reserve_sms=reserve_sms, shared=extra)
+                                   reserve_sms=reserve_sms, shared=extra, inter=inter, out=out)
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         start.record()
-        out = ops.grouped_ffn(rows, w1, w2, seg_offsets, act, ffn, status=self.status, seg_slab=seg_slab,
-                              reserve_sms=reserve_sms, shared=extra)
+        res = ops.grouped_ffn(rows, w1, w2, seg_offsets, act, ffn, status=self.status, seg_slab=seg_slab,
+                              reserve_sms=reserve_sms, shared=extra, inter=inter, out=out)
         end.record()
         ExpertPack.timing.append((self.tag if shared is None else self.tag + "+shared", start, end))
-        return out
+        return res
 
     def run_offsets_combine(self, rows: torch.Tensor, seg_offsets: torch.Tensor, order: torch.Tensor, flat_weights):
         """The grouped FFN with the gate-weighted combine in the second GEMM's epilogue: returns token rows."""
