@@ -558,6 +558,9 @@ int sm_count_here() {
 // the two shapes of the bulk-copy pushes (see above)
 constexpr BulkShape kBulkAlone = {1, 4, 32768};
 constexpr BulkShape kBulkBeside = {4, 3, 16384};
+// (Measured on two GPUs, 18.9 MB to the peer: ring shapes of 1-8 warps x 3-4 buffers x 8-32 KB all give the same
+// rates: about 495 GB/s from all SMs and 300 GB/s from 8 CTAs, against 630 GB/s for a copy-engine transfer of the
+// same bytes; the limit is how fast one SM's copy unit feeds NVLink, not the depth of the rings.)
 
 template <typename Kern>
 int bulk_smem_ready(Kern kernel) {
