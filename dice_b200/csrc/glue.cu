@@ -44,12 +44,13 @@ __device__ __forceinline__ void store_chunk(float* dst, const float* f) {
   *reinterpret_cast<float4*>(dst) = make_float4(f[0], f[1], f[2], f[3]);
 }
 
-template <typename TIn, typename TOut>
+// MAXC: 16-byte chunks of the row one lane holds (the row stays in registers in its storage format and is
+// unpacked in each pass, so a bf16 row of 1152 costs 20 registers per lane and several CTAs share an SM)
+template <typename TIn, typename TOut, int MAXC>
 __global__ void __launch_bounds__(256)
 ln_modulate_kernel(const TIn* __restrict__ x, const TIn* __restrict__ shift, const TIn* __restrict__ scale,
                    int64_t n_tokens, int hidden, int tokens_per_sample, float eps, TOut* __restrict__ out) {
   constexpr int EL = Elem<TIn>::kPerChunk;
-  constexpr int kMaxChunksPerLane = kMaxRowElems / 32 / EL;  // 16-byte chunks of the row held by one lane
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t t = static_cast<int64_t>(blockIdx.x) * 8 + warp;
   pdl_trigger();
@@ -57,15 +58,18 @@ ln_modulate_kernel(const TIn* __restrict__ x, const TIn* __restrict__ shift, con
   if (t >= n_tokens) return;
   const int n_chunks = hidden / EL;
   const uint4* row = reinterpret_cast<const uint4*>(x + t * hidden);
-  float v[kMaxChunksPerLane][EL];
+  uint4 raw[MAXC];
+#pragma unroll
+  for (int i = 0; i < MAXC; ++i)
+    if (lane + 32 * i < n_chunks) raw[i] = ldg_stream16(row + lane + 32 * i);
   float sum = 0.f;
 #pragma unroll
-  for (int i = 0; i < kMaxChunksPerLane; ++i) {
-    const int c = lane + 32 * i;
-    if (c < n_chunks) {
-      Elem<TIn>::unpack(ldg_stream16(row + c), v[i]);
+  for (int i = 0; i < MAXC; ++i) {
+    if (lane + 32 * i < n_chunks) {
+      float v[EL];
+      Elem<TIn>::unpack(raw[i], v);
 #pragma unroll
-      for (int j = 0; j < EL; ++j) sum += v[i][j];
+      for (int j = 0; j < EL; ++j) sum += v[j];
     }
   }
 #pragma unroll
@@ -73,11 +77,13 @@ ln_modulate_kernel(const TIn* __restrict__ x, const TIn* __restrict__ shift, con
   const float mean = sum / static_cast<float>(hidden);
   float sq = 0.f;
 #pragma unroll
-  for (int i = 0; i < kMaxChunksPerLane; ++i) {
+  for (int i = 0; i < MAXC; ++i) {
     if (lane + 32 * i < n_chunks) {
+      float v[EL];
+      Elem<TIn>::unpack(raw[i], v);
 #pragma unroll
       for (int j = 0; j < EL; ++j) {
-        const float d = v[i][j] - mean;
+        const float d = v[j] - mean;
         sq = fmaf(d, d, sq);
       }
     }
@@ -90,14 +96,15 @@ ln_modulate_kernel(const TIn* __restrict__ x, const TIn* __restrict__ shift, con
   const uint4* sc = reinterpret_cast<const uint4*>(scale + b * hidden);
   TOut* o = out + t * hidden;
 #pragma unroll
-  for (int i = 0; i < kMaxChunksPerLane; ++i) {
+  for (int i = 0; i < MAXC; ++i) {
     const int c = lane + 32 * i;
     if (c < n_chunks) {
-      float s[EL], m[EL], r[EL];
+      float v[EL], s[EL], m[EL], r[EL];
+      Elem<TIn>::unpack(raw[i], v);
       Elem<TIn>::unpack(__ldg(sh + c), s);
       Elem<TIn>::unpack(__ldg(sc + c), m);
 #pragma unroll
-      for (int j = 0; j < EL; ++j) r[j] = fmaf((v[i][j] - mean) * rstd, 1.f + m[j], s[j]);
+      for (int j = 0; j < EL; ++j) r[j] = fmaf((v[j] - mean) * rstd, 1.f + m[j], s[j]);
       if constexpr (EL == 8 && sizeof(TOut) == 2) {
         store_chunk(reinterpret_cast<__nv_bfloat16*>(o) + c * 8, r);
       } else if constexpr (EL == 4 && sizeof(TOut) == 4) {
@@ -110,6 +117,27 @@ ln_modulate_kernel(const TIn* __restrict__ x, const TIn* __restrict__ shift, con
       }
     }
   }
+}
+
+template <typename TIn, typename TOut, int MAXC>
+cudaError_t launch_ln(const void* x, const void* shift, const void* scale, int64_t n_tokens, int hidden, int tps, float eps,
+                      void* out, cudaStream_t s) {
+  const dim3 grid(static_cast<unsigned>((n_tokens + 7) / 8));
+  return dice_launch(ln_modulate_kernel<TIn, TOut, MAXC>, grid, dim3(256), 0, s, static_cast<const TIn*>(x),
+                     static_cast<const TIn*>(shift), static_cast<const TIn*>(scale), n_tokens, hidden, tps, eps,
+                     static_cast<TOut*>(out));
+}
+
+// the smallest instantiation whose lanes can hold the row
+template <typename TIn, typename TOut>
+cudaError_t dispatch_ln(const void* x, const void* shift, const void* scale, int64_t n_tokens, int hidden, int tps, float eps,
+                        void* out, cudaStream_t s) {
+  constexpr int EL = Elem<TIn>::kPerChunk;
+  constexpr int kFull = kMaxRowElems / 32 / EL;  // 8 (bf16) or 16 (fp32) chunks per lane
+  const int per_lane = (hidden / EL + 31) / 32;
+  if (per_lane <= kFull / 4) return launch_ln<TIn, TOut, kFull / 4>(x, shift, scale, n_tokens, hidden, tps, eps, out, s);
+  if (per_lane <= (kFull * 5) / 8) return launch_ln<TIn, TOut, (kFull * 5) / 8>(x, shift, scale, n_tokens, hidden, tps, eps, out, s);
+  return launch_ln<TIn, TOut, kFull>(x, shift, scale, n_tokens, hidden, tps, eps, out, s);
 }
 
 }  // namespace
@@ -128,19 +156,12 @@ extern "C" int dice_ln_modulate(const void* x, const void* shift, const void* sc
   const int64_t blocks = (n_tokens + 7) / 8;
   DICE_CHECK_ARG(blocks <= 0x7fffffffLL, DICE_ERR_LIMIT);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const dim3 grid(static_cast<unsigned>(blocks));
+  cudaError_t err;
   if (dtype == DICE_BF16)
-    DICE_CUDA_OK(dice_launch(ln_modulate_kernel<__nv_bfloat16, __nv_bfloat16>, grid, dim3(256), 0, s,
-                             static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(shift),
-                             static_cast<const __nv_bfloat16*>(scale), n_tokens, hidden, tokens_per_sample, eps,
-                             static_cast<__nv_bfloat16*>(out)));
+    err = dispatch_ln<__nv_bfloat16, __nv_bfloat16>(x, shift, scale, n_tokens, hidden, tokens_per_sample, eps, out, s);
   else if (out_dtype == DICE_F32)
-    DICE_CUDA_OK(dice_launch(ln_modulate_kernel<float, float>, grid, dim3(256), 0, s, static_cast<const float*>(x),
-                             static_cast<const float*>(shift), static_cast<const float*>(scale), n_tokens, hidden,
-                             tokens_per_sample, eps, static_cast<float*>(out)));
+    err = dispatch_ln<float, float>(x, shift, scale, n_tokens, hidden, tokens_per_sample, eps, out, s);
   else
-    DICE_CUDA_OK(dice_launch(ln_modulate_kernel<float, __nv_bfloat16>, grid, dim3(256), 0, s, static_cast<const float*>(x),
-                             static_cast<const float*>(shift), static_cast<const float*>(scale), n_tokens, hidden,
-                             tokens_per_sample, eps, static_cast<__nv_bfloat16*>(out)));
-  return DICE_OK;
+    err = dispatch_ln<float, __nv_bfloat16>(x, shift, scale, n_tokens, hidden, tokens_per_sample, eps, out, s);
+  return err == cudaSuccess ? DICE_OK : DICE_ERR_CUDA;
 }

@@ -155,13 +155,20 @@ plan_chunked_kernel(const int64_t* __restrict__ flat_idx, const int* __restrict_
         if (lane + 32 * j < row_vec) pre[j] = ldg_stream16(src + lane + 32 * j);
     }
   }
-  for (int i = threadIdx.x; i < n_chunks * n_experts; i += kChunkRows) {
-    const int c = i / n_experts, e = i - c * n_experts;
-    const int v = chunk_hist[i];
-    if (v != 0) {
-      atomicAdd(&s_total[e], v);
-      if (c < chunk) atomicAdd(&s_before[e], v);
+  // one warp per expert adds up that expert's column of the table: the total and the part in front of this chunk
+  for (int ex = warp; ex < n_experts; ex += kWarps) {
+    int tot = 0, bef = 0;
+    for (int c = lane; c < n_chunks; c += 32) {
+      const int v = chunk_hist[c * n_experts + ex];
+      tot += v;
+      if (c < chunk) bef += v;
     }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+      tot += __shfl_xor_sync(0xffffffffu, tot, off);
+      bef += __shfl_xor_sync(0xffffffffu, bef, off);
+    }
+    if (lane == 0) { s_total[ex] = tot; s_before[ex] = bef; }
   }
   const int64_t r = static_cast<int64_t>(chunk) * kChunkRows + threadIdx.x;
   int e = -1;
