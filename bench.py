@@ -58,7 +58,7 @@ TOKENS_PER_IMAGE = 256
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 # dram__bytes_read.sum + dram__bytes_write.sum of one grouped-GEMM launch of this workload,
 # scaled from the ncu capture summarised under profiles/ (None until a capture exists)
-GEMM_TRAFFIC_BYTES = 452.2e6  # mean of fc1 (415.7 MB) and fc2 (488.6 MB) of the ncu capture summarised under profiles/
+GEMM_TRAFFIC_BYTES = 452.8e6  # mean of fc1 (417.4 MB) and fc2 (488.3 MB) of the ncu capture summarised under profiles/
 
 
 def parse_args():

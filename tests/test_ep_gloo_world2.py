@@ -110,6 +110,42 @@ def test_infer_matches_single_process(world, seed, async_op, pipeline):
     assert _spawn(_infer_worker, world, seed, async_op, pipeline) == [0] * world
 
 
+def _skew_worker(rank, world, port):
+    """Zipf-like routing: three quarters of all rows go to the experts of one rank, which then receives about
+    three times the mean.  The reference has no capacity (ep_fwd.py:247-293): nothing may be dropped."""
+    import torch.nn as nn
+
+    dist = _setup(rank, world, port)
+    from dice_b200.expertpara.ep_fwd import moe_infer_ep
+
+    n_tokens, hidden, n_experts, k = 96, 20, 8, 2
+    torch.manual_seed(7)
+    experts = []
+    for _ in range(n_experts):
+        lin = nn.Linear(hidden, hidden)
+        nn.init.uniform_(lin.weight, 0.0, 1.0)
+        experts.append(lin)
+    torch.manual_seed(70 + rank)
+    hot_rank = 1
+    with torch.no_grad():
+        for it in range(3):
+            x = torch.randn(n_tokens, hidden)
+            flat_idx = torch.randint(0, n_experts, (n_tokens * k,))
+            hot = torch.rand(n_tokens * k) < 0.75
+            flat_idx[hot] = hot_rank + world * torch.randint(0, n_experts // world, (int(hot.sum()),))
+            flat_w = torch.rand(n_tokens * k, 1)
+            got = moe_infer_ep(inp=x, experts=experts, flat_expert_indices=flat_idx, flat_expert_weights=flat_w,
+                               num_experts_per_tok=k, async_op=False, cache_key=0)
+            want = _single_process(experts, k, x, flat_idx, flat_w)
+            assert torch.allclose(got, want, atol=1e-5, rtol=1e-5), f"rank {rank} iter {it}"
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_skewed_routing_drops_nothing():
+    assert _spawn(_skew_worker, 4) == [0] * 4
+
+
 def _trim_worker(rank, world, port, n_experts):
     import torch.nn as nn
 

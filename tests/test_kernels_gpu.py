@@ -655,6 +655,50 @@ def test_exchange_overflow_is_found_by_every_rank_and_touches_nothing(cuda_devic
         assert int(R.done[r].sum()) == 0
 
 
+@pytest.mark.parametrize("max_ctas", [0, 4])
+def test_exchange_of_skewed_routing_with_lossless_capacity(cuda_device, max_ctas):
+    """Three quarters of all rows go to one rank's experts (it receives about three times the mean).  With the
+    receive capacity at world x the largest sender, which no routing can exceed, every row arrives and comes back."""
+    from dice_b200 import _lib
+
+    ops = _ops()
+    lib = _lib.load()
+    world, e, h, k = 4, 8, 128, 2
+    n = [300, 280, 320, 290]
+    xs, poss, segs = _emulated_inputs(world, e, h, n, k, cuda_device, seed=31, hot_owner=1)
+    seg_host = [s.cpu().tolist() for s in segs]
+    el = e // world
+    recv_rows = [sum(seg_host[s][(d + 1) * el] - seg_host[s][d * el] for s in range(world)) for d in range(world)]
+    assert recv_rows[1] > 2.5 * (sum(recv_rows) / world)
+    cap = world * k * max(n)
+    R = _EmulatedRanks(world, e, h, cap, k * max(n), cuda_device, lib)
+    st = torch.cuda.current_stream().cuda_stream
+    seq = 1
+    R.publish_counts(seg_host, seq)
+    for r in range(world):
+        assert lib.dice_ep_exchange_counts(segs[r].data_ptr(), R.table([c.data_ptr() for c in R.ctrl]), R.flags(0),
+                                           R.meta[r].data_ptr(), r, world, e, cap, seq, R.status[r].data_ptr(), st) == 0
+    for r in range(world):
+        assert lib.dice_ep_dispatch_rows(xs[r].data_ptr(), poss[r].data_ptr(), segs[r].data_ptr(), R.meta[r].data_ptr(),
+                                         R.table([t.data_ptr() for t in R.recv]), R.flags(1), R.done[r].data_ptr(), n[r], k,
+                                         h, 0, r, world, e, cap, seq, max_ctas, R.status[r].data_ptr(), st) == 0
+    for r in range(world):
+        assert lib.dice_ep_wait_flags(R.my_flags(r, 1), world, seq, 0, R.status[r].data_ptr(), st) == 0
+    for r in range(world):
+        assert lib.dice_ep_return_rows(R.recv[r].data_ptr(), R.meta[r].data_ptr(), R.table([t.data_ptr() for t in R.back]),
+                                       R.flags(2), R.done[r][1:].data_ptr(), h, 0, r, world, R.back_cap, cap, seq, max_ctas,
+                                       R.status[r].data_ptr(), st) == 0
+    for r in range(world):
+        assert lib.dice_ep_wait_flags(R.my_flags(r, 2), world, seq, 1, R.status[r].data_ptr(), st) == 0
+    torch.cuda.synchronize()
+    for r in range(world):
+        ops.check_status(R.status[r])
+        assert R.meta[r].cpu().tolist()[:2] == [recv_rows[r], 0]
+        want = ops.permute_rows(xs[r], poss[r], k)
+        assert torch.equal(R.back[r][: k * n[r]], want), f"rank {r} did not get its rows back"
+        assert bool((R.back[r][k * n[r]:] == 5.0).all()) and bool((R.recv[r][recv_rows[r]:] == 3.0).all())
+
+
 @pytest.mark.parametrize("max_ctas", [0, -1])
 def test_exchange_failure_reaches_the_peers(cuda_device, max_ctas):
     """Failure detection without a fault: rank 1 of two never publishes its counts, so rank 0's count exchange
