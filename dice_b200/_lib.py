@@ -72,7 +72,8 @@ SIGNATURES = {
     "dice_ep_dispatch_rows": (
         c_int,
         [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int,
-         c_int, c_int, c_uint32, c_int, c_void_p, c_void_p]),
+         c_int, c_int, c_uint32, c_int, c_int, c_void_p, c_void_p, c_void_p]),
+    "dice_ep_wait_dispatch": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_uint32, c_void_p, c_void_p]),
     "dice_ep_wait_flags": (c_int, [c_void_p, c_int, c_uint32, c_int, c_void_p, c_void_p]),
     "dice_ep_return_rows": (
         c_int,

@@ -45,6 +45,7 @@ grouped_gemm_f32_kernel(const float* __restrict__ a, const float* __restrict__ w
   __syncthreads();
   if (s_seg < 0) return;
   const int slab = seg_slab != nullptr ? seg_slab[s_seg] : s_seg;
+  if (slab < 0) return;  // rows that belong to no expert (the unused rest of a source's region)
   const float* wbase = w + static_cast<int64_t>(slab) * w_rows * k_dim;
   const int row0 = s_row0, rows = s_rows;
   const int col0 = blockIdx.y * TN;

@@ -89,7 +89,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       const int cnt = s_seg_off[s + 1] - s_seg_off[s];
       ok = ok && cnt >= 0;
       s_mprefix[s] = run;
-      run += cnt > 0 ? (cnt + BM - 1) / BM : 0;
+      const bool has_weights = p.seg_slab == nullptr || p.seg_slab[s] >= 0;  // slab -1: rows that belong to no expert
+      run += (cnt > 0 && has_weights) ? (cnt + BM - 1) / BM : 0;
     }
     ok = ok && s_seg_off[p.n_seg] <= p.n_rows;
     if (!ok) {

@@ -143,7 +143,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
   pdl_wait();  // the segment table and the rows written by earlier kernels are visible from here on
 
   if (p.ret_world > 0) {
-    if (threadIdx.x <= p.ret_world) s_ret_src[threadIdx.x] = p.ret_meta[2 + 2 * p.ret_world + threadIdx.x];
+    if (threadIdx.x <= p.ret_world) s_ret_src[threadIdx.x] = p.ret_meta[2 + 2 * p.ret_world + threadIdx.x];  // src_off of the meta block
     if (threadIdx.x < p.ret_world) s_ret_base[threadIdx.x] = p.ret_meta[2 + p.ret_world + threadIdx.x];
   }
   for (int i = threadIdx.x; i <= p.n_seg; i += kThreads)
@@ -156,7 +156,8 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
       const int cnt = s_seg_off[s + 1] - s_seg_off[s];
       ok = ok && cnt >= 0;
       s_mprefix[s] = run;
-      run += cnt > 0 ? (cnt + PM - 1) / PM : 0;
+      const bool has_weights = p.seg_slab == nullptr || p.seg_slab[s] >= 0;  // slab -1: rows that belong to no expert
+      run += (cnt > 0 && has_weights) ? (cnt + PM - 1) / PM : 0;
     }
     ok = ok && s_seg_off[p.n_seg] <= p.n_rows;
     if (!ok) {

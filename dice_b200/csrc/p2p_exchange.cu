@@ -89,14 +89,30 @@ __device__ bool wait_flag(const uint32_t* flag, uint32_t seq, uint32_t* status, 
   }
 }
 
-// Layout of the per-slot meta block this rank derives in ep_counts_kernel (int32):
+// Layout of the per-slot meta block (int32) that describes what this rank receives and where its own rows go.
+// It is derived by ep_counts_kernel (packed layout) or by ep_wait_dispatch_kernel (region layout):
 //   [0]                 total rows this rank receives
 //   [1]                 state: 0 ok, 1 a receive buffer would overflow, 2 the peers' counts never arrived
-//   [2, 2+W)            send_base[d]   first row of this rank's block in peer d's dispatch buffer
-//   [2+W, 2+2W)         back_base[s]   first row of this rank's block in peer s's combine buffer
-//   [2+2W, 3+3W)        src_off[s]     first row received from source s (W+1 entries)
-//   [3+3W, 4+3W+W*El)   seg_off[...]   offsets of the (source, slot) segments of the receive buffer
-__host__ __device__ inline int meta_ints(int w, int el) { return kMetaHead + 3 * w + 1 + w * el + 1; }
+//   send_base[W]        first row of this rank's block in peer d's dispatch buffer
+//   back_base[W]        first row of this rank's block in peer s's combine buffer
+//   src_off[W+1]        first row received from source s
+//   src_cnt[W]          rows received from source s
+//   seg_off[...]        offsets of the segments of the receive buffer, ready for the grouped GEMM:
+//                       packed layout: W*El segments in (source, slot) order;
+//                       region layout: W*(El+1) segments, every source's El slots followed by the unused rest
+//                       of its region (weight slab -1: skipped by the GEMM)
+__host__ __device__ inline int meta_ints(int w, int el) { return kMetaHead + 4 * w + 1 + w * (el + 1) + 1; }
+__host__ __device__ inline int meta_seg_base(int w) { return kMetaHead + 4 * w + 1; }
+
+// Two layouts of a receive buffer.
+//  * packed: the sources' blocks follow one another without gaps; a source learns where its block starts from
+//    the other sources' counts, so a count exchange (a rendezvous of all ranks) precedes the dispatch.  Works
+//    for any capacity.
+//  * regions (region_rows > 0): source s owns rows [s * region_rows, (s+1) * region_rows) of every receive
+//    buffer, where region_rows is at least the largest number of rows any rank ever sends.  A source then
+//    needs nobody's counts: the dispatch publishes this rank's counts along with its rows, and the receiver
+//    derives its segment table from the count matrix after the flags are up.  No count exchange, no rendezvous,
+//    and no routing can overflow; it needs capacity_rows = W * region_rows.
 
 // ---- 1. counts ---------------------------------------------------------------------
 __global__ void __launch_bounds__(256)
@@ -131,7 +147,8 @@ ep_counts_kernel(const int* __restrict__ seg_offsets,  // [E+1] this rank's key-
     int* send_base = meta + kMetaHead;
     int* back_base = send_base + world;
     int* src_off = back_base + world;
-    int* seg_off = src_off + world + 1;
+    int* src_cnt = src_off + world + 1;
+    int* seg_off = meta + meta_seg_base(world);
     // rows source s sends to owner d
     auto block_rows = [&](int s, int d) {
       int n = 0;
@@ -164,6 +181,7 @@ ep_counts_kernel(const int* __restrict__ seg_offsets,  // [E+1] this rank's key-
           seg_off[seg++] = run;
           run += s_cnt[s][rank * el + i];
         }
+        src_cnt[s] = run - src_off[s];
       }
       src_off[world] = run;
       seg_off[seg] = run;
@@ -172,7 +190,7 @@ ep_counts_kernel(const int* __restrict__ seg_offsets,  // [E+1] this rank's key-
       // the exchange moves nothing: every destination row lies "beyond the buffer", no rows are received,
       // no segment holds work (the layer's result is invalid and flagged on every rank)
       if (state == kStateOverflow && status != nullptr) atomicCAS(status, 0u, DICE_STATUS_EXCHANGE_OVERFLOW);
-      for (int d = 0; d < world; ++d) { send_base[d] = capacity_rows; back_base[d] = 0; }
+      for (int d = 0; d < world; ++d) { send_base[d] = capacity_rows; back_base[d] = 0; src_cnt[d] = 0; }
       for (int s = 0; s <= world; ++s) src_off[s] = 0;
       for (int i = 0; i <= world * el; ++i) seg_off[i] = 0;
       meta[kMetaTotal] = 0;
@@ -208,20 +226,41 @@ __device__ __forceinline__ void signal_when_grid_done(unsigned int* done_counter
 }
 
 // ---- 2. dispatch: permutation gather fused with the push into the owners' buffers --------
+// What every dispatch CTA needs first: where each owner's block starts in this rank's sorted order and where this
+// rank's rows start in each owner's buffer.  In the region layout the latter is fixed, and block 0 publishes this
+// rank's counts in every peer's matrix (ordered before the flags by the fences of signal_when_grid_done).
+__device__ __forceinline__ void dispatch_prologue(const int* __restrict__ seg_offsets, const int* __restrict__ meta,
+                                                  const PeerTable& matrices, int rank, int world, int el, int region_rows,
+                                                  int* s_first, int* s_base, int* s_fail) {
+  if (threadIdx.x <= world) s_first[threadIdx.x] = seg_offsets[threadIdx.x * el];
+  if (region_rows > 0) {
+    if (threadIdx.x < world) s_base[threadIdx.x] = rank * region_rows;
+    if (threadIdx.x == 0) *s_fail = 0;
+    if (blockIdx.x == 0) {
+      const int n_keys = world * el;
+      for (int i = threadIdx.x; i < world * n_keys; i += blockDim.x) {
+        const int d = i / n_keys, e = i - d * n_keys;
+        static_cast<int*>(matrices.ptr[d])[rank * n_keys + e] = seg_offsets[e + 1] - seg_offsets[e];
+      }
+    }
+  } else {
+    if (threadIdx.x < world) s_base[threadIdx.x] = meta[kMetaHead + threadIdx.x];
+    if (threadIdx.x == 0) *s_fail = meta[kMetaState] == kStateNoCounts;
+  }
+}
+
 template <int K>
 __global__ void __launch_bounds__(256)
 ep_dispatch_kernel(const uint4* __restrict__ x, const int* __restrict__ pos, const int* __restrict__ seg_offsets,
                    const int* __restrict__ meta, PeerTable recv_bufs, PeerTable flags, unsigned int* done_counter,
                    int64_t n_tokens, int row_vec, int rank, int world, int el, int capacity_rows, uint32_t seq,
-                   uint32_t* status) {
+                   uint32_t* status, int region_rows, PeerTable matrices) {
   __shared__ int s_first[kMaxRanks + 1];  // first sorted position of each owner's block
   __shared__ int s_base[kMaxRanks];
   __shared__ int s_fail;
   pdl_trigger();
   pdl_wait();
-  if (threadIdx.x <= world) s_first[threadIdx.x] = seg_offsets[threadIdx.x * el];
-  if (threadIdx.x < world) s_base[threadIdx.x] = meta[kMetaHead + threadIdx.x];
-  if (threadIdx.x == 0) s_fail = meta[kMetaState] == kStateNoCounts;
+  dispatch_prologue(seg_offsets, meta, matrices, rank, world, el, region_rows, s_first, s_base, &s_fail);
   __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   for (int64_t t = static_cast<int64_t>(blockIdx.x) * 8 + warp; t < n_tokens; t += static_cast<int64_t>(gridDim.x) * 8) {
@@ -262,33 +301,102 @@ __global__ void ep_wait_kernel(const uint32_t* __restrict__ my_flags, int world,
   }
 }
 
+// Region layout: wait for every source's rows, then derive the meta block from the count matrix the sources
+// published with them (segments of the receive buffer for the grouped GEMM, where the outputs go back to).
+__global__ void __launch_bounds__(256)
+ep_wait_dispatch_kernel(const uint32_t* __restrict__ my_flags, const int* __restrict__ my_matrix, int* __restrict__ meta,
+                        int rank, int world, int n_keys, int region_rows, uint32_t seq, uint32_t* status) {
+  __shared__ int s_cnt[kMaxRanks][kMaxKeys];
+  __shared__ int s_ok;
+  const int el = n_keys / world;
+  pdl_trigger();
+  pdl_wait();
+  if (threadIdx.x == 0) s_ok = 1;
+  __syncthreads();
+  if (threadIdx.x < world) {
+    if (!wait_flag(my_flags + threadIdx.x, seq, status, DICE_STATUS_WAIT_PEER_DISPATCH)) {
+      s_ok = 0;
+    } else if (ld_acquire_sys(my_flags + kFailMarkBase + threadIdx.x) == seq) {
+      if (status != nullptr) atomicCAS(status, 0u, DICE_STATUS_PEER_FAILED);
+      s_ok = 0;
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < world * n_keys; i += blockDim.x)
+    s_cnt[i / n_keys][i % n_keys] = s_ok ? my_matrix[i] : 0;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int* send_base = meta + kMetaHead;
+    int* back_base = send_base + world;
+    int* src_off = back_base + world;
+    int* src_cnt = src_off + world + 1;
+    int* seg_off = meta + meta_seg_base(world);
+    int total = 0, seg = 0;
+    for (int s = 0; s < world; ++s) {
+      send_base[s] = rank * region_rows;
+      int before = 0;  // rows of source s for the owners in front of this rank: where this rank's outputs go back to
+      for (int d = 0; d < rank; ++d)
+        for (int i = 0; i < el; ++i) before += s_cnt[s][d * el + i];
+      back_base[s] = before;
+      src_off[s] = s * region_rows;
+      int run = s * region_rows;
+      for (int i = 0; i < el; ++i) {
+        seg_off[seg++] = run;
+        run += s_cnt[s][rank * el + i];
+      }
+      // a source can never send more than its region holds; a count that says otherwise is not believed
+      if (run > (s + 1) * region_rows) run = (s + 1) * region_rows;
+      seg_off[seg++] = run;  // the unused rest of the region: a segment without a weight slab
+      src_cnt[s] = run - s * region_rows;
+      total += src_cnt[s];
+    }
+    src_off[world] = world * region_rows;
+    seg_off[seg] = world * region_rows;
+    meta[kMetaTotal] = total;
+    meta[kMetaState] = s_ok ? 0 : kStateNoCounts;
+  }
+}
+
 // ---- 4. return: expert outputs go back to the token owners --------------------------------
 __global__ void __launch_bounds__(256)
 ep_return_kernel(const uint4* __restrict__ rows, const int* __restrict__ meta, PeerTable back_bufs, PeerTable flags,
                  unsigned int* done_counter, int row_vec, int rank, int world, int back_capacity_rows, int max_rows,
                  uint32_t seq, uint32_t* status) {
-  __shared__ int s_src_off[kMaxRanks + 1];
+  __shared__ int s_src_off[kMaxRanks];   // first received row of source s
+  __shared__ int s_pre[kMaxRanks + 1];   // rows received from the sources in front of s
   __shared__ int s_back[kMaxRanks];
   __shared__ int s_fail;
   pdl_trigger();
   pdl_wait();
-  if (threadIdx.x <= world) s_src_off[threadIdx.x] = meta[kMetaHead + 2 * world + threadIdx.x];
-  if (threadIdx.x < world) s_back[threadIdx.x] = meta[kMetaHead + world + threadIdx.x];
-  if (threadIdx.x == 0) s_fail = meta[kMetaState] == kStateNoCounts;
+  if (threadIdx.x < world) {
+    s_src_off[threadIdx.x] = meta[kMetaHead + 2 * world + threadIdx.x];
+    s_back[threadIdx.x] = meta[kMetaHead + world + threadIdx.x];
+  }
+  if (threadIdx.x == 0) {
+    s_fail = meta[kMetaState] == kStateNoCounts;
+    int run = 0;
+    for (int s = 0; s < world; ++s) {
+      s_pre[s] = run;
+      int off = meta[kMetaHead + 2 * world + s], n = meta[kMetaHead + 3 * world + 1 + s];
+      if (off + n > max_rows) n = max_rows > off ? max_rows - off : 0;  // never read past the receive buffer
+      run += n > 0 ? n : 0;
+    }
+    s_pre[world] = run;
+  }
   __syncthreads();
-  int total = s_src_off[world];
-  if (total > max_rows) total = max_rows;  // never read past the receive buffer, whatever the meta block says
+  const int total = s_pre[world];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   for (int64_t r = static_cast<int64_t>(blockIdx.x) * 8 + warp; r < total; r += static_cast<int64_t>(gridDim.x) * 8) {
     int s = 0;
-    while (s + 1 < world && r >= s_src_off[s + 1]) ++s;
-    const int row = s_back[s] + static_cast<int>(r - s_src_off[s]);
+    while (s + 1 < world && r >= s_pre[s + 1]) ++s;
+    const int j = static_cast<int>(r - s_pre[s]);
+    const int row = s_back[s] + j;
     if (row >= back_capacity_rows) {
       if (lane == 0 && status != nullptr) atomicCAS(status, 0u, DICE_STATUS_EXCHANGE_OVERFLOW);
       continue;
     }
     uint4* dst = static_cast<uint4*>(back_bufs.ptr[s]) + static_cast<int64_t>(row) * row_vec;
-    const uint4* src = rows + r * row_vec;
+    const uint4* src = rows + static_cast<int64_t>(s_src_off[s] + j) * row_vec;
 #pragma unroll 4
     for (int c = lane; c < row_vec; c += 32) dst[c] = ldg_stream16(src + c);
   }
@@ -371,7 +479,8 @@ __global__ void __launch_bounds__(32 * kBulkMaxWarps)
 ep_dispatch_bulk_kernel(const uint8_t* __restrict__ x, const int* __restrict__ pos, const int* __restrict__ seg_offsets,
                         const int* __restrict__ meta, PeerTable recv_bufs, PeerTable flags, unsigned int* done_counter,
                         int64_t n_tokens, uint32_t row_bytes, int tokens_per_chunk, int rank, int world, int el,
-                        int capacity_rows, uint32_t seq, uint32_t* status, BulkShape shape) {
+                        int capacity_rows, uint32_t seq, uint32_t* status, BulkShape shape, int region_rows,
+                        PeerTable matrices) {
   extern __shared__ __align__(128) uint8_t bulk_bufs[];
   __shared__ __align__(8) uint64_t bars_all[kBulkMaxWarps][kBulkMaxBufs];
   __shared__ int s_first[kMaxRanks + 1];
@@ -386,9 +495,7 @@ ep_dispatch_bulk_kernel(const uint8_t* __restrict__ x, const int* __restrict__ p
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   pdl_wait();
-  if (threadIdx.x <= world) s_first[threadIdx.x] = seg_offsets[threadIdx.x * el];
-  if (threadIdx.x < world) s_base[threadIdx.x] = meta[kMetaHead + threadIdx.x];
-  if (threadIdx.x == 0) s_fail = meta[kMetaState] == kStateNoCounts;
+  dispatch_prologue(seg_offsets, meta, matrices, rank, world, el, region_rows, s_first, s_base, &s_fail);
   __syncthreads();
   // every warp of the grid is one worker; chunks are dealt round-robin over the workers
   const int64_t worker = static_cast<int64_t>(blockIdx.x) * shape.warps + warp;
@@ -451,7 +558,8 @@ ep_return_bulk_kernel(const uint8_t* __restrict__ rows, const int* __restrict__ 
                       int back_capacity_rows, int max_rows, uint32_t seq, uint32_t* status, BulkShape shape) {
   extern __shared__ __align__(128) uint8_t bulk_bufs[];
   __shared__ __align__(8) uint64_t bars_all[kBulkMaxWarps][kBulkMaxBufs];
-  __shared__ int s_src_off[kMaxRanks + 1];
+  __shared__ int s_src_off[kMaxRanks];
+  __shared__ int s_src_cnt[kMaxRanks];
   __shared__ int s_back[kMaxRanks];
   __shared__ int s_chunk0[kMaxRanks + 1];  // chunks before source s
   __shared__ int s_fail;
@@ -464,19 +572,20 @@ ep_return_bulk_kernel(const uint8_t* __restrict__ rows, const int* __restrict__ 
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   pdl_wait();
-  if (threadIdx.x <= world) {
-    int v = meta[kMetaHead + 2 * world + threadIdx.x];
-    s_src_off[threadIdx.x] = v < max_rows ? v : max_rows;  // never read past the receive buffer
+  if (threadIdx.x < world) {
+    int off = meta[kMetaHead + 2 * world + threadIdx.x], n = meta[kMetaHead + 3 * world + 1 + threadIdx.x];
+    if (off + n > max_rows) n = max_rows > off ? max_rows - off : 0;  // never read past the receive buffer
+    s_src_off[threadIdx.x] = off;
+    s_src_cnt[threadIdx.x] = n > 0 ? n : 0;
+    s_back[threadIdx.x] = meta[kMetaHead + world + threadIdx.x];
   }
-  if (threadIdx.x < world) s_back[threadIdx.x] = meta[kMetaHead + world + threadIdx.x];
   if (threadIdx.x == 0) s_fail = meta[kMetaState] == kStateNoCounts;
   __syncthreads();
   if (threadIdx.x == 0) {
     int run = 0;
     for (int s = 0; s < world; ++s) {
       s_chunk0[s] = run;
-      const int n = s_src_off[s + 1] - s_src_off[s];
-      run += n > 0 ? (n + rows_per_chunk - 1) / rows_per_chunk : 0;
+      run += (s_src_cnt[s] + rows_per_chunk - 1) / rows_per_chunk;
     }
     s_chunk0[world] = run;
   }
@@ -492,7 +601,7 @@ ep_return_bulk_kernel(const uint8_t* __restrict__ rows, const int* __restrict__ 
     s = 0;
     while (s + 1 < world && c >= s_chunk0[s + 1]) ++s;
     r0 = s_src_off[s] + (c - s_chunk0[s]) * rows_per_chunk;
-    n = s_src_off[s + 1] - r0;
+    n = s_src_off[s] + s_src_cnt[s] - r0;
     if (n > rows_per_chunk) n = rows_per_chunk;
   };
   if (lane == 0) {  // a ring is one lane's: one load and one store per chunk
@@ -666,8 +775,13 @@ extern "C" int dice_ep_dispatch_rows(const void* x, const int32_t* pos, const in
                                      const int32_t* meta, const void* const* peer_recv, const void* const* peer_flags,
                                      uint32_t* done_counter, int64_t n_tokens, int k, int hidden, int dtype, int rank,
                                      int world, int n_experts, int capacity_rows, uint32_t seq, int max_ctas,
-                                     uint32_t* status, void* stream) {
-  DICE_CHECK_ARG(n_tokens >= 0 && hidden > 0 && done_counter && meta && seg_offsets, DICE_ERR_ARG);
+                                     int region_rows, const void* const* peer_matrices, uint32_t* status,
+                                     void* stream) {
+  DICE_CHECK_ARG(n_tokens >= 0 && hidden > 0 && done_counter && seg_offsets && region_rows >= 0, DICE_ERR_ARG);
+  DICE_CHECK_ARG(region_rows > 0 || meta != nullptr, DICE_ERR_ARG);
+  DICE_CHECK_ARG(region_rows == 0 || (n_experts <= kMaxKeys && static_cast<int64_t>(world) * region_rows <= capacity_rows &&
+                                      n_tokens * k <= region_rows),
+                 DICE_ERR_SHAPE);
   DICE_CHECK_ARG(k == 1 || k == 2, DICE_ERR_SHAPE);
   DICE_CHECK_ARG(world >= 1 && world <= kMaxRanks && n_experts % world == 0, DICE_ERR_SHAPE);
   const size_t es = dice_dtype_size(dtype);
@@ -679,6 +793,11 @@ extern "C" int dice_ep_dispatch_rows(const void* x, const int32_t* pos, const in
   if (rc != DICE_OK) return rc;
   rc = fill_table(&f, peer_flags, world);
   if (rc != DICE_OK) return rc;
+  PeerTable m = {};
+  if (region_rows > 0) {
+    rc = fill_table(&m, peer_matrices, world);
+    if (rc != DICE_OK) return rc;
+  }
   const int row_vec = static_cast<int>(hidden * es / 16);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int el = n_experts / world;
@@ -698,12 +817,12 @@ extern "C" int dice_ep_dispatch_rows(const void* x, const int32_t* pos, const in
       DICE_CHECK_ARG(bulk_smem_ready(ep_dispatch_bulk_kernel<2>) == DICE_OK, DICE_ERR_CUDA);
       DICE_CUDA_OK(launch_push(ep_dispatch_bulk_kernel<2>, bp.grid, 32u * bp.shape.warps, bulk_smem_bytes(bp.shape), s, bp.pairs,
                                xb, pos, seg_offsets, meta, r, f, done_counter, n_tokens, static_cast<uint32_t>(row_bytes), tpc,
-                               rank, world, el, capacity_rows, seq, status, bp.shape));
+                               rank, world, el, capacity_rows, seq, status, bp.shape, region_rows, m));
     } else {
       DICE_CHECK_ARG(bulk_smem_ready(ep_dispatch_bulk_kernel<1>) == DICE_OK, DICE_ERR_CUDA);
       DICE_CUDA_OK(launch_push(ep_dispatch_bulk_kernel<1>, bp.grid, 32u * bp.shape.warps, bulk_smem_bytes(bp.shape), s, bp.pairs,
                                xb, pos, seg_offsets, meta, r, f, done_counter, n_tokens, static_cast<uint32_t>(row_bytes), tpc,
-                               rank, world, el, capacity_rows, seq, status, bp.shape));
+                               rank, world, el, capacity_rows, seq, status, bp.shape, region_rows, m));
     }
     return DICE_OK;
   }
@@ -714,10 +833,12 @@ extern "C" int dice_ep_dispatch_rows(const void* x, const int32_t* pos, const in
   const dim3 grid(static_cast<unsigned>(blocks));
   if (k == 2)
     DICE_CUDA_OK(dice_launch(ep_dispatch_kernel<2>, grid, dim3(256), 0, s, static_cast<const uint4*>(x), pos, seg_offsets,
-                             meta, r, f, done_counter, n_tokens, row_vec, rank, world, el, capacity_rows, seq, status));
+                             meta, r, f, done_counter, n_tokens, row_vec, rank, world, el, capacity_rows, seq, status,
+                             region_rows, m));
   else
     DICE_CUDA_OK(dice_launch(ep_dispatch_kernel<1>, grid, dim3(256), 0, s, static_cast<const uint4*>(x), pos, seg_offsets,
-                             meta, r, f, done_counter, n_tokens, row_vec, rank, world, el, capacity_rows, seq, status));
+                             meta, r, f, done_counter, n_tokens, row_vec, rank, world, el, capacity_rows, seq, status,
+                             region_rows, m));
   return DICE_OK;
 }
 
@@ -727,6 +848,15 @@ extern "C" int dice_ep_wait_flags(const uint32_t* my_flags, int world, uint32_t 
   const uint32_t code = what == 0 ? DICE_STATUS_WAIT_PEER_DISPATCH : DICE_STATUS_WAIT_PEER_COMBINE;
   DICE_CUDA_OK(dice_launch(ep_wait_kernel, dim3(1), dim3(32), 0, static_cast<cudaStream_t>(stream), my_flags, world, seq,
                            status, code));
+  return DICE_OK;
+}
+
+extern "C" int dice_ep_wait_dispatch(const uint32_t* my_flags, const int32_t* my_matrix, int32_t* meta, int rank, int world,
+                                     int n_experts, int region_rows, uint32_t seq, uint32_t* status, void* stream) {
+  DICE_CHECK_ARG(my_flags && my_matrix && meta && world >= 1 && rank >= 0 && rank < world && region_rows > 0, DICE_ERR_ARG);
+  DICE_CHECK_ARG(world <= kMaxRanks && n_experts <= kMaxKeys && n_experts % world == 0, DICE_ERR_SHAPE);
+  DICE_CUDA_OK(dice_launch(ep_wait_dispatch_kernel, dim3(1), dim3(256), 0, static_cast<cudaStream_t>(stream), my_flags,
+                           my_matrix, meta, rank, world, n_experts, region_rows, seq, status));
   return DICE_OK;
 }
 

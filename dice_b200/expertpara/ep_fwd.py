@@ -218,7 +218,8 @@ def _peer_push(info, async_op, dispatch=None, rows_back=None):
         _lib.check(lib.dice_ep_dispatch_rows(
             inp.data_ptr(), dispatch.pos.data_ptr(), dispatch.seg_offsets.data_ptr(), x._meta_ptrs[slot], tab["recv"],
             tab["f_disp"], x._done_ptrs[2 * slot], inp.shape[0], dispatch.k_eff, inp.shape[1], _dtype_code(inp), x.rank,
-            x.world, x.n_experts, x.min_peer_cap, info.seq, side_ctas, x.status_ptr, stream), "dice_ep_dispatch_rows")
+            x.world, x.n_experts, x.min_peer_cap, info.seq, side_ctas, x.region_rows, tab["matrix"], x.status_ptr, stream),
+            "dice_ep_dispatch_rows")
         out, which = x._recv_views[slot], 0
     else:
         _lib.check(lib.dice_ep_return_rows(
@@ -273,7 +274,7 @@ def proc_experts(inp, experts, token_counts_global, num_local_experts):
         offs = token_counts_global.seg_dev.tolist()  # arbitrary expert modules need the bounds on the host
         outp = torch.empty_like(inp)
         for j, slot in enumerate(seg_slab):
-            if offs[j + 1] > offs[j]:
+            if slot >= 0 and offs[j + 1] > offs[j]:
                 outp[offs[j]:offs[j + 1]] = experts[rank + slot * world_size](inp[offs[j]:offs[j + 1]])
         return outp
     world_size, rank = dist.get_world_size(), dist.get_rank()
@@ -401,14 +402,19 @@ def moe_infer_ep(inp: torch.Tensor, experts: nn.ModuleList, flat_expert_indices,
         # a rendezvous of all ranks, off the main stream: it runs on the side stream in front of the dispatch.
         # Whoever consumes the exchange later waits for the side stream's event and for the sources' flags.
         side = async_op and not diep._forced_sync
-        with _scope("exchange_token_counts"):
-            if side:
-                for t in (seg_offsets, pos, inp):
-                    t.record_stream(xchg._comm)
-            _lib.check(xchg.lib.dice_ep_exchange_counts(
-                seg_offsets.data_ptr(), tab["matrix"], tab["f_cnt"], xchg._meta_ptrs[slot], xchg.rank, xchg.world,
-                xchg.n_experts, xchg.min_peer_cap, seq, xchg.status_ptr, xchg.fork_to_comm() if side else _stream()),
-                "dice_ep_exchange_counts")
+        if xchg.region_rows:
+            # every source owns a fixed region of each receive buffer: no count exchange; the dispatch carries this
+            # rank's counts and the consumer derives its segment table from them (PeerHandle.wait)
+            side = False
+        else:
+            with _scope("exchange_token_counts"):
+                if side:
+                    for t in (seg_offsets, pos, inp):
+                        t.record_stream(xchg._comm)
+                _lib.check(xchg.lib.dice_ep_exchange_counts(
+                    seg_offsets.data_ptr(), tab["matrix"], tab["f_cnt"], xchg._meta_ptrs[slot], xchg.rank, xchg.world,
+                    xchg.n_experts, xchg.min_peer_cap, seq, xchg.status_ptr, xchg.fork_to_comm() if side else _stream()),
+                    "dice_ep_exchange_counts")
         counts_local = None
         counts_global = p2p.SegInfo(xchg, slot, seq, tab, n_tokens * k_eff)
         grouped_dup_inp = p2p.PendingRows(inp, pos, seg_offsets, k_eff, counts_global, on_side=side)

@@ -76,6 +76,10 @@ class PeerExchange:
             fit = int((share / n_slots - self.max_rows * row_bytes) // row_bytes)  # recv + back per slot
             self.capacity_rows = int(min(lossless, max(2 * biggest, fit)))
         self.lossless = self.capacity_rows >= lossless
+        # With room for W x the largest sender, every source gets a fixed region of each receive buffer and the
+        # exchange needs no count rendezvous (csrc/p2p_exchange.cu); otherwise the sources' blocks are packed and
+        # a count exchange tells every source where its block starts.
+        self.region_rows = biggest if (self.lossless and os.environ.get("DICE_EP_P2P_REGIONS", "1") != "0") else 0
 
         w, e = self.world, n_experts
         self.ctrl_stride = ((w * e + _FLAG_PAD - 1) // _FLAG_PAD + 3) * _FLAG_PAD
@@ -142,13 +146,18 @@ class PeerExchange:
         # the smallest receive / return capacity among the peers bounds what this rank may write
         self.min_peer_cap = min(self.peer_cap)
         self.min_peer_rows = min(self.peer_max_rows)
-        a = 3 * self.world + 3  # first of the (source, slot) segment offsets in a meta block
-        self._seg_views = [self.meta[s, a:a + self.world * self.el + 1] for s in range(n_slots)]
+        a = 4 * self.world + 3  # first of the segment offsets in a meta block
+        segs_per_source = self.el + 1 if self.region_rows else self.el
+        self.n_seg = self.world * segs_per_source
+        self._seg_views = [self.meta[s, a:a + self.n_seg + 1] for s in range(n_slots)]
         self._meta_ptrs = [self.meta[s].data_ptr() for s in range(n_slots)]
         self._done_ptrs = [self.done.data_ptr() + 4 * i for i in range(2 * n_slots)]
         self._recv_views = [self.recv[s] for s in range(n_slots)]
         self.status_ptr = self.status.data_ptr()
-        self.seg_slab = [i for _ in range(self.world) for i in range(self.el)]
+        # weight slab of every segment; in the region layout every source's slots are followed by the unused rest
+        # of its region, which has no slab (-1: the GEMM skips it)
+        per_source = list(range(self.el)) + ([-1] if self.region_rows else [])
+        self.seg_slab = [i for _ in range(self.world) for i in per_source]
         self.seg_slab_dev = torch.tensor(self.seg_slab, dtype=torch.int32, device=self.device)
         self._fork = torch.cuda.Event()
         self._side_events = [torch.cuda.Event() for _ in range(2 * n_slots)]
@@ -425,6 +434,14 @@ class PeerHandle:
             from ..ops import current_stream_object
 
             current_stream_object().wait_event(self.event)
+        if self.which == 0 and x.region_rows:
+            # region layout: the wait for the dispatched rows also derives this exchange's meta block from the
+            # counts that came with them
+            slot = self.info.slot
+            _lib.check(x.lib.dice_ep_wait_dispatch(
+                x.my_flags_ptr(slot, 1), x.ctrl.data_ptr() + slot * x.ctrl_stride * 4, x._meta_ptrs[slot], x.rank, x.world,
+                x.n_experts, x.region_rows, self.info.seq, x.status.data_ptr(), _stream()), "dice_ep_wait_dispatch")
+            return
         _lib.check(x.lib.dice_ep_wait_flags(x.my_flags_ptr(self.info.slot, 1 + self.which), x.world, self.info.seq,
                                             self.which, x.status.data_ptr(), _stream()), "dice_ep_wait_flags")
 

@@ -314,7 +314,7 @@ class ExpertPack:
             start.record()
         _lib.check(x.lib.dice_grouped_ffn_return(
             rows.data_ptr(), n_rows, h, ffn, ops.ACT_CODES[act], w1.data_ptr(), w2.data_ptr(), w1.shape[0],
-            info.seg_dev.data_ptr(), x.seg_slab_dev.data_ptr(), x.world * x.el, inter.data_ptr(), x._meta_ptrs[info.slot],
+            info.seg_dev.data_ptr(), x.seg_slab_dev.data_ptr(), x.n_seg, inter.data_ptr(), x._meta_ptrs[info.slot],
             info.tab["back"], info.tab["f_back"], x._done_ptrs[2 * info.slot + 1], x.rank, x.world, x.min_peer_rows,
             info.seq, 0, self.status.data_ptr(), ops._stream()), "dice_grouped_ffn_return")
         if timing is not None:

@@ -315,17 +315,27 @@ DICE_API int dice_grouped_ffn_f32(const void* rows_in, int64_t n_rows, int hidde
  *   of that peer: [0, world) the flags, [32, 32 + world) failure marks (a push
  *   that could not complete writes its sequence number there before raising the
  *   flag; the waiting peer then records "a peer rank reported ...");
- *   meta: int32 [dice_ep_meta_ints(world, n_experts/world)], written by
- *   dice_ep_exchange_counts: total rows received | state (0 ok, 1 a receive
- *   buffer is too small, 2 the peers' counts never arrived) | send_base[W] |
- *   back_base[W] | src_off[W+1] | seg_off[W*El+1] (segments of the receive
- *   buffer in (source, slot) order, ready for dice_grouped_ffn with
- *   seg_slab[s*El+i] = i).  Every rank holds the whole count matrix, so a
- *   receive buffer that is too small ANYWHERE is found by every rank: all of
- *   them record the overflow status and the exchange then moves no rows (the
- *   reference has no capacity and never drops a row: size the buffers so that
- *   this cannot happen, capacity_rows = world * the largest sender is always
- *   enough);
+ *   meta: int32 [dice_ep_meta_ints(world, n_experts/world)]: total rows
+ *   received | state (0 ok, 1 a receive buffer is too small, 2 the peers'
+ *   counts never arrived) | send_base[W] | back_base[W] | src_off[W+1] |
+ *   src_cnt[W] | seg_off[...] (segments of the receive buffer, ready for
+ *   dice_grouped_ffn).
+ *   Two layouts of a receive buffer:
+ *   - packed (region_rows == 0): the sources' blocks follow one another; a
+ *     source learns where its block starts from everyone's counts, so
+ *     dice_ep_exchange_counts (a rendezvous of all ranks) runs first and writes
+ *     meta; W*El segments in (source, slot) order, seg_slab[s*El+i] = i.  Every
+ *     rank holds the whole count matrix, so a receive buffer that is too small
+ *     ANYWHERE is found by every rank: all of them record the overflow status
+ *     and the exchange then moves no rows;
+ *   - regions (region_rows > 0, capacity_rows >= world * region_rows,
+ *     region_rows >= the rows any rank ever sends): source s owns rows
+ *     [s*region_rows, (s+1)*region_rows) of every receive buffer.  No count
+ *     exchange: dice_ep_dispatch_rows publishes this rank's counts with its
+ *     rows, dice_ep_wait_dispatch waits for the sources and derives meta;
+ *     W*(El+1) segments, seg_slab[s*(El+1)+i] = i for i < El and -1 for the
+ *     unused rest of a region (the GEMM skips it).  Like the reference's
+ *     all_to_all, it cannot drop a row;
  *   seq: a number that grows with every use of the same buffers;
  *   done_counter: device uint32, zero before first use, one per call site;
  *   max_ctas selects the form of a push: 0 = the push has the GPU to itself:
@@ -346,7 +356,14 @@ DICE_API int dice_ep_dispatch_rows(const void* x, const int32_t* pos, const int3
                           const int32_t* meta, const void* const* peer_recv,
                           const void* const* peer_flags, uint32_t* done_counter, int64_t n_tokens,
                           int k, int hidden, int dtype, int rank, int world, int n_experts,
-                          int capacity_rows, uint32_t seq, int max_ctas, uint32_t* status, void* stream);
+                          int capacity_rows, uint32_t seq, int max_ctas, int region_rows,
+                          const void* const* peer_matrices, uint32_t* status, void* stream);
+/* region layout: wait (bounded) for every source's rows and failure marks, then
+ * derive `meta` from the count matrix the sources published (my_matrix: this
+ * rank's own [world][n_experts] matrix) */
+DICE_API int dice_ep_wait_dispatch(const uint32_t* my_flags, const int32_t* my_matrix, int32_t* meta, int rank,
+                          int world, int n_experts, int region_rows, uint32_t seq, uint32_t* status,
+                          void* stream);
 /* wait (bounded) until every source raised flag >= seq, then look at the
  * sources' failure marks; what: 0 dispatch, 1 combine */
 DICE_API int dice_ep_wait_flags(const uint32_t* my_flags, int world, uint32_t seq, int what,

@@ -397,7 +397,7 @@ def test_exchange_world_of_one(cuda_device):
         assert lib.dice_ep_exchange_counts(seg.data_ptr(), tab(ctrl.data_ptr()), tab(f(0)), meta.data_ptr(), 0, 1, e, cap,
                                            seq, status.data_ptr(), st) == 0
         assert lib.dice_ep_dispatch_rows(x.data_ptr(), pos.data_ptr(), seg.data_ptr(), meta.data_ptr(), tab(recv.data_ptr()),
-                                         tab(f(1)), done.data_ptr(), n, 2, h, 0, 0, 1, e, cap, seq, 7 * (seq - 1), status.data_ptr(), st) == 0
+                                         tab(f(1)), done.data_ptr(), n, 2, h, 0, 0, 1, e, cap, seq, 7 * (seq - 1), 0, None, status.data_ptr(), st) == 0
         assert lib.dice_ep_wait_flags(f(1), 1, seq, 0, status.data_ptr(), st) == 0
         assert lib.dice_ep_return_rows(recv.data_ptr(), meta.data_ptr(), tab(back.data_ptr()), tab(f(2)), done[1:].data_ptr(),
                                        h, 0, 0, 1, 2 * n, cap, seq, 5 * (seq - 1), status.data_ptr(), st) == 0
@@ -409,8 +409,8 @@ def test_exchange_world_of_one(cuda_device):
         assert bool((recv[2 * n:] == 3.0).all())
         m = meta.cpu().tolist()
         assert m[0] == 2 * n and m[1] == 0                                # rows received, state
-        assert m[2] == 0 and m[3] == 0 and m[4:6] == [0, 2 * n]           # send_base, back_base, src_off
-        assert m[6:6 + e + 1] == seg.cpu().tolist()
+        assert m[2] == 0 and m[3] == 0 and m[4:6] == [0, 2 * n] and m[6] == 2 * n   # send_base, back_base, src_off, src_cnt
+        assert m[7:7 + e + 1] == seg.cpu().tolist()
     # a receive buffer that is too small is reported, not overrun
     assert lib.dice_ep_exchange_counts(seg.data_ptr(), tab(ctrl.data_ptr()), tab(f(0)), meta.data_ptr(), 0, 1, e, 100, 3,
                                        status.data_ptr(), st) == 0
@@ -460,7 +460,7 @@ def test_exchange_bulk_copy_pushes_equal_simt_pushes(cuda_device, n, h, k, dtype
                                                cap, seq, status.data_ptr(), st) == 0
             assert lib.dice_ep_dispatch_rows(x.data_ptr(), pos.data_ptr(), seg.data_ptr(), meta.data_ptr(),
                                              tab(recv.data_ptr()), tab(f(1)), done.data_ptr(), n, k, h, code, 0, 1, e, cap,
-                                             seq, max_ctas, status.data_ptr(), st) == 0
+                                             seq, max_ctas, 0, None, status.data_ptr(), st) == 0
             assert lib.dice_ep_wait_flags(f(1), 1, seq, 0, status.data_ptr(), st) == 0
             assert lib.dice_ep_return_rows(recv.data_ptr(), meta.data_ptr(), tab(back.data_ptr()), tab(f(2)),
                                            done[1:].data_ptr(), h, code, 0, 1, cap, cap, seq, max_ctas, status.data_ptr(),
@@ -535,7 +535,7 @@ def test_exchange_of_emulated_ranks_on_one_gpu(cuda_device, world, max_ctas):
     for r in range(world):
         assert lib.dice_ep_dispatch_rows(xs[r].data_ptr(), poss[r].data_ptr(), segs[r].data_ptr(), meta[r].data_ptr(),
                                          table([t.data_ptr() for t in recv]), flags(1), done[r].data_ptr(), n[r], k, h, 0,
-                                         r, world, e, cap, seq, max_ctas, status.data_ptr(), st) == 0
+                                         r, world, e, cap, seq, max_ctas, 0, None, status.data_ptr(), st) == 0
     for r in range(world):
         assert lib.dice_ep_wait_flags(my_flags(r, 1), world, seq, 0, status.data_ptr(), st) == 0
     for r in range(world):  # identity FFN: the received rows go straight back
@@ -635,7 +635,7 @@ def test_exchange_overflow_is_found_by_every_rank_and_touches_nothing(cuda_devic
     for r in range(world):
         assert lib.dice_ep_dispatch_rows(xs[r].data_ptr(), poss[r].data_ptr(), segs[r].data_ptr(), R.meta[r].data_ptr(),
                                          R.table([t.data_ptr() for t in R.recv]), R.flags(1), R.done[r].data_ptr(), n[r], k,
-                                         h, 0, r, world, e, cap, seq, max_ctas, R.status[r].data_ptr(), st) == 0
+                                         h, 0, r, world, e, cap, seq, max_ctas, 0, None, R.status[r].data_ptr(), st) == 0
     for r in range(world):
         assert lib.dice_ep_wait_flags(R.my_flags(r, 1), world, seq, 0, R.status[r].data_ptr(), st) == 0
     for r in range(world):
@@ -648,7 +648,7 @@ def test_exchange_overflow_is_found_by_every_rank_and_touches_nothing(cuda_devic
     for r in range(world):
         m = R.meta[r].cpu().tolist()
         assert m[0] == 0 and m[1] == 1, f"rank {r}: meta head {m[:2]}"                  # no rows, state = overflow
-        assert all(v == 0 for v in m[2 + 3 * world + 1:]), "segments must be empty"
+        assert all(v == 0 for v in m[2 + 4 * world + 1:2 + 4 * world + 1 + e + 1]), "segments must be empty"
         with pytest.raises(RuntimeError, match="more rows"):
             ops.check_status(R.status[r])
         assert bool((R.recv[r] == 3.0).all()) and bool((R.back[r] == 5.0).all()), f"rank {r}: a buffer was written"
@@ -681,7 +681,7 @@ def test_exchange_of_skewed_routing_with_lossless_capacity(cuda_device, max_ctas
     for r in range(world):
         assert lib.dice_ep_dispatch_rows(xs[r].data_ptr(), poss[r].data_ptr(), segs[r].data_ptr(), R.meta[r].data_ptr(),
                                          R.table([t.data_ptr() for t in R.recv]), R.flags(1), R.done[r].data_ptr(), n[r], k,
-                                         h, 0, r, world, e, cap, seq, max_ctas, R.status[r].data_ptr(), st) == 0
+                                         h, 0, r, world, e, cap, seq, max_ctas, 0, None, R.status[r].data_ptr(), st) == 0
     for r in range(world):
         assert lib.dice_ep_wait_flags(R.my_flags(r, 1), world, seq, 0, R.status[r].data_ptr(), st) == 0
     for r in range(world):
@@ -697,6 +697,91 @@ def test_exchange_of_skewed_routing_with_lossless_capacity(cuda_device, max_ctas
         want = ops.permute_rows(xs[r], poss[r], k)
         assert torch.equal(R.back[r][: k * n[r]], want), f"rank {r} did not get its rows back"
         assert bool((R.back[r][k * n[r]:] == 5.0).all()) and bool((R.recv[r][recv_rows[r]:] == 3.0).all())
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+@pytest.mark.parametrize("max_ctas", [0, -1, 4])
+def test_exchange_in_the_region_layout(cuda_device, world, max_ctas):
+    """The exchange without a count rendezvous: every source owns a fixed region of each receive buffer, the
+    dispatch publishes the source's counts with its rows, and dice_ep_wait_dispatch derives the receiver's segment
+    table (with a slab-less segment for the unused rest of every region).  Skewed routing (three quarters of the
+    rows to one rank) on `world` ranks whose buffers share this GPU; identity FFN: every rank gets its own rows
+    back, every region holds its source's rows in slot order, nothing else is touched.  Twice on the same buffers."""
+    from dice_b200 import _lib
+
+    ops = _ops()
+    lib = _lib.load()
+    e, h, k = 8, 128, 2
+    el = e // world
+    n = [150 + 13 * r for r in range(world)]
+    region = k * max(n)
+    cap = world * region
+    R = _EmulatedRanks(world, e, h, cap, region, cuda_device, lib)
+    st = torch.cuda.current_stream().cuda_stream
+    matrices = R.table([c.data_ptr() for c in R.ctrl])
+    for seq in (1, 2):
+        xs, poss, segs = _emulated_inputs(world, e, h, n, k, cuda_device, seed=40 + seq, hot_owner=world - 1)
+        seg_host = [s.cpu().tolist() for s in segs]
+        for r in range(world):
+            assert lib.dice_ep_dispatch_rows(xs[r].data_ptr(), poss[r].data_ptr(), segs[r].data_ptr(), None,
+                                             R.table([t.data_ptr() for t in R.recv]), R.flags(1), R.done[r].data_ptr(), n[r],
+                                             k, h, 0, r, world, e, cap, seq, max_ctas, region, matrices,
+                                             R.status[r].data_ptr(), st) == 0
+        for r in range(world):
+            assert lib.dice_ep_wait_dispatch(R.my_flags(r, 1), R.ctrl[r].data_ptr(), R.meta[r].data_ptr(), r, world, e, region,
+                                             seq, R.status[r].data_ptr(), st) == 0
+        for r in range(world):  # identity FFN: the received rows go straight back
+            assert lib.dice_ep_return_rows(R.recv[r].data_ptr(), R.meta[r].data_ptr(), R.table([t.data_ptr() for t in R.back]),
+                                           R.flags(2), R.done[r][1:].data_ptr(), h, 0, r, world, R.back_cap, cap, seq, max_ctas,
+                                           R.status[r].data_ptr(), st) == 0
+        for r in range(world):
+            assert lib.dice_ep_wait_flags(R.my_flags(r, 2), world, seq, 1, R.status[r].data_ptr(), st) == 0
+        torch.cuda.synchronize()
+        sorted_rows = [ops.permute_rows(xs[r], poss[r], k) for r in range(world)]
+        for r in range(world):
+            ops.check_status(R.status[r])
+            assert torch.equal(R.back[r][: k * n[r]], sorted_rows[r]), f"rank {r} did not get its rows back"
+            assert bool((R.back[r][k * n[r]:] == 5.0).all())
+        for d in range(world):
+            m = R.meta[d].cpu().tolist()
+            seg_off = m[2 + 4 * world + 1: 2 + 4 * world + 1 + world * (el + 1) + 1]
+            got_total = 0
+            for s in range(world):
+                lo, hi = seg_host[s][d * el], seg_host[s][(d + 1) * el]
+                want = sorted_rows[s][lo:hi]
+                assert torch.equal(R.recv[d][s * region: s * region + hi - lo], want), f"region of source {s} at rank {d}"
+                # segments of source s: its slots, then the rest of the region
+                slots = [seg_host[s][d * el + i] - lo + s * region for i in range(el + 1)]
+                assert seg_off[s * (el + 1): s * (el + 1) + el + 1] == slots
+                assert m[2 + 2 * world + s] == s * region and m[2 + 3 * world + 1 + s] == hi - lo   # src_off, src_cnt
+                got_total += hi - lo
+            assert seg_off[-1] == cap and m[0] == got_total and m[1] == 0
+            assert bool((R.recv[d][cap:] == 3.0).all())
+
+
+def test_grouped_gemm_skips_segments_without_a_slab(cuda_device):
+    """Segments whose weight slab is -1 (the unused rest of a source's region in the region layout) produce no
+    tiles: their output rows stay untouched."""
+    ops = _ops()
+    g = torch.Generator().manual_seed(77)
+    counts, slabs = [100, 300, 0, 140, 260, 50], [0, -1, 1, -1, 1, -1]
+    r, k, n = sum(counts), 64, 96
+    a = torch.randn(r, k, generator=g).bfloat16()
+    w = (torch.randn(2, n, k, generator=g) / 8).bfloat16()
+    seg = _segments(counts, cuda_device)
+    status = torch.zeros(1, dtype=torch.int32, device=cuda_device)
+    out = torch.full((r, n), 7.0, dtype=torch.bfloat16, device=cuda_device)
+    ops.grouped_gemm(a.to(cuda_device), w.to(cuda_device), seg, ops.EPI_STORE, n, status,
+                     seg_slab=torch.tensor(slabs, dtype=torch.int32, device=cuda_device), out=out)
+    torch.cuda.synchronize()
+    ops.check_status(status)
+    offs = seg.cpu().tolist()
+    for s, slab in enumerate(slabs):
+        got = out[offs[s]:offs[s + 1]].cpu().float()
+        if slab < 0:
+            assert bool((got == 7.0).all())
+        elif counts[s]:
+            torch.testing.assert_close(got, a[offs[s]:offs[s + 1]].float() @ w[slab].float().t(), rtol=2e-2, atol=2e-2)
 
 
 @pytest.mark.parametrize("max_ctas", [0, -1])
@@ -723,7 +808,7 @@ def test_exchange_failure_reaches_the_peers(cuda_device, max_ctas):
                                        R.meta[0].data_ptr(), 0, world, e, R.cap, seq, R.status[0].data_ptr(), st) == 0
     assert lib.dice_ep_dispatch_rows(xs[0].data_ptr(), poss[0].data_ptr(), segs[0].data_ptr(), R.meta[0].data_ptr(),
                                      R.table([t.data_ptr() for t in R.recv]), R.flags(1), R.done[0].data_ptr(), n[0], k, h, 0,
-                                     0, world, e, R.cap, seq, max_ctas, R.status[0].data_ptr(), st) == 0
+                                     0, world, e, R.cap, seq, max_ctas, 0, None, R.status[0].data_ptr(), st) == 0
     # rank 1's own push is played by hand: its dispatch flag on rank 1 is up, so that only rank 0's mark matters
     R.ctrl[1][R.flag_base + 64 + 1] = seq
     assert lib.dice_ep_wait_flags(R.my_flags(1, 1), world, seq, 0, R.status[1].data_ptr(), st) == 0
@@ -744,7 +829,7 @@ def test_exchange_failure_reaches_the_peers(cuda_device, max_ctas):
     for r in range(world):
         assert lib.dice_ep_dispatch_rows(xs[r].data_ptr(), poss[r].data_ptr(), segs[r].data_ptr(), R.meta[r].data_ptr(),
                                          R.table([t.data_ptr() for t in R.recv]), R.flags(1), R.done[r].data_ptr(), n[r], k,
-                                         h, 0, r, world, e, R.cap, seq, max_ctas, R.status[r].data_ptr(), st) == 0
+                                         h, 0, r, world, e, R.cap, seq, max_ctas, 0, None, R.status[r].data_ptr(), st) == 0
     for r in range(world):
         assert lib.dice_ep_wait_flags(R.my_flags(r, 1), world, seq, 0, R.status[r].data_ptr(), st) == 0
     torch.cuda.synchronize()
@@ -818,7 +903,7 @@ def test_ffn_with_fused_return_world_of_one(cuda_device):
         back.zero_()
         assert lib.dice_ep_exchange_counts(seg.data_ptr(), tab(ctrl.data_ptr()), tab(f_cnt), meta.data_ptr(), 0, 1, e,
                                            2 * n, seq, status.data_ptr(), st) == 0
-        seg_dev = meta[6:6 + e + 1]
+        seg_dev = meta[7:7 + e + 1]
         assert lib.dice_grouped_ffn_return(rows.data_ptr(), 2 * n, h, f, 0, w1.data_ptr(), w2.data_ptr(), e,
                                            seg_dev.data_ptr(), slab.data_ptr(), e, inter.data_ptr(), meta.data_ptr(),
                                            tab(back.data_ptr()), tab(f_back), done[1:].data_ptr(), 0, 1, 2 * n, seq, 0,
