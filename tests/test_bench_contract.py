@@ -26,3 +26,21 @@ def test_other_ranks_of_the_reference_arm_do_nothing():
     r = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--gpus", "2"],
                        capture_output=True, text=True, timeout=120, env=env)
     assert r.returncode == 0 and r.stdout.strip() == ""
+
+
+def test_bench_helpers_are_deterministic():
+    """Every parameter is drawn from its own (layer, name) seed, so a trimmed expert-parallel block and an unsharded
+    block hold the same values; the Zipf routing option parses as documented."""
+    import importlib.util
+
+    spec = importlib.util.spec_from_file_location("bench_under_test", os.path.join(ROOT, "bench.py"))
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    assert bench._param_seed(0, 3, "experts.5.fc1.weight") == bench._param_seed(0, 3, "experts.5.fc1.weight")
+    assert bench._param_seed(0, 3, "experts.5.fc1.weight") != bench._param_seed(0, 4, "experts.5.fc1.weight")
+    assert bench._param_seed(0, 3, "experts.5.fc1.weight") != bench._param_seed(0, 3, "experts.6.fc1.weight")
+    assert bench.zipf_route("router") is None
+    assert bench.zipf_route("zipf:1.2") == (1.2, 1.0) and bench.zipf_route("zipf:1.2:0.5") == (1.2, 0.5)
+    # algorithmic FLOPs of one FFN call: 2 rows per token x 4 h F (GELU), plus the shared expert in the SwiGLU variant
+    assert bench.ffn_flops(16384, "gelu_tanh") == 2 * 16384 * 4 * 1152 * 4608
+    assert bench.ffn_flops(16384, "swiglu") == 2 * 16384 * 6 * 1152 * 4608 + 16384 * 6 * 1152 * 2304
