@@ -54,7 +54,7 @@ SIGNATURES = {
     "dice_grouped_ffn": (
         c_int,
         [c_void_p, c_int64, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p,
-         c_void_p, c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p],
+         c_void_p, c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p],
     ),
     "dice_grouped_ffn_combine": (
         c_int,
@@ -79,6 +79,10 @@ SIGNATURES = {
         c_int,
         [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_uint32, c_int,
          c_void_p, c_void_p]),
+    "dice_ep_return_rows_following": (
+        c_int,
+        [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_uint32, c_int,
+         c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p]),
     "dice_grouped_ffn_return": (
         c_int,
         [c_void_p, c_int64, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p,

@@ -47,6 +47,7 @@ extern "C" const char* dice_status_message(uint32_t status) {
     case DICE_STATUS_WAIT_PEER_COMBINE: return "timed out waiting for a peer rank's expert outputs";
     case DICE_STATUS_EXCHANGE_OVERFLOW: return "a rank received more rows than its exchange buffer holds";
     case DICE_STATUS_PEER_FAILED: return "a peer rank reported that the rows it sent are incomplete";
+    case DICE_STATUS_WAIT_FFN_ROWS: return "timed out waiting for the expert outputs that a return push follows";
     default: return "unknown device status";
   }
 }

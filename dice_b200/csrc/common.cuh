@@ -28,6 +28,7 @@
 #define DICE_STATUS_WAIT_PEER_COMBINE 8u   // exchange: a peer's expert outputs never arrived
 #define DICE_STATUS_EXCHANGE_OVERFLOW 9u   // exchange: more rows than the receive buffer holds
 #define DICE_STATUS_PEER_FAILED 10u        // exchange: a source rank marked its push as incomplete
+#define DICE_STATUS_WAIT_FFN_ROWS 11u      // exchange: the expert outputs a return push follows never completed
 
 static inline bool dice_aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
@@ -122,4 +123,6 @@ int dice_internal_gemm_pair(const void* a, int64_t n_rows, int k_dim, const void
                             const int32_t* seg_offsets, const int32_t* seg_slab, int n_seg, int epilogue, void* out,
                             int64_t ld_out, int n_out, int reserve_sms, uint32_t* status, cudaStream_t stream,
                             const DiceReturnSpec* ret = nullptr, const DiceDenseSpec* extra = nullptr,
-                            const DiceCombineSpec* combine = nullptr);
+                            const DiceCombineSpec* combine = nullptr, uint32_t* rows_done = nullptr);
+// completions the CTA-pair kernel counts per 256-row block and output tile when rows_done is given
+constexpr int kRowsDonePerTile = 16;  // 2 CTAs x 8 epilogue warps

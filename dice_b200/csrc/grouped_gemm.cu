@@ -508,9 +508,12 @@ extern "C" int dice_grouped_ffn(const void* rows_in, int64_t n_rows, int hidden,
                                 const void* w2, int n_slabs, const int32_t* seg_offsets, const int32_t* seg_slab,
                                 int n_seg, void* inter, void* rows_out, const void* shared_in, int64_t n_shared,
                                 int shared_ffn, const void* shared_w1, const void* shared_w2, void* shared_inter,
-                                void* shared_out, int reserve_sms, uint32_t* status, void* stream) {
+                                void* shared_out, int reserve_sms, uint32_t* rows_done, uint32_t* status,
+                                void* stream) {
   DICE_CHECK_ARG(act == DICE_ACT_SWIGLU || act == DICE_ACT_GELU_TANH, DICE_ERR_ARG);
   DICE_CHECK_ARG(hidden > 0 && ffn > 0 && reserve_sms >= 0, DICE_ERR_ARG);
+  // counting finished blocks of the output is the CTA-pair kernel's; a caller that asked for it waits on the counters
+  if (rows_done != nullptr) DICE_CHECK_ARG(use_cta_pairs() && n_rows > 0 && n_seg > 0, DICE_ERR_ARG);
   if (n_rows > 0 && n_seg > 0) DICE_CHECK_ARG(inter != nullptr, DICE_ERR_ARG);
   const int epi1 = act == DICE_ACT_SWIGLU ? DICE_EPI_SWIGLU : DICE_EPI_GELU_TANH;
   const int64_t w1_rows = act == DICE_ACT_SWIGLU ? dice_w13_rows(ffn) : ffn;
@@ -518,6 +521,13 @@ extern "C" int dice_grouped_ffn(const void* rows_in, int64_t n_rows, int hidden,
     int rc = dice_grouped_gemm(rows_in, n_rows, hidden, w1, n_slabs, w1_rows, seg_offsets, seg_slab, n_seg, epi1, inter,
                                ffn, ffn, reserve_sms, status, stream);
     if (rc != DICE_OK) return rc;
+    if (rows_done != nullptr) {
+      DICE_CHECK_ARG(n_seg <= kMaxSeg && n_rows < 0x7fffff00LL && hidden % 8 == 0 && ffn % 8 == 0, DICE_ERR_LIMIT);
+      DICE_CHECK_ARG(w2 && rows_out && dice_aligned16(w2) && dice_aligned16(rows_out), DICE_ERR_ALIGN);
+      return dice_internal_gemm_pair(inter, n_rows, ffn, w2, n_slabs, hidden, seg_offsets, seg_slab, n_seg, DICE_EPI_STORE,
+                                     rows_out, hidden, hidden, reserve_sms, status, static_cast<cudaStream_t>(stream),
+                                     nullptr, nullptr, nullptr, rows_done);
+    }
     return dice_grouped_gemm(inter, n_rows, ffn, w2, n_slabs, hidden, seg_offsets, seg_slab, n_seg, DICE_EPI_STORE,
                              rows_out, hidden, hidden, reserve_sms, status, stream);
   }
@@ -550,7 +560,7 @@ extern "C" int dice_grouped_ffn(const void* rows_in, int64_t n_rows, int hidden,
   if (rc != DICE_OK) return rc;
   DiceDenseSpec x2 = {shared_inter, n_shared, shared_ffn, shared_w2, hidden, shared_out, hidden, hidden};
   return dice_internal_gemm_pair(inter, n_rows, ffn, w2, n_slabs, hidden, seg_offsets, seg_slab, n_seg, DICE_EPI_STORE,
-                                 rows_out, hidden, hidden, reserve_sms, status, s, nullptr, &x2);
+                                 rows_out, hidden, hidden, reserve_sms, status, s, nullptr, &x2, nullptr, rows_done);
 }
 
 // The expert FFN whose second GEMM scales every row by its gate weight and adds it to its token's row

@@ -379,6 +379,11 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
           staged_store(v, col0 + c, n_valid - c);
         }
       }
+      if (p.rows_done != nullptr && ti.g == 0) {
+        __threadfence();  // every lane's stores of this tile are visible device-wide before the block is counted
+        __syncwarp();
+        if (lane == 0) atomicAdd(&p.rows_done[t / p.n_nblk], 1u);
+      }
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(map_to_cta(acc_empty_bar + 8 * acc, 0));
@@ -452,7 +457,8 @@ int resident_pairs() {
 int dice_internal_gemm_pair(const void* a, int64_t n_rows, int k_dim, const void* w, int n_slabs, int64_t w_rows,
                             const int32_t* seg_offsets, const int32_t* seg_slab, int n_seg, int epilogue, void* out,
                             int64_t ld_out, int n_out, int reserve_sms, uint32_t* status, cudaStream_t stream,
-                            const DiceReturnSpec* ret, const DiceDenseSpec* extra, const DiceCombineSpec* combine) {
+                            const DiceReturnSpec* ret, const DiceDenseSpec* extra, const DiceCombineSpec* combine,
+                            uint32_t* rows_done) {
   int pairs = resident_pairs();
   if (pairs <= 0) return DICE_ERR_CUDA;
   // SM pairs left to kernels of other streams (the side-stream pushes of the asynchronous exchange)
@@ -498,6 +504,7 @@ int dice_internal_gemm_pair(const void* a, int64_t n_rows, int k_dim, const void
   p.status = status;
   p.b_box_rows = 128;
   p.n_stages = kPairStages;
+  p.rows_done = rows_done;
   if (combine != nullptr) {
     if (epilogue != DICE_EPI_STORE || ret != nullptr || extra != nullptr || !combine->order || !combine->weights)
       return DICE_ERR_ARG;

@@ -203,7 +203,8 @@ ep_counts_kernel(const int* __restrict__ seg_offsets,  // [E+1] this rank's key-
 // non-zero when this CTA could not complete its part) is collected over the grid in the upper half of the
 // counter; the last CTA then writes the failure marks before it raises the flags.  Grids stay below 65536 CTAs.
 __device__ __forceinline__ void signal_when_grid_done(unsigned int* done_counter, PeerTable flags, int rank, int world,
-                                                      uint32_t seq, const int* fail) {
+                                                      uint32_t seq, const int* fail, unsigned int* clear = nullptr,
+                                                      int clear_ints = 0) {
   __threadfence_system();
   __syncthreads();
   __shared__ int s_last, s_any_fail;
@@ -215,6 +216,8 @@ __device__ __forceinline__ void signal_when_grid_done(unsigned int* done_counter
   }
   __syncthreads();
   if (s_last) {
+    // counters that this grid consumed (the blocks of a GEMM output it followed) start from zero next time
+    for (int i = threadIdx.x; i < clear_ints; i += blockDim.x) clear[i] = 0u;
     __threadfence_system();
     if (threadIdx.x < world) {
       uint32_t* f = static_cast<uint32_t*>(flags.ptr[threadIdx.x]);
@@ -552,10 +555,27 @@ ep_dispatch_bulk_kernel(const uint8_t* __restrict__ x, const int* __restrict__ p
   signal_when_grid_done(done_counter, flags, rank, world, seq, &s_fail);
 }
 
+// What a return push needs to FOLLOW a running second GEMM: the GEMM counts, per 256-row block of its tile list, the
+// epilogue warps that have stored a tile (rows_done); a block is complete at `target`.  The push derives the same
+// block numbering from the segment table, waits (bounded) for the blocks a chunk of rows lies in, and only then
+// copies the chunk; when the grid is done its last CTA clears the counters for the next use.
+struct FollowSpec {
+  unsigned int* rows_done;  // null: the rows are complete when the kernel starts
+  unsigned int target;
+  int n_ints;               // entries of rows_done
+  const int* seg_slab;
+  int n_seg;
+};
+constexpr int kMaxFollowSeg = 288;
+constexpr int kFollowRowsPerBlock = 256;  // rows per tile pair of the CTA-pair GEMM
+
 __global__ void __launch_bounds__(32 * kBulkMaxWarps)
 ep_return_bulk_kernel(const uint8_t* __restrict__ rows, const int* __restrict__ meta, PeerTable back_bufs, PeerTable flags,
                       unsigned int* done_counter, uint32_t row_bytes, int rows_per_chunk, int rank, int world,
-                      int back_capacity_rows, int max_rows, uint32_t seq, uint32_t* status, BulkShape shape) {
+                      int back_capacity_rows, int max_rows, uint32_t seq, uint32_t* status, BulkShape shape,
+                      FollowSpec follow) {
+  __shared__ int s_fseg[kMaxFollowSeg + 1];  // segment offsets of the receive buffer
+  __shared__ int s_fmb[kMaxFollowSeg + 1];   // 256-row blocks in front of segment g (-1 in the table: no weights)
   extern __shared__ __align__(128) uint8_t bulk_bufs[];
   __shared__ __align__(8) uint64_t bars_all[kBulkMaxWarps][kBulkMaxBufs];
   __shared__ int s_src_off[kMaxRanks];
@@ -580,6 +600,10 @@ ep_return_bulk_kernel(const uint8_t* __restrict__ rows, const int* __restrict__ 
     s_back[threadIdx.x] = meta[kMetaHead + world + threadIdx.x];
   }
   if (threadIdx.x == 0) s_fail = meta[kMetaState] == kStateNoCounts;
+  if (follow.rows_done != nullptr) {
+    const int* seg_off = meta + meta_seg_base(world);
+    for (int g = threadIdx.x; g <= follow.n_seg; g += blockDim.x) s_fseg[g] = seg_off[g];
+  }
   __syncthreads();
   if (threadIdx.x == 0) {
     int run = 0;
@@ -588,8 +612,45 @@ ep_return_bulk_kernel(const uint8_t* __restrict__ rows, const int* __restrict__ 
       run += (s_src_cnt[s] + rows_per_chunk - 1) / rows_per_chunk;
     }
     s_chunk0[world] = run;
+    if (follow.rows_done != nullptr) {  // the GEMM's numbering of 256-row blocks (grouped_gemm_pair.cu)
+      int mb = 0;
+      for (int g = 0; g < follow.n_seg; ++g) {
+        const int cnt = s_fseg[g + 1] - s_fseg[g];
+        const bool has_weights = follow.seg_slab == nullptr || follow.seg_slab[g] >= 0;
+        s_fmb[g] = has_weights ? mb : -1;
+        if (cnt > 0 && has_weights) mb += (cnt + kFollowRowsPerBlock - 1) / kFollowRowsPerBlock;
+      }
+    }
   }
   __syncthreads();
+  // rows [r0, r0 + n) of source s are final once every block of the GEMM's output that they touch is complete
+  const int segs_per_source = follow.rows_done != nullptr ? follow.n_seg / world : 0;
+  auto rows_ready = [&](int s, int r0, int n) -> bool {
+    for (int g = s * segs_per_source; g < (s + 1) * segs_per_source; ++g) {
+      if (s_fmb[g] < 0) continue;
+      const int lo = r0 > s_fseg[g] ? r0 : s_fseg[g];
+      const int hi = r0 + n < s_fseg[g + 1] ? r0 + n : s_fseg[g + 1];
+      if (lo >= hi) continue;
+      const int b0 = s_fmb[g] + (lo - s_fseg[g]) / kFollowRowsPerBlock;
+      const int b1 = s_fmb[g] + (hi - 1 - s_fseg[g]) / kFollowRowsPerBlock;
+      for (int b = b0; b <= b1; ++b) {
+        if (b >= follow.n_ints) return false;
+        const uint64_t t0 = timer_ns();
+        uint32_t spins = 0;
+        for (;;) {
+          unsigned int v;
+          asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(follow.rows_done + b) : "memory");
+          if (v >= follow.target) break;
+          if ((++spins & 63u) == 0) {
+            if (timer_ns() - t0 > kPeerWaitLimitNs) return false;
+            __nanosleep(100);
+          }
+        }
+      }
+    }
+    asm volatile("fence.proxy.async;" ::: "memory");  // the copy unit reads what the GEMM's epilogue stored
+    return true;
+  };
   const int64_t worker = static_cast<int64_t>(blockIdx.x) * shape.warps + warp;
   const int64_t n_workers = static_cast<int64_t>(gridDim.x) * shape.warps;
   const int64_t n_chunks = s_chunk0[world];
@@ -610,6 +671,12 @@ ep_return_bulk_kernel(const uint8_t* __restrict__ rows, const int* __restrict__ 
         if (j >= bufs) bulk_wait_read_1();
         int s, r0, n;
         locate(j, s, r0, n);
+        if (follow.rows_done != nullptr && !rows_ready(s, r0, n)) {
+          if (status != nullptr) atomicCAS(status, 0u, DICE_STATUS_WAIT_FFN_ROWS);
+          atomicExch(&s_fail, 1);
+          bulk_settle(bars, bufs, j - lag - 1, j - 1);
+          break;
+        }
         const int b = static_cast<int>(j % bufs);
         bulk_load(buf0 + b * shape.buf_bytes, rows + static_cast<int64_t>(r0) * row_bytes, static_cast<uint32_t>(n) * row_bytes,
                   smem_addr32(&bars[b]));
@@ -639,7 +706,7 @@ ep_return_bulk_kernel(const uint8_t* __restrict__ rows, const int* __restrict__ 
     bulk_drain();
   }
   __syncwarp();
-  signal_when_grid_done(done_counter, flags, rank, world, seq, &s_fail);
+  signal_when_grid_done(done_counter, flags, rank, world, seq, &s_fail, follow.rows_done, follow.n_ints);
 }
 
 // DICE_EP_P2P_BULK=0 keeps the SIMT pushes everywhere
@@ -860,10 +927,10 @@ extern "C" int dice_ep_wait_dispatch(const uint32_t* my_flags, const int32_t* my
   return DICE_OK;
 }
 
-extern "C" int dice_ep_return_rows(const void* rows, const int32_t* meta, const void* const* peer_back,
-                                   const void* const* peer_flags, uint32_t* done_counter, int hidden, int dtype,
-                                   int rank, int world, int back_capacity_rows, int max_rows, uint32_t seq,
-                                   int max_ctas, uint32_t* status, void* stream) {
+namespace {
+int return_rows(const void* rows, const int32_t* meta, const void* const* peer_back, const void* const* peer_flags,
+                uint32_t* done_counter, int hidden, int dtype, int rank, int world, int back_capacity_rows, int max_rows,
+                uint32_t seq, int max_ctas, uint32_t* status, void* stream, const FollowSpec& follow) {
   DICE_CHECK_ARG(rows && meta && done_counter && hidden > 0 && max_rows >= 0, DICE_ERR_ARG);
   DICE_CHECK_ARG(world >= 1 && world <= kMaxRanks, DICE_ERR_SHAPE);
   const size_t es = dice_dtype_size(dtype);
@@ -887,9 +954,10 @@ extern "C" int dice_ep_return_rows(const void* rows, const int32_t* meta, const 
     DICE_CUDA_OK(launch_push(ep_return_bulk_kernel, bp.grid, 32u * bp.shape.warps, bulk_smem_bytes(bp.shape),
                              static_cast<cudaStream_t>(stream), bp.pairs, static_cast<const uint8_t*>(rows), meta, b, f,
                              done_counter, static_cast<uint32_t>(row_bytes), max_ctas == 0 ? rpc_alone : rpc_beside, rank, world,
-                             back_capacity_rows, max_rows, seq, status, bp.shape));
+                             back_capacity_rows, max_rows, seq, status, bp.shape, follow));
     return DICE_OK;
   }
+  DICE_CHECK_ARG(follow.rows_done == nullptr, DICE_ERR_SHAPE);  // only the bulk-copy push can follow a GEMM
   int64_t blocks = (static_cast<int64_t>(max_rows) + 7) / 8;
   if (blocks < 1) blocks = 1;
   if (blocks > sms * 16) blocks = sms * 16;  // grid-stride over the rows actually received
@@ -898,6 +966,30 @@ extern "C" int dice_ep_return_rows(const void* rows, const int32_t* meta, const 
                            static_cast<cudaStream_t>(stream), static_cast<const uint4*>(rows), meta, b, f, done_counter,
                            row_vec, rank, world, back_capacity_rows, max_rows, seq, status));
   return DICE_OK;
+}
+}  // namespace
+
+extern "C" int dice_ep_return_rows(const void* rows, const int32_t* meta, const void* const* peer_back,
+                                   const void* const* peer_flags, uint32_t* done_counter, int hidden, int dtype,
+                                   int rank, int world, int back_capacity_rows, int max_rows, uint32_t seq,
+                                   int max_ctas, uint32_t* status, void* stream) {
+  const FollowSpec none = {nullptr, 0u, 0, nullptr, 0};
+  return return_rows(rows, meta, peer_back, peer_flags, done_counter, hidden, dtype, rank, world, back_capacity_rows,
+                     max_rows, seq, max_ctas, status, stream, none);
+}
+
+extern "C" int dice_ep_return_rows_following(const void* rows, const int32_t* meta, const void* const* peer_back,
+                                             const void* const* peer_flags, uint32_t* done_counter, int hidden,
+                                             int rank, int world, int back_capacity_rows, int max_rows, uint32_t seq,
+                                             int max_ctas, uint32_t* rows_done, int rows_done_ints,
+                                             const int32_t* seg_slab, int n_seg, uint32_t* status, void* stream) {
+  DICE_CHECK_ARG(rows_done && rows_done_ints > 0 && max_ctas > 0 && max_rows > 0, DICE_ERR_ARG);
+  DICE_CHECK_ARG(n_seg > 0 && n_seg <= kMaxFollowSeg && world >= 1 && n_seg % world == 0, DICE_ERR_LIMIT);
+  // every 256-row block of the GEMM's output takes part in ceil(hidden / 256) tiles
+  const FollowSpec follow = {rows_done, static_cast<unsigned int>(kRowsDonePerTile * ((hidden + 255) / 256)),
+                             rows_done_ints, seg_slab, n_seg};
+  return return_rows(rows, meta, peer_back, peer_flags, done_counter, hidden, DICE_BF16, rank, world,
+                     back_capacity_rows, max_rows, seq, max_ctas, status, stream, follow);
 }
 
 // ---- CUDA IPC plumbing (set-up time only) ---------------------------------------------------

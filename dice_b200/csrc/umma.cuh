@@ -56,6 +56,9 @@ struct GemmParams {
   int x_rows, x_kblk, x_nblk, x_w_rows, x_n_out;
   __nv_bfloat16* x_out;
   int64_t x_ld_out;
+  // when set (CTA-pair kernel, first problem only): every epilogue warp adds 1 to rows_done[m-block] after its
+  // stores of a tile are visible, so that a concurrent kernel can follow the output block by block
+  unsigned int* rows_done;
   // combine epilogue (CTA-pair kernel only): sorted position -> flat (token, slot) row, and the flat rows' gate weights
   const int* cmb_order;
   const float* cmb_weights;

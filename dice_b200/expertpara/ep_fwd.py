@@ -187,7 +187,7 @@ def global_combine(grouped_dup_outp, token_counts_local, token_counts_global, as
     if isinstance(token_counts_global, p2p.SegInfo):
         if isinstance(grouped_dup_outp, p2p.ReturnedRows):  # the FFN kernel already returned the rows
             info = token_counts_global
-            handle = p2p.PeerHandle(info, 1, None)
+            handle = p2p.PeerHandle(info, 1, grouped_dup_outp.event)
             if not async_op:
                 handle.wait()
             return info.xchg.back[info.slot][: info.rows_sent], [handle]
@@ -263,6 +263,17 @@ def proc_experts(inp, experts, token_counts_global, num_local_experts):
             job = _shared_job
             xchg = token_counts_global.xchg
             inter, out = xchg.ffn_buffers(pack.ffn_width(inp.dtype)) if inp.shape[0] == xchg.capacity_rows else (None, None)
+            if (out is not None and inp.dtype == torch.bfloat16 and p2p.return_follows() and p2p.reserve_sms() == 0
+                    and xchg.rows_done is not None):
+                # synchronous exchange: the return push starts beside the FFN and follows its second GEMM
+                returned = xchg.follow_ffn(token_counts_global, out)
+                shared = (job.x, job.pack) if job is not None else None
+                res = pack.run_offsets(inp, token_counts_global.seg_dev, xchg.seg_slab_dev,
+                                       reserve_sms=p2p.side_push_ctas(), shared=shared, inter=inter, out=out,
+                                       rows_done=xchg.rows_done)
+                if job is not None:
+                    job.out = res[1]
+                return returned
             if job is not None and inp.dtype == torch.bfloat16:
                 outp, job.out = pack.run_offsets(inp, token_counts_global.seg_dev, xchg.seg_slab_dev,
                                                  reserve_sms=p2p.reserve_sms(), shared=(job.x, job.pack), inter=inter, out=out)

@@ -159,6 +159,11 @@ class PeerExchange:
         per_source = list(range(self.el)) + ([-1] if self.region_rows else [])
         self.seg_slab = [i for _ in range(self.world) for i in per_source]
         self.seg_slab_dev = torch.tensor(self.seg_slab, dtype=torch.int32, device=self.device)
+        # finished 256-row blocks of the expert FFN's output (see follow_ffn); None where the kernels have no counters
+        self.rows_done = None
+        if self.dtype == torch.bfloat16 and len(self.seg_slab) <= 256:
+            self.rows_done = torch.zeros(self.capacity_rows // 256 + len(self.seg_slab) + 1, dtype=torch.int32,
+                                         device=self.device)
         self._fork = torch.cuda.Event()
         self._side_events = [torch.cuda.Event() for _ in range(2 * n_slots)]
         self._ring_events = [torch.cuda.Event() for _ in range(self.FFN_OUT_RING)]
@@ -193,6 +198,22 @@ class PeerExchange:
         self.calls += 1
         self.seq[slot] += 1
         return slot, self.seq[slot], self._tables[slot]
+
+    def follow_ffn(self, info: "SegInfo", out: torch.Tensor) -> "ReturnedRows":
+        """Launch, on the side stream, the return push that follows the expert FFN about to be launched on the
+        current stream with ``rows_done=self.rows_done`` into ``out``."""
+        from .._lib import check
+        from ..ops import device_status
+
+        tab, slot = info.tab, info.slot
+        stream = self.fork_to_comm()  # after the wait that completed this exchange's meta block
+        check(self.lib.dice_ep_return_rows_following(
+            out.data_ptr(), self._meta_ptrs[slot], tab["back"], tab["f_back"], self._done_ptrs[2 * slot + 1], self.hidden,
+            self.rank, self.world, self.min_peer_rows, self.capacity_rows, info.seq, side_push_ctas(),
+            self.rows_done.data_ptr(), self.rows_done.numel(), self.seg_slab_dev.data_ptr(), self.n_seg, self.status_ptr,
+            stream), "dice_ep_return_rows_following")
+        self.note_output_read_on_side(out)
+        return ReturnedRows(info, self.record_side_event(slot, 1))
 
     def fork_to_comm(self) -> int:
         """Order the side stream (on which asynchronous pushes run next to the
@@ -319,6 +340,20 @@ def reserve_sms() -> int:
 
 
 _fused_return = os.environ.get("DICE_EP_P2P_FUSED_RETURN", "0") == "1"
+_return_follows = os.environ.get("DICE_EP_P2P_RETURN_FOLLOWS", "0") == "1"
+
+
+def set_return_follows(flag: bool) -> None:
+    global _return_follows
+    _return_follows = flag
+
+
+def return_follows() -> bool:
+    """Whether, in a synchronous exchange, the return push is launched on the
+    side stream together with the expert FFN and sends each chunk of rows as
+    soon as the second GEMM has finished the blocks it lies in (the reference
+    runs FFN and all-to-all one after the other, ep_fwd.py:375-381)."""
+    return _return_follows and side_push_ctas() > 0
 
 
 def set_fused_return(flag: bool) -> None:
@@ -407,14 +442,17 @@ class PendingRows:
 
 
 class ReturnedRows:
-    """Plays the part of the expert outputs (``grouped_dup_outp``) when the FFN
-    kernel has already written them into the token owners' buffers: the combine
-    that follows has nothing left to send."""
+    """Plays the part of the expert outputs (``grouped_dup_outp``) when the rows
+    are already on their way into the token owners' buffers (written by the
+    FFN kernel itself, or by a push on the side stream that follows the FFN
+    block by block; ``event`` then marks the side stream after that push): the
+    combine that follows has nothing left to send."""
 
     keepalive = None
 
-    def __init__(self, info: SegInfo):
+    def __init__(self, info: SegInfo, event=None):
         self.info = info
+        self.event = event
 
 
 class PeerHandle:

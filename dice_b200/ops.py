@@ -441,6 +441,7 @@ def grouped_ffn(
     out: Optional[torch.Tensor] = None,
     reserve_sms: int = 0,
     shared=None,
+    rows_done: Optional[torch.Tensor] = None,
 ):
     """Expert FFN over expert-sorted rows (ep_fwd.py:199-211; models.py:368-376).
 
@@ -451,8 +452,12 @@ def grouped_ffn(
 
     ``shared = (tokens [N, h], w1 [1, ..., h], w2 [1, h, Fs], Fs)`` (bf16 only)
     runs the block's shared expert over all tokens inside the same two
-    launches; the result is then ``(rows_out, shared_out)``."""
-    _require_cuda(rows, w1, w2, seg_offsets, status, seg_slab, inter, out)
+    launches; the result is then ``(rows_out, shared_out)``.
+
+    ``rows_done`` (bf16 only): zeroed int32 counters, one per 256-row block of
+    the output, that the second GEMM raises as blocks complete (a return push
+    on another stream follows them)."""
+    _require_cuda(rows, w1, w2, seg_offsets, status, seg_slab, inter, out, rows_done)
     assert rows.is_contiguous() and w1.is_contiguous() and w2.is_contiguous()
     assert seg_offsets.dtype == torch.int32
     n_rows, h = rows.shape
@@ -481,12 +486,13 @@ def grouped_ffn(
             lib.dice_grouped_ffn(
                 _ptr(rows), n_rows, h, ffn, ACT_CODES[act], _ptr(w1), _ptr(w2), n_slabs, _ptr(seg_offsets),
                 _ptr(seg_slab), n_seg, _ptr(inter), _ptr(out), _ptr(sx), n_shared, s_ffn, _ptr(sw1), _ptr(sw2),
-                _ptr(s_inter), _ptr(s_out), reserve_sms, _ptr(status), _stream(),
+                _ptr(s_inter), _ptr(s_out), reserve_sms, _ptr(rows_done), _ptr(status), _stream(),
             ),
             "dice_grouped_ffn",
         )
         return (out, s_out) if shared is not None else out
     assert shared is None, "the shared expert rides along in the bf16 kernel only"
+    assert rows_done is None, "block counters are the bf16 kernel's"
     if rows.dtype == torch.float32:
         _lib.check(
             lib.dice_grouped_ffn_f32(

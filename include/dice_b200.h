@@ -262,12 +262,22 @@ DICE_API int dice_grouped_gemm(const void* a, int64_t n_rows, int k_dim, const v
  *   shared_in  [n_shared, hidden] the tokens (NULL: no shared expert),
  *   shared_w1 / shared_w2 as w1 / w2 for one slab of width shared_ffn,
  *   shared_inter [n_shared, shared_ffn] scratch, shared_out [n_shared, hidden].
+ *   rows_done  NULL, or device counters (zero on entry), one per 256-row block
+ *              of the second GEMM's tile list (block b of segment g: rows
+ *              [256 b, 256 b + 256) of the segment; segments in order, those
+ *              without rows or without weights take no block; at most
+ *              n_rows / 256 + n_seg blocks).  Every finished tile adds 16 to its
+ *              block's counter after its stores are visible device-wide, so a
+ *              block is complete at 16 * ceil(hidden / 256).  A kernel on another
+ *              stream (dice_ep_return_rows_following) can then send rows on
+ *              while later blocks are still being computed.
  */
 DICE_API int dice_grouped_ffn(const void* rows_in, int64_t n_rows, int hidden, int ffn, int act, const void* w1,
                      const void* w2, int n_slabs, const int32_t* seg_offsets, const int32_t* seg_slab,
                      int n_seg, void* inter, void* rows_out, const void* shared_in, int64_t n_shared,
                      int shared_ffn, const void* shared_w1, const void* shared_w2, void* shared_inter,
-                     void* shared_out, int reserve_sms, uint32_t* status, void* stream);
+                     void* shared_out, int reserve_sms, uint32_t* rows_done, uint32_t* status,
+                     void* stream);
 
 /* The expert FFN whose second GEMM also does the weighted combine
  * (models.py:377-381: mul_ by the gate weights, scatter_reduce_ into the token
@@ -375,6 +385,20 @@ DICE_API int dice_ep_return_rows(const void* rows, const int32_t* meta, const vo
                         const void* const* peer_flags, uint32_t* done_counter, int hidden, int dtype,
                         int rank, int world, int back_capacity_rows, int max_rows, uint32_t seq,
                         int max_ctas, uint32_t* status, void* stream);
+/* The same return (bf16 rows, bulk-copy form on max_ctas > 0 CTAs), launched on a
+ * second stream BEFORE or WHILE dice_grouped_ffn(..., rows_done) runs with
+ * reserve_sms >= max_ctas: a chunk of rows leaves as soon as the blocks of the
+ * second GEMM's output that it lies in are complete, so that the transfer of the
+ * synchronous all-to-all (ep_fwd.py:326-340) hides under the GEMM that produces
+ * its rows.  seg_slab / n_seg: the segment table the GEMM runs with (n_seg a
+ * multiple of world, at most 288; segments of one source are consecutive).  The
+ * last CTA clears rows_done[0, rows_done_ints) before it raises the flags.  A
+ * block that does not complete within the wait limit raises status 11. */
+DICE_API int dice_ep_return_rows_following(const void* rows, const int32_t* meta, const void* const* peer_back,
+                        const void* const* peer_flags, uint32_t* done_counter, int hidden, int rank,
+                        int world, int back_capacity_rows, int max_rows, uint32_t seq, int max_ctas,
+                        uint32_t* rows_done, int rows_done_ints, const int32_t* seg_slab, int n_seg,
+                        uint32_t* status, void* stream);
 /* The expert FFN fused with the return: same as dice_grouped_ffn over the
  * receive buffer, but the second GEMM's epilogue stores every output row
  * straight into the combine buffer of the rank that owns the token (NVLink

@@ -913,3 +913,89 @@ def test_ffn_with_fused_return_world_of_one(cuda_device):
         ops.check_status(status)
         assert torch.equal(back[: 2 * n], want)
         assert bool((back[2 * n:] == 0).all()) and int(done.sum()) == 0
+
+
+@pytest.mark.parametrize("layout", ["regions", "packed"])
+def test_return_push_that_follows_the_second_gemm(cuda_device, layout):
+    """The return of a synchronous exchange launched on a second stream BEFORE the expert FFN: it sends a chunk of
+    rows once the second GEMM has counted the 256-row blocks it lies in as complete.  `world` ranks whose buffers
+    share this GPU, skewed routing, real expert weights; every rank must get back exactly what an FFN followed by an
+    ordinary return delivers, the block counters must be zero again afterwards, twice on the same buffers."""
+    from dice_b200 import _lib
+
+    ops = _ops()
+    lib = _lib.load()
+    world, e, h, ffn, k = 2, 8, 256, 512, 2
+    el = e // world
+    n = [900, 1100]
+    region = k * max(n) if layout == "regions" else 0
+    cap = world * k * max(n)
+    R = _EmulatedRanks(world, e, h, cap, k * max(n), cuda_device, lib)
+    n_seg = world * (el + 1) if region else world * el
+    seg_slab = torch.tensor([i for _ in range(world) for i in (list(range(el)) + ([-1] if region else []))],
+                            dtype=torch.int32, device=cuda_device)
+    g = torch.Generator().manual_seed(77)
+    w1 = (torch.randn(el, ffn, h, generator=g) / 16).bfloat16().to(cuda_device)
+    w2 = (torch.randn(el, h, ffn, generator=g) / 16).bfloat16().to(cuda_device)
+    rows_done = torch.zeros(cap // 256 + n_seg + 1, dtype=torch.int32, device=cuda_device)
+    status = ops.device_status(cuda_device)
+    main, side = torch.cuda.current_stream(), torch.cuda.Stream()
+    st = main.cuda_stream
+    matrices = R.table([c.data_ptr() for c in R.ctrl])
+    seg_base = 2 + 4 * world + 1
+    for seq in (1, 2):
+        xs, poss, segs = _emulated_inputs(world, e, h, n, k, cuda_device, seed=50 + seq, hot_owner=1)
+        seg_host = [s.cpu().tolist() for s in segs]
+        if not region:
+            R.publish_counts(seg_host, seq)
+            for r in range(world):
+                assert lib.dice_ep_exchange_counts(segs[r].data_ptr(), matrices, R.flags(0), R.meta[r].data_ptr(), r, world,
+                                                   e, cap, seq, R.status[r].data_ptr(), st) == 0
+        for r in range(world):
+            assert lib.dice_ep_dispatch_rows(xs[r].data_ptr(), poss[r].data_ptr(), segs[r].data_ptr(),
+                                             None if region else R.meta[r].data_ptr(),
+                                             R.table([t.data_ptr() for t in R.recv]), R.flags(1), R.done[r].data_ptr(), n[r],
+                                             k, h, 0, r, world, e, cap, seq, 0, region, matrices if region else None,
+                                             R.status[r].data_ptr(), st) == 0
+        for r in range(world):
+            if region:
+                assert lib.dice_ep_wait_dispatch(R.my_flags(r, 1), R.ctrl[r].data_ptr(), R.meta[r].data_ptr(), r, world, e,
+                                                 region, seq, R.status[r].data_ptr(), st) == 0
+            else:
+                assert lib.dice_ep_wait_flags(R.my_flags(r, 1), world, seq, 0, R.status[r].data_ptr(), st) == 0
+        # what an FFN followed by an ordinary return delivers
+        outs = []
+        for r in range(world):
+            seg_dev = R.meta[r][seg_base: seg_base + n_seg + 1]
+            outs.append(ops.grouped_ffn(R.recv[r][:cap], w1, w2, seg_dev, "gelu_tanh", ffn, status=status, seg_slab=seg_slab))
+        for r in range(world):
+            assert lib.dice_ep_return_rows(outs[r].data_ptr(), R.meta[r].data_ptr(), R.table([t.data_ptr() for t in R.back]),
+                                           R.flags(2), R.done[r][1:].data_ptr(), h, 0, r, world, R.back_cap, cap, seq, 0,
+                                           R.status[r].data_ptr(), st) == 0
+        torch.cuda.synchronize()
+        want = [b[: k * n[r]].clone() for r, b in enumerate(R.back)]
+        for r in range(world):
+            R.back[r].fill_(5.0)
+            R.ctrl[r][R.flag_base + 128: R.flag_base + 128 + world] = 0  # the return flags, for the second delivery
+        torch.cuda.synchronize()
+        for r in range(world):
+            out = torch.zeros(cap, h, dtype=torch.bfloat16, device=cuda_device)
+            seg_dev = R.meta[r][seg_base: seg_base + n_seg + 1]
+            side.wait_stream(main)
+            assert lib.dice_ep_return_rows_following(
+                out.data_ptr(), R.meta[r].data_ptr(), R.table([t.data_ptr() for t in R.back]), R.flags(2),
+                R.done[r][1:].data_ptr(), h, r, world, R.back_cap, cap, seq, 4, rows_done.data_ptr(), rows_done.numel(),
+                seg_slab.data_ptr(), n_seg, R.status[r].data_ptr(), side.cuda_stream) == 0
+            got = ops.grouped_ffn(R.recv[r][:cap], w1, w2, seg_dev, "gelu_tanh", ffn, status=status, seg_slab=seg_slab,
+                                  out=out, reserve_sms=4, rows_done=rows_done)
+            main.wait_stream(side)  # the next rank's FFN counts into the same counters
+            assert got.data_ptr() == out.data_ptr()
+        for r in range(world):
+            assert lib.dice_ep_wait_flags(R.my_flags(r, 2), world, seq, 1, R.status[r].data_ptr(), st) == 0
+        torch.cuda.synchronize()
+        ops.check_status(status)
+        assert int(rows_done.abs().sum()) == 0, "the push must leave the block counters at zero"
+        for r in range(world):
+            ops.check_status(R.status[r])
+            assert torch.equal(R.back[r][: k * n[r]], want[r]), f"rank {r}: rows differ from FFN + ordinary return"
+            assert bool((R.back[r][k * n[r]:] == 5.0).all())
