@@ -473,7 +473,7 @@ __device__ __forceinline__ void bulk_drain() {
 // A ring that gave up at chunk `k` still has the loads of chunks (k, last_loaded] in flight: give them a
 // short, bounded time to land before the CTA's shared memory is released.
 __device__ __forceinline__ void bulk_settle(const uint64_t* bars, int bufs, int64_t k, int64_t last_loaded) {
-  for (int64_t i = k + 1; i <= last_loaded; ++i)
+  for (int64_t i = k + 1 > 0 ? k + 1 : 0; i <= last_loaded; ++i)
     bulk_bar_wait(smem_addr32(&bars[i % bufs]), static_cast<uint32_t>((i / bufs) & 1), kBulkDrainLimitNs);
 }
 

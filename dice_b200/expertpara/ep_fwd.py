@@ -266,14 +266,14 @@ def proc_experts(inp, experts, token_counts_global, num_local_experts):
             if (out is not None and inp.dtype == torch.bfloat16 and p2p.return_follows() and p2p.reserve_sms() == 0
                     and xchg.rows_done is not None):
                 # synchronous exchange: the return push starts beside the FFN and follows its second GEMM
-                returned = xchg.follow_ffn(token_counts_global, out)
+                side = xchg.fork_to_comm()  # the push needs what is queued so far (the meta block), not the FFN
                 shared = (job.x, job.pack) if job is not None else None
                 res = pack.run_offsets(inp, token_counts_global.seg_dev, xchg.seg_slab_dev,
                                        reserve_sms=p2p.side_push_ctas(), shared=shared, inter=inter, out=out,
                                        rows_done=xchg.rows_done)
                 if job is not None:
                     job.out = res[1]
-                return returned
+                return xchg.follow_ffn(token_counts_global, out, side)
             if job is not None and inp.dtype == torch.bfloat16:
                 outp, job.out = pack.run_offsets(inp, token_counts_global.seg_dev, xchg.seg_slab_dev,
                                                  reserve_sms=p2p.reserve_sms(), shared=(job.x, job.pack), inter=inter, out=out)

@@ -199,14 +199,15 @@ class PeerExchange:
         self.seq[slot] += 1
         return slot, self.seq[slot], self._tables[slot]
 
-    def follow_ffn(self, info: "SegInfo", out: torch.Tensor) -> "ReturnedRows":
-        """Launch, on the side stream, the return push that follows the expert FFN about to be launched on the
-        current stream with ``rows_done=self.rows_done`` into ``out``."""
+    def follow_ffn(self, info: "SegInfo", out: torch.Tensor, stream: int) -> "ReturnedRows":
+        """Launch, on the side stream, the return push that follows the expert FFN just launched on the current
+        stream with ``rows_done=self.rows_done`` into ``out``.  ``stream``: what ``fork_to_comm`` returned BEFORE
+        the FFN was launched (the push only needs this exchange's meta block, not the FFN).  The push is launched
+        after its producer, so that it never waits for a kernel the host has yet to launch (a first launch may load
+        its module, which can wait for running kernels)."""
         from .._lib import check
-        from ..ops import device_status
 
         tab, slot = info.tab, info.slot
-        stream = self.fork_to_comm()  # after the wait that completed this exchange's meta block
         check(self.lib.dice_ep_return_rows_following(
             out.data_ptr(), self._meta_ptrs[slot], tab["back"], tab["f_back"], self._done_ptrs[2 * slot + 1], self.hidden,
             self.rank, self.world, self.min_peer_rows, self.capacity_rows, info.seq, side_push_ctas(),

@@ -386,8 +386,12 @@ DICE_API int dice_ep_return_rows(const void* rows, const int32_t* meta, const vo
                         int rank, int world, int back_capacity_rows, int max_rows, uint32_t seq,
                         int max_ctas, uint32_t* status, void* stream);
 /* The same return (bf16 rows, bulk-copy form on max_ctas > 0 CTAs), launched on a
- * second stream BEFORE or WHILE dice_grouped_ffn(..., rows_done) runs with
- * reserve_sms >= max_ctas: a chunk of rows leaves as soon as the blocks of the
+ * second stream right AFTER dice_grouped_ffn(..., rows_done) was launched with
+ * reserve_sms >= max_ctas (after its producer, so that the push never depends
+ * on a launch the host has yet to make: the first launch of a kernel may load
+ * its module, which can wait for running kernels; the second stream only has to
+ * be ordered after the kernel that completed `meta`).  A chunk of rows leaves as
+ * soon as the blocks of the
  * second GEMM's output that it lies in are complete, so that the transfer of the
  * synchronous all-to-all (ep_fwd.py:326-340) hides under the GEMM that produces
  * its rows.  seg_slab / n_seg: the segment table the GEMM runs with (n_seg a

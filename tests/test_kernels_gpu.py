@@ -982,6 +982,8 @@ def test_return_push_that_follows_the_second_gemm(cuda_device, layout):
             out = torch.zeros(cap, h, dtype=torch.bfloat16, device=cuda_device)
             seg_dev = R.meta[r][seg_base: seg_base + n_seg + 1]
             side.wait_stream(main)
+            # the push is launched FIRST here, so that it really has to wait for the GEMM (whose kernel is already
+            # loaded: the FFN above ran it); the product launches it right after the FFN
             assert lib.dice_ep_return_rows_following(
                 out.data_ptr(), R.meta[r].data_ptr(), R.table([t.data_ptr() for t in R.back]), R.flags(2),
                 R.done[r][1:].data_ptr(), h, r, world, R.back_cap, cap, seq, 4, rows_done.data_ptr(), rows_done.numel(),
