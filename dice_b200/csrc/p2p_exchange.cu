@@ -576,6 +576,7 @@ ep_return_bulk_kernel(const uint8_t* __restrict__ rows, const int* __restrict__ 
                       FollowSpec follow) {
   __shared__ int s_fseg[kMaxFollowSeg + 1];  // segment offsets of the receive buffer
   __shared__ int s_fmb[kMaxFollowSeg + 1];   // 256-row blocks in front of segment g (-1 in the table: no weights)
+  __shared__ int s_fnblk;                    // blocks of the whole output
   extern __shared__ __align__(128) uint8_t bulk_bufs[];
   __shared__ __align__(8) uint64_t bars_all[kBulkMaxWarps][kBulkMaxBufs];
   __shared__ int s_src_off[kMaxRanks];
@@ -620,35 +621,46 @@ ep_return_bulk_kernel(const uint8_t* __restrict__ rows, const int* __restrict__ 
         s_fmb[g] = has_weights ? mb : -1;
         if (cnt > 0 && has_weights) mb += (cnt + kFollowRowsPerBlock - 1) / kFollowRowsPerBlock;
       }
+      s_fnblk = mb;
     }
   }
   __syncthreads();
-  // rows [r0, r0 + n) of source s are final once every block of the GEMM's output that they touch is complete
-  const int segs_per_source = follow.rows_done != nullptr ? follow.n_seg / world : 0;
-  auto rows_ready = [&](int s, int r0, int n) -> bool {
-    for (int g = s * segs_per_source; g < (s + 1) * segs_per_source; ++g) {
-      if (s_fmb[g] < 0) continue;
-      const int lo = r0 > s_fseg[g] ? r0 : s_fseg[g];
-      const int hi = r0 + n < s_fseg[g + 1] ? r0 + n : s_fseg[g + 1];
-      if (lo >= hi) continue;
-      const int b0 = s_fmb[g] + (lo - s_fseg[g]) / kFollowRowsPerBlock;
-      const int b1 = s_fmb[g] + (hi - 1 - s_fseg[g]) / kFollowRowsPerBlock;
-      for (int b = b0; b <= b1; ++b) {
-        if (b >= follow.n_ints) return false;
-        const uint64_t t0 = timer_ns();
-        uint32_t spins = 0;
-        for (;;) {
-          unsigned int v;
-          asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(follow.rows_done + b) : "memory");
-          if (v >= follow.target) break;
-          if ((++spins & 63u) == 0) {
-            if (timer_ns() - t0 > kPeerWaitLimitNs) return false;
-            __nanosleep(100);
-          }
+  // Rows [.., r_last] of source s are final once every block of the GEMM's output up to the one r_last lies in
+  // is complete.  The warp keeps a watermark (blocks [0, ready_upto) are complete: the GEMM finishes its blocks
+  // roughly in order) and moves it with one acquire load per lane, 32 blocks per round trip.
+  const bool following = follow.rows_done != nullptr;
+  const int segs_per_source = following ? follow.n_seg / world : 0;
+  int ready_upto = 0;
+  auto last_block = [&](int s, int r_last) -> int {
+    int need = -1;
+    for (int g = s * segs_per_source; g < (s + 1) * segs_per_source; ++g)
+      if (s_fmb[g] >= 0 && r_last >= s_fseg[g] && r_last < s_fseg[g + 1])
+        need = s_fmb[g] + (r_last - s_fseg[g]) / kFollowRowsPerBlock;
+    return need;
+  };
+  auto wait_for_block = [&](int need) -> bool {  // all lanes of the warp
+    if (need >= s_fnblk || need >= follow.n_ints) return false;
+    const uint64_t t0 = timer_ns();
+    uint32_t spins = 0;
+    while (ready_upto <= need) {
+      const int b = ready_upto + lane;
+      bool done = false;
+      if (b < s_fnblk) {
+        unsigned int v;
+        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(follow.rows_done + b) : "memory");
+        done = v >= follow.target;
+      }
+      const unsigned m = __ballot_sync(0xffffffffu, done);
+      const int run = m == 0xffffffffu ? 32 : __ffs(static_cast<int>(~m)) - 1;
+      ready_upto += run;
+      if (run == 0) {
+        if ((++spins & 15u) == 0) {  // lane 0's clock decides for the warp
+          const int expired = timer_ns() - t0 > kPeerWaitLimitNs ? 1 : 0;
+          if (__shfl_sync(0xffffffffu, expired, 0) != 0) return false;
         }
+        __nanosleep(200);
       }
     }
-    asm volatile("fence.proxy.async;" ::: "memory");  // the copy unit reads what the GEMM's epilogue stored
     return true;
   };
   const int64_t worker = static_cast<int64_t>(blockIdx.x) * shape.warps + warp;
@@ -665,45 +677,65 @@ ep_return_bulk_kernel(const uint8_t* __restrict__ rows, const int* __restrict__ 
     n = s_src_off[s] + s_src_cnt[s] - r0;
     if (n > rows_per_chunk) n = rows_per_chunk;
   };
-  if (lane == 0) {  // a ring is one lane's: one load and one store per chunk
+  // A ring is one lane's: one load and one store per chunk.  A push that follows a GEMM runs the loop with the
+  // whole warp (the other lanes only help to watch the block counters); every branch below is then warp-uniform.
+  if (lane == 0 || following) {
     for (int64_t j = 0; j < mine + lag; ++j) {
       if (j < mine) {
-        if (j >= bufs) bulk_wait_read_1();
+        if (lane == 0 && j >= bufs) bulk_wait_read_1();
         int s, r0, n;
         locate(j, s, r0, n);
-        if (follow.rows_done != nullptr && !rows_ready(s, r0, n)) {
-          if (status != nullptr) atomicCAS(status, 0u, DICE_STATUS_WAIT_FFN_ROWS);
-          atomicExch(&s_fail, 1);
-          bulk_settle(bars, bufs, j - lag - 1, j - 1);
-          break;
+        if (following) {
+          const int need = last_block(s, r0 + n - 1);
+          bool ok = need < 0 || need < ready_upto || wait_for_block(need);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) {
+            if (lane == 0) {
+              if (status != nullptr) atomicCAS(status, 0u, DICE_STATUS_WAIT_FFN_ROWS);
+              atomicExch(&s_fail, 1);
+              bulk_settle(bars, bufs, j - lag - 1, j - 1);
+            }
+            break;
+          }
+          if (lane == 0) asm volatile("fence.proxy.async;" ::: "memory");  // the copy unit reads the GEMM's stores
         }
-        const int b = static_cast<int>(j % bufs);
-        bulk_load(buf0 + b * shape.buf_bytes, rows + static_cast<int64_t>(r0) * row_bytes, static_cast<uint32_t>(n) * row_bytes,
-                  smem_addr32(&bars[b]));
+        if (lane == 0) {
+          const int b = static_cast<int>(j % bufs);
+          bulk_load(buf0 + b * shape.buf_bytes, rows + static_cast<int64_t>(r0) * row_bytes,
+                    static_cast<uint32_t>(n) * row_bytes, smem_addr32(&bars[b]));
+        }
       }
       const int64_t k = j - lag;
       if (k >= 0) {
         const int b = static_cast<int>(k % bufs);
-        if (!bulk_bar_wait(smem_addr32(&bars[b]), static_cast<uint32_t>((k / bufs) & 1), kBulkWaitLimitNs)) {
-          if (status != nullptr) atomicCAS(status, 0u, DICE_STATUS_WAIT_SMEM_FULL);
-          atomicExch(&s_fail, 1);
-          bulk_settle(bars, bufs, k, (j < mine ? j : mine - 1));
+        bool arrived = true;
+        if (lane == 0)
+          arrived = bulk_bar_wait(smem_addr32(&bars[b]), static_cast<uint32_t>((k / bufs) & 1), kBulkWaitLimitNs);
+        if (following) arrived = __shfl_sync(0xffffffffu, arrived ? 1 : 0, 0) != 0;
+        if (!arrived) {
+          if (lane == 0) {
+            if (status != nullptr) atomicCAS(status, 0u, DICE_STATUS_WAIT_SMEM_FULL);
+            atomicExch(&s_fail, 1);
+            bulk_settle(bars, bufs, k, (j < mine ? j : mine - 1));
+          }
           break;
         }
-        int s, r0, n;
-        locate(k, s, r0, n);
-        const int row = s_back[s] + (r0 - s_src_off[s]);
-        if (row + n > back_capacity_rows) {
-          if (status != nullptr) atomicCAS(status, 0u, DICE_STATUS_EXCHANGE_OVERFLOW);
-          n = back_capacity_rows > row ? back_capacity_rows - row : 0;
+        if (lane == 0) {
+          int s, r0, n;
+          locate(k, s, r0, n);
+          const int row = s_back[s] + (r0 - s_src_off[s]);
+          if (row + n > back_capacity_rows) {
+            if (status != nullptr) atomicCAS(status, 0u, DICE_STATUS_EXCHANGE_OVERFLOW);
+            n = back_capacity_rows > row ? back_capacity_rows - row : 0;
+          }
+          if (n > 0)
+            bulk_store(static_cast<uint8_t*>(back_bufs.ptr[s]) + static_cast<int64_t>(row) * row_bytes,
+                       buf0 + b * shape.buf_bytes, static_cast<uint32_t>(n) * row_bytes);
+          bulk_commit();
         }
-        if (n > 0)
-          bulk_store(static_cast<uint8_t*>(back_bufs.ptr[s]) + static_cast<int64_t>(row) * row_bytes, buf0 + b * shape.buf_bytes,
-                     static_cast<uint32_t>(n) * row_bytes);
-        bulk_commit();
       }
     }
-    bulk_drain();
+    if (lane == 0) bulk_drain();
   }
   __syncwarp();
   signal_when_grid_done(done_counter, flags, rank, world, seq, &s_fail, follow.rows_done, follow.n_ints);
