@@ -514,12 +514,15 @@ extern "C" int dice_grouped_ffn(const void* rows_in, int64_t n_rows, int hidden,
   DICE_CHECK_ARG(hidden > 0 && ffn > 0 && reserve_sms >= 0, DICE_ERR_ARG);
   // counting finished blocks of the output is the CTA-pair kernel's; a caller that asked for it waits on the counters
   if (rows_done != nullptr) DICE_CHECK_ARG(use_cta_pairs() && n_rows > 0 && n_seg > 0, DICE_ERR_ARG);
+  // the push that follows the second GEMM is launched after this call and cannot start before the first GEMM has
+  // ended: only the second GEMM leaves SMs free for it
+  const int reserve1 = rows_done != nullptr ? 0 : reserve_sms;
   if (n_rows > 0 && n_seg > 0) DICE_CHECK_ARG(inter != nullptr, DICE_ERR_ARG);
   const int epi1 = act == DICE_ACT_SWIGLU ? DICE_EPI_SWIGLU : DICE_EPI_GELU_TANH;
   const int64_t w1_rows = act == DICE_ACT_SWIGLU ? dice_w13_rows(ffn) : ffn;
   if (shared_in == nullptr || n_shared == 0) {
     int rc = dice_grouped_gemm(rows_in, n_rows, hidden, w1, n_slabs, w1_rows, seg_offsets, seg_slab, n_seg, epi1, inter,
-                               ffn, ffn, reserve_sms, status, stream);
+                               ffn, ffn, reserve1, status, stream);
     if (rc != DICE_OK) return rc;
     if (rows_done != nullptr) {
       DICE_CHECK_ARG(n_seg <= kMaxSeg && n_rows < 0x7fffff00LL && hidden % 8 == 0 && ffn % 8 == 0, DICE_ERR_LIMIT);
@@ -556,7 +559,7 @@ extern "C" int dice_grouped_ffn(const void* rows_in, int64_t n_rows, int hidden,
                  DICE_ERR_ALIGN);
   DiceDenseSpec x1 = {shared_in, n_shared, hidden, shared_w1, sw1_rows, shared_inter, shared_ffn, shared_ffn};
   int rc = dice_internal_gemm_pair(rows_in, n_rows, hidden, w1, n_slabs, w1_rows, seg_offsets, seg_slab, n_seg, epi1, inter,
-                                   ffn, ffn, reserve_sms, status, s, nullptr, &x1);
+                                   ffn, ffn, reserve1, status, s, nullptr, &x1);
   if (rc != DICE_OK) return rc;
   DiceDenseSpec x2 = {shared_inter, n_shared, shared_ffn, shared_w2, hidden, shared_out, hidden, hidden};
   return dice_internal_gemm_pair(inter, n_rows, ffn, w2, n_slabs, hidden, seg_offsets, seg_slab, n_seg, DICE_EPI_STORE,

@@ -141,6 +141,13 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
   }
   if (warp == 1) tmem_alloc_pair(smem_u32(tmem_slot), kTmemCols);
   pdl_wait();  // the segment table and the rows written by earlier kernels are visible from here on
+#ifdef DICE_FOLLOW_TRACE
+  if (p.rows_done != nullptr && threadIdx.x == 0) {
+    unsigned long long now;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+    atomicMin(reinterpret_cast<unsigned long long*>(p.rows_done + 1024), now);
+  }
+#endif
 
   if (p.ret_world > 0) {
     if (threadIdx.x <= p.ret_world) s_ret_src[threadIdx.x] = p.ret_meta[2 + 2 * p.ret_world + threadIdx.x];  // src_off of the meta block
@@ -414,6 +421,13 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
       if (threadIdx.x == 0) *p.ret_done_counter = 0;
     }
   }
+#ifdef DICE_FOLLOW_TRACE
+  if (p.rows_done != nullptr && threadIdx.x == 64) {
+    unsigned long long now;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+    atomicMax(reinterpret_cast<unsigned long long*>(p.rows_done + 1026), now);
+  }
+#endif
   cluster_barrier();  // neither CTA leaves while the other may still signal its mbarriers or read its operands
   if (warp == 1) {
     __syncwarp();

@@ -663,6 +663,10 @@ ep_return_bulk_kernel(const uint8_t* __restrict__ rows, const int* __restrict__ 
     }
     return true;
   };
+#ifdef DICE_FOLLOW_TRACE
+  unsigned long long* trace = following ? reinterpret_cast<unsigned long long*>(follow.rows_done + 1024) : nullptr;
+  if (trace != nullptr && lane == 0) atomicMin(trace + 2, timer_ns());
+#endif
   const int64_t worker = static_cast<int64_t>(blockIdx.x) * shape.warps + warp;
   const int64_t n_workers = static_cast<int64_t>(gridDim.x) * shape.warps;
   const int64_t n_chunks = s_chunk0[world];
@@ -698,6 +702,13 @@ ep_return_bulk_kernel(const uint8_t* __restrict__ rows, const int* __restrict__ 
             break;
           }
           if (lane == 0) asm volatile("fence.proxy.async;" ::: "memory");  // the copy unit reads the GEMM's stores
+#ifdef DICE_FOLLOW_TRACE
+          if (lane == 0) {
+            if (j == 0) atomicMin(trace + 3, timer_ns());
+            if (j == mine / 2) atomicMax(trace + 4, timer_ns());
+            if (j == mine - 1) atomicMax(trace + 5, timer_ns());
+          }
+#endif
         }
         if (lane == 0) {
           const int b = static_cast<int>(j % bufs);
@@ -736,6 +747,9 @@ ep_return_bulk_kernel(const uint8_t* __restrict__ rows, const int* __restrict__ 
       }
     }
     if (lane == 0) bulk_drain();
+#ifdef DICE_FOLLOW_TRACE
+    if (trace != nullptr && lane == 0) atomicMax(trace + 6, timer_ns());
+#endif
   }
   __syncwarp();
   signal_when_grid_done(done_counter, flags, rank, world, seq, &s_fail, follow.rows_done, follow.n_ints);

@@ -269,7 +269,7 @@ def proc_experts(inp, experts, token_counts_global, num_local_experts):
                 side = xchg.fork_to_comm()  # the push needs what is queued so far (the meta block), not the FFN
                 shared = (job.x, job.pack) if job is not None else None
                 res = pack.run_offsets(inp, token_counts_global.seg_dev, xchg.seg_slab_dev,
-                                       reserve_sms=p2p.side_push_ctas(), shared=shared, inter=inter, out=out,
+                                       reserve_sms=p2p.follow_ctas(), shared=shared, inter=inter, out=out,
                                        rows_done=xchg.rows_done)
                 if job is not None:
                     job.out = res[1]

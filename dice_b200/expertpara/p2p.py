@@ -210,7 +210,7 @@ class PeerExchange:
         tab, slot = info.tab, info.slot
         check(self.lib.dice_ep_return_rows_following(
             out.data_ptr(), self._meta_ptrs[slot], tab["back"], tab["f_back"], self._done_ptrs[2 * slot + 1], self.hidden,
-            self.rank, self.world, self.min_peer_rows, self.capacity_rows, info.seq, side_push_ctas(),
+            self.rank, self.world, self.min_peer_rows, self.capacity_rows, info.seq, follow_ctas(),
             self.rows_done.data_ptr(), self.rows_done.numel(), self.seg_slab_dev.data_ptr(), self.n_seg, self.status_ptr,
             stream), "dice_ep_return_rows_following")
         self.note_output_read_on_side(out)
@@ -349,12 +349,22 @@ def set_return_follows(flag: bool) -> None:
     _return_follows = flag
 
 
+_follow_ctas = int(os.environ.get("DICE_EP_P2P_FOLLOW_CTAS", "16"))
+
+
+def follow_ctas() -> int:
+    """CTAs (= SMs) of the return push that follows the second expert GEMM.  One SM's copy unit moves about
+    30-38 GB/s through shared memory, so hiding a whole return under the second GEMM takes more SMs than a push
+    that has a whole FFN to hide under (``side_push_ctas``)."""
+    return _follow_ctas
+
+
 def return_follows() -> bool:
     """Whether, in a synchronous exchange, the return push is launched on the
     side stream together with the expert FFN and sends each chunk of rows as
     soon as the second GEMM has finished the blocks it lies in (the reference
     runs FFN and all-to-all one after the other, ep_fwd.py:375-381)."""
-    return _return_follows and side_push_ctas() > 0
+    return _return_follows and _follow_ctas > 0
 
 
 def set_fused_return(flag: bool) -> None:

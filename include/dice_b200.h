@@ -270,7 +270,8 @@ DICE_API int dice_grouped_gemm(const void* a, int64_t n_rows, int k_dim, const v
  *              block's counter after its stores are visible device-wide, so a
  *              block is complete at 16 * ceil(hidden / 256).  A kernel on another
  *              stream (dice_ep_return_rows_following) can then send rows on
- *              while later blocks are still being computed.
+ *              while later blocks are still being computed.  With rows_done
+ *              only the second GEMM leaves reserve_sms SMs free.
  */
 DICE_API int dice_grouped_ffn(const void* rows_in, int64_t n_rows, int hidden, int ffn, int act, const void* w1,
                      const void* w2, int n_slabs, const int32_t* seg_offsets, const int32_t* seg_slab,
