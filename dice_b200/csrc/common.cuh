@@ -65,6 +65,21 @@ static inline cudaError_t dice_launch(void (*kernel)(KArgs...), dim3 grid, dim3 
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
+// plain stream order: the kernel starts only when everything before it in the stream has completed.  For a kernel
+// behind work that shares the GPU with a kernel of another stream: blocks that became resident early would sit on
+// the SMs left free for that other kernel.
+template <typename... KArgs, typename... Args>
+static inline cudaError_t dice_launch_ordered(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                              cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  dice_count_launch();
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 // streaming 16-byte load (coherent: the kernels that use it may start while the producer of the data still runs)
 __device__ __forceinline__ uint4 ldg_stream16(const void* p) {
   uint4 v;

@@ -97,6 +97,12 @@ __device__ __forceinline__ void red_add_bf16x8(void* dst, const uint4& v) {
 // The loader and the tensor-core warp run their loops with all 32 lanes (the waits are warp-wide) and elect one
 // lane for the TMA / MMA instructions: loop state stays warp-uniform for the compiler, and the issue loop is
 // short enough to keep the tensor pipe fed (a single-lane loop under `lane == 0` was 15 % slower).
+#ifdef DICE_FOLLOW_TRACE
+// debug build only: first start and last end of every launch (time stamps of the global timer)
+__device__ unsigned long long g_gemm_start[1024];
+__device__ unsigned long long g_gemm_end[1024];
+#endif
+
 __global__ void __launch_bounds__(kThreads, 1)
 grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                          const __grid_constant__ CUtensorMap tm_b_narrow, const __grid_constant__ CUtensorMap tm_xa,
@@ -142,10 +148,10 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
   if (warp == 1) tmem_alloc_pair(smem_u32(tmem_slot), kTmemCols);
   pdl_wait();  // the segment table and the rows written by earlier kernels are visible from here on
 #ifdef DICE_FOLLOW_TRACE
-  if (p.rows_done != nullptr && threadIdx.x == 0) {
+  if (threadIdx.x == 0) {
     unsigned long long now;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
-    atomicMin(reinterpret_cast<unsigned long long*>(p.rows_done + 1024), now);
+    atomicMin(&g_gemm_start[p.trace_id & 1023], now);
   }
 #endif
 
@@ -422,10 +428,10 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
     }
   }
 #ifdef DICE_FOLLOW_TRACE
-  if (p.rows_done != nullptr && threadIdx.x == 64) {
+  if (threadIdx.x == 64) {
     unsigned long long now;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
-    atomicMax(reinterpret_cast<unsigned long long*>(p.rows_done + 1026), now);
+    atomicMax(&g_gemm_end[p.trace_id & 1023], now);
   }
 #endif
   cluster_barrier();  // neither CTA leaves while the other may still signal its mbarriers or read its operands
@@ -468,6 +474,28 @@ int resident_pairs() {
 }  // namespace
 
 // Internal entry used by dice_grouped_gemm: same arguments, already validated.
+#ifdef DICE_FOLLOW_TRACE
+static int g_trace_next = 0;
+static int g_trace_kind[1024];
+extern "C" __attribute__((visibility("default"))) int dice_debug_gemm_trace(unsigned long long* start, unsigned long long* end,
+                                                                            int* kind) {
+  cudaDeviceSynchronize();
+  const int n = g_trace_next < 1024 ? g_trace_next : 1024;
+  if (start != nullptr) {
+    cudaMemcpyFromSymbol(start, g_gemm_start, sizeof(unsigned long long) * 1024);
+    cudaMemcpyFromSymbol(end, g_gemm_end, sizeof(unsigned long long) * 1024);
+    for (int i = 0; i < 1024; ++i) kind[i] = g_trace_kind[i];
+  }
+  void *ps, *pe;
+  cudaGetSymbolAddress(&ps, g_gemm_start);
+  cudaGetSymbolAddress(&pe, g_gemm_end);
+  cudaMemset(ps, 0xff, sizeof(unsigned long long) * 1024);
+  cudaMemset(pe, 0, sizeof(unsigned long long) * 1024);
+  g_trace_next = 0;
+  return n;
+}
+#endif
+
 int dice_internal_gemm_pair(const void* a, int64_t n_rows, int k_dim, const void* w, int n_slabs, int64_t w_rows,
                             const int32_t* seg_offsets, const int32_t* seg_slab, int n_seg, int epilogue, void* out,
                             int64_t ld_out, int n_out, int reserve_sms, uint32_t* status, cudaStream_t stream,
@@ -519,6 +547,11 @@ int dice_internal_gemm_pair(const void* a, int64_t n_rows, int k_dim, const void
   p.b_box_rows = 128;
   p.n_stages = kPairStages;
   p.rows_done = rows_done;
+#ifdef DICE_FOLLOW_TRACE
+  p.trace_id = g_trace_next;
+  g_trace_kind[g_trace_next & 1023] = epilogue + (rows_done != nullptr ? 1000 : 0);
+  ++g_trace_next;
+#endif
   if (combine != nullptr) {
     if (epilogue != DICE_EPI_STORE || ret != nullptr || extra != nullptr || !combine->order || !combine->weights)
       return DICE_ERR_ARG;

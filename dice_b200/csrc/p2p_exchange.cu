@@ -559,7 +559,16 @@ ep_dispatch_bulk_kernel(const uint8_t* __restrict__ x, const int* __restrict__ p
 // epilogue warps that have stored a tile (rows_done); a block is complete at `target`.  The push derives the same
 // block numbering from the segment table, waits (bounded) for the blocks a chunk of rows lies in, and only then
 // copies the chunk; when the grid is done its last CTA clears the counters for the next use.
+#ifdef DICE_FOLLOW_TRACE
+// debug build only: per launch of the bulk return: first start, first chunk ready (min); half, last ready, done (max)
+__device__ unsigned long long g_push_trace[1024][8];
+static int g_push_next = 0;
+static int g_push_kind[1024];
+#endif
 struct FollowSpec {
+#ifdef DICE_FOLLOW_TRACE
+  int trace_id;
+#endif
   unsigned int* rows_done;  // null: the rows are complete when the kernel starts
   unsigned int target;
   int n_ints;               // entries of rows_done
@@ -664,8 +673,8 @@ ep_return_bulk_kernel(const uint8_t* __restrict__ rows, const int* __restrict__ 
     return true;
   };
 #ifdef DICE_FOLLOW_TRACE
-  unsigned long long* trace = following ? reinterpret_cast<unsigned long long*>(follow.rows_done + 1024) : nullptr;
-  if (trace != nullptr && lane == 0) atomicMin(trace + 2, timer_ns());
+  unsigned long long* trace = g_push_trace[follow.trace_id & 1023];
+  if (lane == 0) atomicMin(trace + 0, timer_ns());
 #endif
   const int64_t worker = static_cast<int64_t>(blockIdx.x) * shape.warps + warp;
   const int64_t n_workers = static_cast<int64_t>(gridDim.x) * shape.warps;
@@ -704,9 +713,9 @@ ep_return_bulk_kernel(const uint8_t* __restrict__ rows, const int* __restrict__ 
           if (lane == 0) asm volatile("fence.proxy.async;" ::: "memory");  // the copy unit reads the GEMM's stores
 #ifdef DICE_FOLLOW_TRACE
           if (lane == 0) {
-            if (j == 0) atomicMin(trace + 3, timer_ns());
-            if (j == mine / 2) atomicMax(trace + 4, timer_ns());
-            if (j == mine - 1) atomicMax(trace + 5, timer_ns());
+            if (j == 0) atomicMin(trace + 1, timer_ns());
+            if (j == mine / 2) atomicMax(trace + 2, timer_ns());
+            if (j == mine - 1) atomicMax(trace + 3, timer_ns());
           }
 #endif
         }
@@ -748,7 +757,7 @@ ep_return_bulk_kernel(const uint8_t* __restrict__ rows, const int* __restrict__ 
     }
     if (lane == 0) bulk_drain();
 #ifdef DICE_FOLLOW_TRACE
-    if (trace != nullptr && lane == 0) atomicMax(trace + 6, timer_ns());
+    if (lane == 0) atomicMax(trace + 4, timer_ns());
 #endif
   }
   __syncwarp();
@@ -958,9 +967,13 @@ extern "C" int dice_ep_dispatch_rows(const void* x, const int32_t* pos, const in
 extern "C" int dice_ep_wait_flags(const uint32_t* my_flags, int world, uint32_t seq, int what, uint32_t* status,
                                   void* stream) {
   DICE_CHECK_ARG(my_flags && world >= 1 && world <= kMaxRanks, DICE_ERR_ARG);
-  const uint32_t code = what == 0 ? DICE_STATUS_WAIT_PEER_DISPATCH : DICE_STATUS_WAIT_PEER_COMBINE;
-  DICE_CUDA_OK(dice_launch(ep_wait_kernel, dim3(1), dim3(32), 0, static_cast<cudaStream_t>(stream), my_flags, world, seq,
-                           status, code));
+  const uint32_t code = (what & 1) == 0 ? DICE_STATUS_WAIT_PEER_DISPATCH : DICE_STATUS_WAIT_PEER_COMBINE;
+  if ((what & 2) != 0)
+    DICE_CUDA_OK(dice_launch_ordered(ep_wait_kernel, dim3(1), dim3(32), 0, static_cast<cudaStream_t>(stream), my_flags,
+                                     world, seq, status, code));
+  else
+    DICE_CUDA_OK(dice_launch(ep_wait_kernel, dim3(1), dim3(32), 0, static_cast<cudaStream_t>(stream), my_flags, world, seq,
+                             status, code));
   return DICE_OK;
 }
 
@@ -1019,7 +1032,12 @@ extern "C" int dice_ep_return_rows(const void* rows, const int32_t* meta, const 
                                    const void* const* peer_flags, uint32_t* done_counter, int hidden, int dtype,
                                    int rank, int world, int back_capacity_rows, int max_rows, uint32_t seq,
                                    int max_ctas, uint32_t* status, void* stream) {
+#ifdef DICE_FOLLOW_TRACE
+  g_push_kind[g_push_next & 1023] = max_ctas;
+  const FollowSpec none = {g_push_next++, nullptr, 0u, 0, nullptr, 0};
+#else
   const FollowSpec none = {nullptr, 0u, 0, nullptr, 0};
+#endif
   return return_rows(rows, meta, peer_back, peer_flags, done_counter, hidden, dtype, rank, world, back_capacity_rows,
                      max_rows, seq, max_ctas, status, stream, none);
 }
@@ -1032,11 +1050,34 @@ extern "C" int dice_ep_return_rows_following(const void* rows, const int32_t* me
   DICE_CHECK_ARG(rows_done && rows_done_ints > 0 && max_ctas > 0 && max_rows > 0, DICE_ERR_ARG);
   DICE_CHECK_ARG(n_seg > 0 && n_seg <= kMaxFollowSeg && world >= 1 && n_seg % world == 0, DICE_ERR_LIMIT);
   // every 256-row block of the GEMM's output takes part in ceil(hidden / 256) tiles
+#ifdef DICE_FOLLOW_TRACE
+  g_push_kind[g_push_next & 1023] = 1000 + max_ctas;
+  const FollowSpec follow = {g_push_next++, rows_done, static_cast<unsigned int>(kRowsDonePerTile * ((hidden + 255) / 256)),
+                             rows_done_ints, seg_slab, n_seg};
+#else
   const FollowSpec follow = {rows_done, static_cast<unsigned int>(kRowsDonePerTile * ((hidden + 255) / 256)),
                              rows_done_ints, seg_slab, n_seg};
+#endif
   return return_rows(rows, meta, peer_back, peer_flags, done_counter, hidden, DICE_BF16, rank, world,
                      back_capacity_rows, max_rows, seq, max_ctas, status, stream, follow);
 }
+
+#ifdef DICE_FOLLOW_TRACE
+extern "C" __attribute__((visibility("default"))) int dice_debug_push_trace(unsigned long long* out, int* kind) {
+  cudaDeviceSynchronize();
+  const int n = g_push_next < 1024 ? g_push_next : 1024;
+  if (out != nullptr) {
+    cudaMemcpyFromSymbol(out, g_push_trace, sizeof(unsigned long long) * 1024 * 8);
+    for (int i = 0; i < 1024; ++i) kind[i] = g_push_kind[i];
+  }
+  void* pt;
+  cudaGetSymbolAddress(&pt, g_push_trace);
+  unsigned long long init[8] = {~0ull, ~0ull, 0, 0, 0, 0, 0, 0};
+  for (int i = 0; i < 1024; ++i) cudaMemcpy(static_cast<unsigned long long*>(pt) + i * 8, init, sizeof(init), cudaMemcpyHostToDevice);
+  g_push_next = 0;
+  return n;
+}
+#endif
 
 // ---- CUDA IPC plumbing (set-up time only) ---------------------------------------------------
 extern "C" int dice_ipc_export(const void* ptr, uint8_t* out_handle64, uint64_t* out_offset) {

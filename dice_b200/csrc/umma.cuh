@@ -59,6 +59,9 @@ struct GemmParams {
   // when set (CTA-pair kernel, first problem only): every epilogue warp adds 1 to rows_done[m-block] after its
   // stores of a tile are visible, so that a concurrent kernel can follow the output block by block
   unsigned int* rows_done;
+#ifdef DICE_FOLLOW_TRACE
+  int trace_id;
+#endif
   // combine epilogue (CTA-pair kernel only): sorted position -> flat (token, slot) row, and the flat rows' gate weights
   const int* cmb_order;
   const float* cmb_weights;

@@ -187,7 +187,7 @@ def global_combine(grouped_dup_outp, token_counts_local, token_counts_global, as
     if isinstance(token_counts_global, p2p.SegInfo):
         if isinstance(grouped_dup_outp, p2p.ReturnedRows):  # the FFN kernel already returned the rows
             info = token_counts_global
-            handle = p2p.PeerHandle(info, 1, grouped_dup_outp.event)
+            handle = p2p.PeerHandle(info, 1, grouped_dup_outp.event, ordered=grouped_dup_outp.beside_ffn)
             if not async_op:
                 handle.wait()
             return info.xchg.back[info.slot][: info.rows_sent], [handle]
@@ -268,12 +268,14 @@ def proc_experts(inp, experts, token_counts_global, num_local_experts):
                 # synchronous exchange: the return push starts beside the FFN and follows its second GEMM
                 side = xchg.fork_to_comm()  # the push needs what is queued so far (the meta block), not the FFN
                 shared = (job.x, job.pack) if job is not None else None
+                returned = []
                 res = pack.run_offsets(inp, token_counts_global.seg_dev, xchg.seg_slab_dev,
                                        reserve_sms=p2p.follow_ctas(), shared=shared, inter=inter, out=out,
-                                       rows_done=xchg.rows_done)
+                                       rows_done=xchg.rows_done,
+                                       then=lambda: returned.append(xchg.follow_ffn(token_counts_global, out, side)))
                 if job is not None:
                     job.out = res[1]
-                return xchg.follow_ffn(token_counts_global, out, side)
+                return returned[0]
             if job is not None and inp.dtype == torch.bfloat16:
                 outp, job.out = pack.run_offsets(inp, token_counts_global.seg_dev, xchg.seg_slab_dev,
                                                  reserve_sms=p2p.reserve_sms(), shared=(job.x, job.pack), inter=inter, out=out)

@@ -168,7 +168,7 @@ class PeerExchange:
         self._side_events = [torch.cuda.Event() for _ in range(2 * n_slots)]
         self._ring_events = [torch.cuda.Event() for _ in range(self.FFN_OUT_RING)]
         self._ffn_inter, self._ffn_out, self._ffn_out_event, self._ffn_out_index, self._ffn_next = {}, [], [], {}, 0
-        self._comm = torch.cuda.Stream(device=self.device)
+        self._comm = torch.cuda.Stream(device=self.device, priority=_side_priority)
         self.comm_raw = self._comm.cuda_stream
         dist.barrier(group=group)
 
@@ -214,7 +214,9 @@ class PeerExchange:
             self.rows_done.data_ptr(), self.rows_done.numel(), self.seg_slab_dev.data_ptr(), self.n_seg, self.status_ptr,
             stream), "dice_ep_return_rows_following")
         self.note_output_read_on_side(out)
-        return ReturnedRows(info, self.record_side_event(slot, 1))
+        # no event for the consumer: the push raises this rank's own flag too when all its stores are out, and the
+        # combine waits for every source's flag on the device; an event wait would only cut the launch chain
+        return ReturnedRows(info, None, beside_ffn=True)
 
     def fork_to_comm(self) -> int:
         """Order the side stream (on which asynchronous pushes run next to the
@@ -319,6 +321,7 @@ def side_push_ctas() -> int:
 
 
 _side_ctas = int(os.environ.get("DICE_EP_P2P_SIDE_CTAS", "8"))  # read once: this is on the per-layer path
+_side_priority = int(os.environ.get("DICE_EP_P2P_SIDE_PRIORITY", "0"))  # CUDA stream priority of the side stream
 
 
 _side_pushes = False
@@ -461,9 +464,10 @@ class ReturnedRows:
 
     keepalive = None
 
-    def __init__(self, info: SegInfo, event=None):
+    def __init__(self, info: SegInfo, event=None, beside_ffn: bool = False):
         self.info = info
         self.event = event
+        self.beside_ffn = beside_ffn  # a push on the side stream is still running beside the FFN
 
 
 class PeerHandle:
@@ -472,8 +476,11 @@ class PeerHandle:
     on the device) until every source raised this exchange's flag;
     ``is_completed`` tells whether this rank's own push has left its buffers."""
 
-    def __init__(self, info: SegInfo, which: int, event: Optional[torch.cuda.Event]):
+    def __init__(self, info: SegInfo, which: int, event: Optional[torch.cuda.Event], ordered: bool = False):
         self.info, self.which, self.event = info, which, event
+        # behind an FFN that shares the GPU with a push of the side stream the wait kernel is launched in plain
+        # stream order, so that neither it nor the kernels after it become resident on the SMs left to the push
+        self.ordered = ordered
 
     def wait(self) -> None:
         from ..ops import _stream
@@ -492,7 +499,8 @@ class PeerHandle:
                 x.n_experts, x.region_rows, self.info.seq, x.status.data_ptr(), _stream()), "dice_ep_wait_dispatch")
             return
         _lib.check(x.lib.dice_ep_wait_flags(x.my_flags_ptr(self.info.slot, 1 + self.which), x.world, self.info.seq,
-                                            self.which, x.status.data_ptr(), _stream()), "dice_ep_wait_flags")
+                                            self.which + (2 if self.ordered else 0), x.status.data_ptr(), _stream()),
+                   "dice_ep_wait_flags")
 
     def is_completed(self) -> bool:
         return self.event is None or self.event.query()

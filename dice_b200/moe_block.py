@@ -263,10 +263,12 @@ class ExpertPack:
         return self.get(dtype)[1]
 
     def run_offsets(self, rows: torch.Tensor, seg_offsets: torch.Tensor, seg_slab: Optional[torch.Tensor] = None,
-                    reserve_sms: int = 0, shared=None, inter=None, out=None, rows_done=None):
+                    reserve_sms: int = 0, shared=None, inter=None, out=None, rows_done=None, then=None):
         """The grouped FFN over ``rows``.  ``shared = (tokens, pack of the shared expert)`` lets the shared expert
         ride in the same launches (bf16); the result is then ``(rows_out, shared_out)``.  ``inter`` / ``out`` are
-        caller-owned buffers for the intermediate and the result (allocated per call when None)."""
+        caller-owned buffers for the intermediate and the result (allocated per call when None).  ``then()`` is
+        called right after the launches (before anything else is recorded on the stream): the place for work on
+        another stream that should start beside them."""
         act, ffn, w1, w2 = self.get(rows.dtype)
         extra = None
         if shared is not None:
@@ -275,12 +277,17 @@ class ExpertPack:
             assert s_act == act
             extra = (sx, sw1, sw2, s_ffn)
         if not ExpertPack._want_timing():
-            return ops.grouped_ffn(rows, w1, w2, seg_offsets, act, ffn, status=self.status, seg_slab=seg_slab,
-                                   reserve_sms=reserve_sms, shared=extra, inter=inter, out=out, rows_done=rows_done)
+            res = ops.grouped_ffn(rows, w1, w2, seg_offsets, act, ffn, status=self.status, seg_slab=seg_slab,
+                                  reserve_sms=reserve_sms, shared=extra, inter=inter, out=out, rows_done=rows_done)
+            if then is not None:
+                then()
+            return res
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         start.record()
         res = ops.grouped_ffn(rows, w1, w2, seg_offsets, act, ffn, status=self.status, seg_slab=seg_slab,
                               reserve_sms=reserve_sms, shared=extra, inter=inter, out=out, rows_done=rows_done)
+        if then is not None:
+            then()
         end.record()
         ExpertPack.timing.append((self.tag if shared is None else self.tag + "+shared", start, end))
         return res

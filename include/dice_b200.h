@@ -376,7 +376,10 @@ DICE_API int dice_ep_wait_dispatch(const uint32_t* my_flags, const int32_t* my_m
                           int world, int n_experts, int region_rows, uint32_t seq, uint32_t* status,
                           void* stream);
 /* wait (bounded) until every source raised flag >= seq, then look at the
- * sources' failure marks; what: 0 dispatch, 1 combine */
+ * sources' failure marks; what: 0 dispatch, 1 combine; + 2: the kernel is
+ * launched in plain stream order (it, and what follows it in the stream, does
+ * not become resident while the kernel before it runs: needed behind an FFN
+ * that leaves SMs free for dice_ep_return_rows_following) */
 DICE_API int dice_ep_wait_flags(const uint32_t* my_flags, int world, uint32_t seq, int what,
                        uint32_t* status, void* stream);
 /* expert outputs back to the token owners, in the order the rows were sent
