@@ -54,7 +54,8 @@ SIGNATURES = {
     "dice_grouped_ffn": (
         c_int,
         [c_void_p, c_int64, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p,
-         c_void_p, c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p],
+         c_void_p, c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+         c_void_p],
     ),
     "dice_grouped_ffn_combine": (
         c_int,

@@ -508,15 +508,21 @@ extern "C" int dice_grouped_ffn(const void* rows_in, int64_t n_rows, int hidden,
                                 const void* w2, int n_slabs, const int32_t* seg_offsets, const int32_t* seg_slab,
                                 int n_seg, void* inter, void* rows_out, const void* shared_in, int64_t n_shared,
                                 int shared_ffn, const void* shared_w1, const void* shared_w2, void* shared_inter,
-                                void* shared_out, int reserve_sms, uint32_t* rows_done, uint32_t* status,
-                                void* stream) {
+                                void* shared_out, int reserve_sms, uint32_t* rows_done, void* first_gemm_done,
+                                uint32_t* status, void* stream) {
   DICE_CHECK_ARG(act == DICE_ACT_SWIGLU || act == DICE_ACT_GELU_TANH, DICE_ERR_ARG);
   DICE_CHECK_ARG(hidden > 0 && ffn > 0 && reserve_sms >= 0, DICE_ERR_ARG);
   // counting finished blocks of the output is the CTA-pair kernel's; a caller that asked for it waits on the counters
   if (rows_done != nullptr) DICE_CHECK_ARG(use_cta_pairs() && n_rows > 0 && n_seg > 0, DICE_ERR_ARG);
-  // the push that follows the second GEMM is launched after this call and cannot start before the first GEMM has
-  // ended: only the second GEMM leaves SMs free for it
-  const int reserve1 = rows_done != nullptr ? 0 : reserve_sms;
+  // the push that follows the second GEMM waits for `first_gemm_done`: only the second GEMM leaves SMs free for it
+  DICE_CHECK_ARG(first_gemm_done == nullptr || rows_done != nullptr, DICE_ERR_ARG);
+  const int reserve1 = first_gemm_done != nullptr ? 0 : reserve_sms;
+  auto mark_first_done = [&]() -> int {
+    if (first_gemm_done == nullptr) return DICE_OK;
+    return cudaEventRecord(static_cast<cudaEvent_t>(first_gemm_done), static_cast<cudaStream_t>(stream)) == cudaSuccess
+               ? DICE_OK
+               : DICE_ERR_CUDA;
+  };
   if (n_rows > 0 && n_seg > 0) DICE_CHECK_ARG(inter != nullptr, DICE_ERR_ARG);
   const int epi1 = act == DICE_ACT_SWIGLU ? DICE_EPI_SWIGLU : DICE_EPI_GELU_TANH;
   const int64_t w1_rows = act == DICE_ACT_SWIGLU ? dice_w13_rows(ffn) : ffn;
@@ -524,6 +530,7 @@ extern "C" int dice_grouped_ffn(const void* rows_in, int64_t n_rows, int hidden,
     int rc = dice_grouped_gemm(rows_in, n_rows, hidden, w1, n_slabs, w1_rows, seg_offsets, seg_slab, n_seg, epi1, inter,
                                ffn, ffn, reserve1, status, stream);
     if (rc != DICE_OK) return rc;
+    if ((rc = mark_first_done()) != DICE_OK) return rc;
     if (rows_done != nullptr) {
       DICE_CHECK_ARG(n_seg <= kMaxSeg && n_rows < 0x7fffff00LL && hidden % 8 == 0 && ffn % 8 == 0, DICE_ERR_LIMIT);
       DICE_CHECK_ARG(w2 && rows_out && dice_aligned16(w2) && dice_aligned16(rows_out), DICE_ERR_ALIGN);
@@ -561,6 +568,7 @@ extern "C" int dice_grouped_ffn(const void* rows_in, int64_t n_rows, int hidden,
   int rc = dice_internal_gemm_pair(rows_in, n_rows, hidden, w1, n_slabs, w1_rows, seg_offsets, seg_slab, n_seg, epi1, inter,
                                    ffn, ffn, reserve1, status, s, nullptr, &x1);
   if (rc != DICE_OK) return rc;
+  if ((rc = mark_first_done()) != DICE_OK) return rc;
   DiceDenseSpec x2 = {shared_inter, n_shared, shared_ffn, shared_w2, hidden, shared_out, hidden, hidden};
   return dice_internal_gemm_pair(inter, n_rows, ffn, w2, n_slabs, hidden, seg_offsets, seg_slab, n_seg, DICE_EPI_STORE,
                                  rows_out, hidden, hidden, reserve_sms, status, s, nullptr, &x2, nullptr, rows_done);

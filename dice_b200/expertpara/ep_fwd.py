@@ -266,13 +266,12 @@ def proc_experts(inp, experts, token_counts_global, num_local_experts):
             if (out is not None and inp.dtype == torch.bfloat16 and p2p.return_follows() and p2p.reserve_sms() == 0
                     and xchg.rows_done is not None):
                 # synchronous exchange: the return push starts beside the FFN and follows its second GEMM
-                side = xchg.fork_to_comm()  # the push needs what is queued so far (the meta block), not the FFN
                 shared = (job.x, job.pack) if job is not None else None
                 returned = []
                 res = pack.run_offsets(inp, token_counts_global.seg_dev, xchg.seg_slab_dev,
                                        reserve_sms=p2p.follow_ctas(), shared=shared, inter=inter, out=out,
-                                       rows_done=xchg.rows_done,
-                                       then=lambda: returned.append(xchg.follow_ffn(token_counts_global, out, side)))
+                                       rows_done=xchg.rows_done, first_gemm_done=xchg._fork,
+                                       then=lambda: returned.append(xchg.follow_ffn(token_counts_global, out)))
                 if job is not None:
                     job.out = res[1]
                 return returned[0]

@@ -165,6 +165,7 @@ class PeerExchange:
             self.rows_done = torch.zeros(self.capacity_rows // 256 + len(self.seg_slab) + 1, dtype=torch.int32,
                                          device=self.device)
         self._fork = torch.cuda.Event()
+        self._fork.record()  # torch creates the CUDA event at its first record; the C side is handed its handle
         self._side_events = [torch.cuda.Event() for _ in range(2 * n_slots)]
         self._ring_events = [torch.cuda.Event() for _ in range(self.FFN_OUT_RING)]
         self._ffn_inter, self._ffn_out, self._ffn_out_event, self._ffn_out_index, self._ffn_next = {}, [], [], {}, 0
@@ -199,14 +200,16 @@ class PeerExchange:
         self.seq[slot] += 1
         return slot, self.seq[slot], self._tables[slot]
 
-    def follow_ffn(self, info: "SegInfo", out: torch.Tensor, stream: int) -> "ReturnedRows":
+    def follow_ffn(self, info: "SegInfo", out: torch.Tensor) -> "ReturnedRows":
         """Launch, on the side stream, the return push that follows the expert FFN just launched on the current
-        stream with ``rows_done=self.rows_done`` into ``out``.  ``stream``: what ``fork_to_comm`` returned BEFORE
-        the FFN was launched (the push only needs this exchange's meta block, not the FFN).  The push is launched
-        after its producer, so that it never waits for a kernel the host has yet to launch (a first launch may load
-        its module, which can wait for running kernels)."""
+        stream with ``rows_done=self.rows_done, first_gemm_done=self._fork`` into ``out``.  The side stream waits
+        for the first GEMM, which had the whole GPU; the push then takes the SMs that the second GEMM leaves free.
+        The push is launched after its producer, so that it never waits for a kernel the host has yet to launch
+        (a first launch may load its module, which can wait for running kernels)."""
         from .._lib import check
 
+        self._comm.wait_event(self._fork)
+        stream = self.comm_raw
         tab, slot = info.tab, info.slot
         check(self.lib.dice_ep_return_rows_following(
             out.data_ptr(), self._meta_ptrs[slot], tab["back"], tab["f_back"], self._done_ptrs[2 * slot + 1], self.hidden,
@@ -344,7 +347,7 @@ def reserve_sms() -> int:
 
 
 _fused_return = os.environ.get("DICE_EP_P2P_FUSED_RETURN", "0") == "1"
-_return_follows = os.environ.get("DICE_EP_P2P_RETURN_FOLLOWS", "0") == "1"
+_return_follows = os.environ.get("DICE_EP_P2P_RETURN_FOLLOWS", "1") == "1"
 
 
 def set_return_follows(flag: bool) -> None:

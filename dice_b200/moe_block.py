@@ -263,7 +263,8 @@ class ExpertPack:
         return self.get(dtype)[1]
 
     def run_offsets(self, rows: torch.Tensor, seg_offsets: torch.Tensor, seg_slab: Optional[torch.Tensor] = None,
-                    reserve_sms: int = 0, shared=None, inter=None, out=None, rows_done=None, then=None):
+                    reserve_sms: int = 0, shared=None, inter=None, out=None, rows_done=None, first_gemm_done=None,
+                    then=None):
         """The grouped FFN over ``rows``.  ``shared = (tokens, pack of the shared expert)`` lets the shared expert
         ride in the same launches (bf16); the result is then ``(rows_out, shared_out)``.  ``inter`` / ``out`` are
         caller-owned buffers for the intermediate and the result (allocated per call when None).  ``then()`` is
@@ -278,14 +279,16 @@ class ExpertPack:
             extra = (sx, sw1, sw2, s_ffn)
         if not ExpertPack._want_timing():
             res = ops.grouped_ffn(rows, w1, w2, seg_offsets, act, ffn, status=self.status, seg_slab=seg_slab,
-                                  reserve_sms=reserve_sms, shared=extra, inter=inter, out=out, rows_done=rows_done)
+                                  reserve_sms=reserve_sms, shared=extra, inter=inter, out=out, rows_done=rows_done,
+                                  first_gemm_done=first_gemm_done)
             if then is not None:
                 then()
             return res
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         start.record()
         res = ops.grouped_ffn(rows, w1, w2, seg_offsets, act, ffn, status=self.status, seg_slab=seg_slab,
-                              reserve_sms=reserve_sms, shared=extra, inter=inter, out=out, rows_done=rows_done)
+                              reserve_sms=reserve_sms, shared=extra, inter=inter, out=out, rows_done=rows_done,
+                              first_gemm_done=first_gemm_done)
         if then is not None:
             then()
         end.record()

@@ -428,6 +428,17 @@ def grouped_gemm(
     return out
 
 
+def _event_handle(event: Optional[torch.cuda.Event]):
+    """The cudaEvent_t behind a torch event (torch creates it at the first record)."""
+    if event is None:
+        return None
+    handle = event.cuda_event
+    handle = getattr(handle, "value", handle)
+    if not handle:
+        raise RuntimeError("the event has never been recorded: torch has not created its CUDA event yet")
+    return handle
+
+
 def grouped_ffn(
     rows: torch.Tensor,
     w1: torch.Tensor,
@@ -442,6 +453,7 @@ def grouped_ffn(
     reserve_sms: int = 0,
     shared=None,
     rows_done: Optional[torch.Tensor] = None,
+    first_gemm_done: Optional[torch.cuda.Event] = None,
 ):
     """Expert FFN over expert-sorted rows (ep_fwd.py:199-211; models.py:368-376).
 
@@ -456,7 +468,8 @@ def grouped_ffn(
 
     ``rows_done`` (bf16 only): zeroed int32 counters, one per 256-row block of
     the output, that the second GEMM raises as blocks complete (a return push
-    on another stream follows them)."""
+    on another stream follows them); ``first_gemm_done``: an event recorded
+    between the two GEMMs (that push's stream waits for it)."""
     _require_cuda(rows, w1, w2, seg_offsets, status, seg_slab, inter, out, rows_done)
     assert rows.is_contiguous() and w1.is_contiguous() and w2.is_contiguous()
     assert seg_offsets.dtype == torch.int32
@@ -486,7 +499,8 @@ def grouped_ffn(
             lib.dice_grouped_ffn(
                 _ptr(rows), n_rows, h, ffn, ACT_CODES[act], _ptr(w1), _ptr(w2), n_slabs, _ptr(seg_offsets),
                 _ptr(seg_slab), n_seg, _ptr(inter), _ptr(out), _ptr(sx), n_shared, s_ffn, _ptr(sw1), _ptr(sw2),
-                _ptr(s_inter), _ptr(s_out), reserve_sms, _ptr(rows_done), _ptr(status), _stream(),
+                _ptr(s_inter), _ptr(s_out), reserve_sms, _ptr(rows_done),
+                _event_handle(first_gemm_done), _ptr(status), _stream(),
             ),
             "dice_grouped_ffn",
         )

@@ -270,15 +270,19 @@ DICE_API int dice_grouped_gemm(const void* a, int64_t n_rows, int k_dim, const v
  *              block's counter after its stores are visible device-wide, so a
  *              block is complete at 16 * ceil(hidden / 256).  A kernel on another
  *              stream (dice_ep_return_rows_following) can then send rows on
- *              while later blocks are still being computed.  With rows_done
- *              only the second GEMM leaves reserve_sms SMs free.
+ *              while later blocks are still being computed.
+ *   first_gemm_done  NULL, or (with rows_done) a cudaEvent_t that is recorded on
+ *              `stream` between the two GEMMs; then only the second GEMM leaves
+ *              reserve_sms SMs free.  The stream of the following push waits
+ *              for this event, so that the push takes its SMs when the first
+ *              GEMM has left them, not before.
  */
 DICE_API int dice_grouped_ffn(const void* rows_in, int64_t n_rows, int hidden, int ffn, int act, const void* w1,
                      const void* w2, int n_slabs, const int32_t* seg_offsets, const int32_t* seg_slab,
                      int n_seg, void* inter, void* rows_out, const void* shared_in, int64_t n_shared,
                      int shared_ffn, const void* shared_w1, const void* shared_w2, void* shared_inter,
-                     void* shared_out, int reserve_sms, uint32_t* rows_done, uint32_t* status,
-                     void* stream);
+                     void* shared_out, int reserve_sms, uint32_t* rows_done, void* first_gemm_done,
+                     uint32_t* status, void* stream);
 
 /* The expert FFN whose second GEMM also does the weighted combine
  * (models.py:377-381: mul_ by the gate weights, scatter_reduce_ into the token
@@ -390,11 +394,11 @@ DICE_API int dice_ep_return_rows(const void* rows, const int32_t* meta, const vo
                         int rank, int world, int back_capacity_rows, int max_rows, uint32_t seq,
                         int max_ctas, uint32_t* status, void* stream);
 /* The same return (bf16 rows, bulk-copy form on max_ctas > 0 CTAs), launched on a
- * second stream right AFTER dice_grouped_ffn(..., rows_done) was launched with
- * reserve_sms >= max_ctas (after its producer, so that the push never depends
- * on a launch the host has yet to make: the first launch of a kernel may load
- * its module, which can wait for running kernels; the second stream only has to
- * be ordered after the kernel that completed `meta`).  A chunk of rows leaves as
+ * second stream right AFTER dice_grouped_ffn(..., rows_done, first_gemm_done)
+ * was launched with reserve_sms >= max_ctas, the second stream waiting for
+ * first_gemm_done (after its producer, so that the push never depends on a
+ * launch the host has yet to make: the first launch of a kernel may load its
+ * module, which can wait for running kernels).  A chunk of rows leaves as
  * soon as the blocks of the
  * second GEMM's output that it lies in are complete, so that the transfer of the
  * synchronous all-to-all (ep_fwd.py:326-340) hides under the GEMM that produces

@@ -47,7 +47,7 @@ def test_argument_errors_are_reported_on_the_host():
     assert lib.dice_grouped_gemm(None, 4, 60, None, 1, 32, None, None, 1, 0, None, 32, 32, 0, None, None) == -2
     assert lib.dice_grouped_gemm(None, 4, 64, None, 1, 32, None, None, 300, 0, None, 32, 32, 0, None, None) == -7
     assert lib.dice_grouped_ffn(None, 4, 64, 64, 5, None, None, 1, None, None, 1, None, None, None, 0, 0, None, None, None, None, 0, None,
-                                None, None) == -1
+                                None, None, None) == -1
 
 
 def test_missing_library_fails_loudly(monkeypatch, tmp_path):

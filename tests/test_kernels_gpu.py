@@ -915,8 +915,9 @@ def test_ffn_with_fused_return_world_of_one(cuda_device):
         assert bool((back[2 * n:] == 0).all()) and int(done.sum()) == 0
 
 
+@pytest.mark.parametrize("world", [2, 4, 8])
 @pytest.mark.parametrize("layout", ["regions", "packed"])
-def test_return_push_that_follows_the_second_gemm(cuda_device, layout):
+def test_return_push_that_follows_the_second_gemm(cuda_device, layout, world):
     """The return of a synchronous exchange launched on a second stream BEFORE the expert FFN: it sends a chunk of
     rows once the second GEMM has counted the 256-row blocks it lies in as complete.  `world` ranks whose buffers
     share this GPU, skewed routing, real expert weights; every rank must get back exactly what an FFN followed by an
@@ -925,9 +926,9 @@ def test_return_push_that_follows_the_second_gemm(cuda_device, layout):
 
     ops = _ops()
     lib = _lib.load()
-    world, e, h, ffn, k = 2, 8, 256, 512, 2
+    e, h, ffn, k = 8, 256, 512, 2
     el = e // world
-    n = [900, 1100]
+    n = [900 + 57 * r for r in range(world)]
     region = k * max(n) if layout == "regions" else 0
     cap = world * k * max(n)
     R = _EmulatedRanks(world, e, h, cap, k * max(n), cuda_device, lib)
@@ -940,13 +941,15 @@ def test_return_push_that_follows_the_second_gemm(cuda_device, layout):
     rows_done = torch.zeros(cap // 256 + n_seg + 1, dtype=torch.int32, device=cuda_device)
     status = ops.device_status(cuda_device)
     main, side = torch.cuda.current_stream(), torch.cuda.Stream()
+    between = torch.cuda.Event()
+    between.record()  # torch creates the CUDA event at the first record
     st = main.cuda_stream
     matrices = R.table([c.data_ptr() for c in R.ctrl])
     seg_base = 2 + 4 * world + 1
     for seq in (1, 2):
         xs, poss, segs = _emulated_inputs(world, e, h, n, k, cuda_device, seed=50 + seq, hot_owner=1)
         seg_host = [s.cpu().tolist() for s in segs]
-        if not region:
+        if not region:  # (the packed layout's capacity here is the lossless one too, so the skew fits)
             R.publish_counts(seg_host, seq)
             for r in range(world):
                 assert lib.dice_ep_exchange_counts(segs[r].data_ptr(), matrices, R.flags(0), R.meta[r].data_ptr(), r, world,
@@ -981,15 +984,26 @@ def test_return_push_that_follows_the_second_gemm(cuda_device, layout):
         for r in range(world):
             out = torch.zeros(cap, h, dtype=torch.bfloat16, device=cuda_device)
             seg_dev = R.meta[r][seg_base: seg_base + n_seg + 1]
-            side.wait_stream(main)
-            # the push is launched FIRST here, so that it really has to wait for the GEMM (whose kernel is already
-            # loaded: the FFN above ran it); the product launches it right after the FFN
-            assert lib.dice_ep_return_rows_following(
-                out.data_ptr(), R.meta[r].data_ptr(), R.table([t.data_ptr() for t in R.back]), R.flags(2),
-                R.done[r][1:].data_ptr(), h, r, world, R.back_cap, cap, seq, 4, rows_done.data_ptr(), rows_done.numel(),
-                seg_slab.data_ptr(), n_seg, R.status[r].data_ptr(), side.cuda_stream) == 0
-            got = ops.grouped_ffn(R.recv[r][:cap], w1, w2, seg_dev, "gelu_tanh", ffn, status=status, seg_slab=seg_slab,
-                                  out=out, reserve_sms=4, rows_done=rows_done)
+            def push():
+                assert lib.dice_ep_return_rows_following(
+                    out.data_ptr(), R.meta[r].data_ptr(), R.table([t.data_ptr() for t in R.back]), R.flags(2),
+                    R.done[r][1:].data_ptr(), h, r, world, R.back_cap, cap, seq, 4, rows_done.data_ptr(), rows_done.numel(),
+                    seg_slab.data_ptr(), n_seg, R.status[r].data_ptr(), side.cuda_stream) == 0
+
+            if seq == 1:
+                # the push is launched FIRST, so that it really has to wait for the GEMM (whose kernel is already
+                # loaded: the FFN above ran it)
+                side.wait_stream(main)
+                push()
+                got = ops.grouped_ffn(R.recv[r][:cap], w1, w2, seg_dev, "gelu_tanh", ffn, status=status, seg_slab=seg_slab,
+                                      out=out, reserve_sms=4, rows_done=rows_done)
+            else:
+                # the product's order: FFN first (its first GEMM on all SMs), the push's stream waits for the event
+                # between the two GEMMs
+                got = ops.grouped_ffn(R.recv[r][:cap], w1, w2, seg_dev, "gelu_tanh", ffn, status=status, seg_slab=seg_slab,
+                                      out=out, reserve_sms=4, rows_done=rows_done, first_gemm_done=between)
+                side.wait_event(between)
+                push()
             main.wait_stream(side)  # the next rank's FFN counts into the same counters
             assert got.data_ptr() == out.data_ptr()
         for r in range(world):
