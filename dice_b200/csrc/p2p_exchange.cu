@@ -555,16 +555,16 @@ ep_dispatch_bulk_kernel(const uint8_t* __restrict__ x, const int* __restrict__ p
   signal_when_grid_done(done_counter, flags, rank, world, seq, &s_fail);
 }
 
-// What a return push needs to FOLLOW a running second GEMM: the GEMM counts, per 256-row block of its tile list, the
-// epilogue warps that have stored a tile (rows_done); a block is complete at `target`.  The push derives the same
-// block numbering from the segment table, waits (bounded) for the blocks a chunk of rows lies in, and only then
-// copies the chunk; when the grid is done its last CTA clears the counters for the next use.
 #ifdef DICE_FOLLOW_TRACE
 // debug build only: per launch of the bulk return: first start, first chunk ready (min); half, last ready, done (max)
 __device__ unsigned long long g_push_trace[1024][8];
 static int g_push_next = 0;
 static int g_push_kind[1024];
 #endif
+// What a return push needs to FOLLOW a running second GEMM: the GEMM counts, per 256-row block of its tile list, the
+// epilogue warps that have stored a tile (rows_done); a block is complete at `target`.  The push derives the same
+// block numbering from the segment table, waits (bounded) for the blocks up to the one a chunk of rows ends in, and
+// only then copies the chunk; when the grid is done its last CTA clears the counters for the next use.
 struct FollowSpec {
 #ifdef DICE_FOLLOW_TRACE
   int trace_id;

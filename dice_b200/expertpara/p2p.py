@@ -356,6 +356,7 @@ def set_return_follows(flag: bool) -> None:
 
 
 _follow_ctas = int(os.environ.get("DICE_EP_P2P_FOLLOW_CTAS", "16"))
+_pair_gemm = os.environ.get("DICE_GEMM_PAIR", "1") != "0"  # only the CTA-pair GEMM counts finished blocks
 
 
 def follow_ctas() -> int:
@@ -370,7 +371,7 @@ def return_follows() -> bool:
     side stream together with the expert FFN and sends each chunk of rows as
     soon as the second GEMM has finished the blocks it lies in (the reference
     runs FFN and all-to-all one after the other, ep_fwd.py:375-381)."""
-    return _return_follows and _follow_ctas > 0
+    return _return_follows and _follow_ctas > 0 and _pair_gemm
 
 
 def set_fused_return(flag: bool) -> None:

@@ -1015,3 +1015,56 @@ def test_return_push_that_follows_the_second_gemm(cuda_device, layout, world):
             ops.check_status(R.status[r])
             assert torch.equal(R.back[r][: k * n[r]], want[r]), f"rank {r}: rows differ from FFN + ordinary return"
             assert bool((R.back[r][k * n[r]:] == 5.0).all())
+
+
+def test_following_push_gives_up_when_no_block_completes(cuda_device):
+    """Failure detection without a fault: the return push that follows a GEMM is launched, but nothing ever counts
+    a block of the output as complete.  Every ring's bounded wait runs out, the push records the expired wait,
+    moves no row, marks its flags as failed, and the rank that waits for the rows records "a peer rank reported"."""
+    import time
+
+    from dice_b200 import _lib
+
+    ops = _ops()
+    lib = _lib.load()
+    world, e, h, k = 2, 8, 256, 2
+    el = e // world
+    n = [600, 640]
+    region = k * max(n)
+    cap = world * region
+    R = _EmulatedRanks(world, e, h, cap, region, cuda_device, lib)
+    n_seg = world * (el + 1)
+    seg_slab = torch.tensor([i for _ in range(world) for i in (list(range(el)) + [-1])], dtype=torch.int32,
+                            device=cuda_device)
+    rows_done = torch.zeros(cap // 256 + n_seg + 1, dtype=torch.int32, device=cuda_device)
+    st = torch.cuda.current_stream().cuda_stream
+    matrices = R.table([c.data_ptr() for c in R.ctrl])
+    xs, poss, segs = _emulated_inputs(world, e, h, n, k, cuda_device, seed=61)
+    seq = 1
+    for r in range(world):
+        assert lib.dice_ep_dispatch_rows(xs[r].data_ptr(), poss[r].data_ptr(), segs[r].data_ptr(), None,
+                                         R.table([t.data_ptr() for t in R.recv]), R.flags(1), R.done[r].data_ptr(), n[r], k,
+                                         h, 0, r, world, e, cap, seq, 0, region, matrices, R.status[r].data_ptr(), st) == 0
+    for r in range(world):
+        assert lib.dice_ep_wait_dispatch(R.my_flags(r, 1), R.ctrl[r].data_ptr(), R.meta[r].data_ptr(), r, world, e, region,
+                                         seq, R.status[r].data_ptr(), st) == 0
+    torch.cuda.synchronize()
+    for r in range(world):
+        ops.check_status(R.status[r])
+    out = torch.zeros(cap, h, dtype=torch.bfloat16, device=cuda_device)
+    t0 = time.time()
+    assert lib.dice_ep_return_rows_following(out.data_ptr(), R.meta[0].data_ptr(), R.table([t.data_ptr() for t in R.back]),
+                                             R.flags(2), R.done[0][1:].data_ptr(), h, 0, world, R.back_cap, cap, seq, 4,
+                                             rows_done.data_ptr(), rows_done.numel(), seg_slab.data_ptr(), n_seg,
+                                             R.status[0].data_ptr(), st) == 0
+    # rank 1's own return to itself is played by hand, so that only rank 0's mark matters to its wait
+    R.ctrl[1][R.flag_base + 128 + 1] = seq
+    assert lib.dice_ep_wait_flags(R.my_flags(1, 2), world, seq, 1, R.status[1].data_ptr(), st) == 0
+    torch.cuda.synchronize()
+    assert 1.0 < time.time() - t0 < 15.0
+    with pytest.raises(RuntimeError, match="expert outputs that a return push follows"):
+        ops.check_status(R.status[0])
+    with pytest.raises(RuntimeError, match="peer rank reported"):
+        ops.check_status(R.status[1])
+    assert bool((R.back[0] == 5.0).all()) and bool((R.back[1] == 5.0).all()), "no row may have moved"
+    assert int(rows_done.abs().sum()) == 0
