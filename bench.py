@@ -702,6 +702,12 @@ def run_ours(args):
         "clocks": clocks, "roofline": roofline, "roofline_hbm": roofline_hbm,
         "tokens_per_s_per_gpu": round(value / world, 1), "host_us_per_layer": round(host_us, 1),
     }
+    if ep and exchange != "nccl":
+        x = p2p._exchange
+        follows = p2p.return_follows() and x.rows_done is not None
+        line["config"]["receive_layout"] = "regions (no count exchange)" if x.region_rows else "packed (count exchange)"
+        line["config"]["return_of_a_sync_exchange"] = (
+            f"follows the second GEMM on {p2p.follow_ctas()} CTAs" if follows else "after the FFN, on all SMs")
     if ep_parity is not None:
         line["ep_parity"] = ep_parity
         line["load"] = load

@@ -124,7 +124,6 @@ ep_counts_kernel(const int* __restrict__ seg_offsets,  // [E+1] this rank's key-
   __shared__ int s_cnt[kMaxRanks][kMaxKeys];
   __shared__ int s_ok;
   const int el = n_keys / world;
-  pdl_trigger();
   pdl_wait();
   if (threadIdx.x == 0) s_ok = 1;
   // publish my row everywhere (my own matrix included)
@@ -140,6 +139,7 @@ ep_counts_kernel(const int* __restrict__ seg_offsets,  // [E+1] this rank's key-
     if (!wait_flag(my_flags + threadIdx.x, seq, status, DICE_STATUS_WAIT_PEER_COUNTS)) s_ok = 0;
   }
   __syncthreads();
+  pdl_trigger();  // only now (see ep_wait_kernel)
   for (int i = threadIdx.x; i < world * n_keys; i += blockDim.x)
     s_cnt[i / n_keys][i % n_keys] = s_ok ? my_matrix[i] : 0;
   __syncthreads();
@@ -295,13 +295,18 @@ ep_dispatch_kernel(const uint4* __restrict__ x, const int* __restrict__ pos, con
 // ---- 3. wait for all sources ------------------------------------------------------------
 __global__ void ep_wait_kernel(const uint32_t* __restrict__ my_flags, int world, uint32_t seq, uint32_t* status,
                                uint32_t code) {
-  pdl_trigger();
   pdl_wait();
   if (threadIdx.x < world) {
     if (wait_flag(my_flags + threadIdx.x, seq, status, code) &&
         ld_acquire_sys(my_flags + kFailMarkBase + threadIdx.x) == seq && status != nullptr)
       atomicCAS(status, 0u, DICE_STATUS_PEER_FAILED);  // the source says its rows are incomplete
   }
+  __syncwarp();
+  // The kernels behind this one may become resident only NOW, not while it spins: their blocks, parked in
+  // griddepcontrol.wait, hold shared memory and thread slots on every SM, and a push of another stream of THIS GPU
+  // that the flags depend on (the return that follows the second GEMM, queued behind earlier pushes) would find no
+  // SM to start on.  That cycle ended only when the bounded wait ran out.
+  pdl_trigger();
 }
 
 // Region layout: wait for every source's rows, then derive the meta block from the count matrix the sources
@@ -312,7 +317,6 @@ ep_wait_dispatch_kernel(const uint32_t* __restrict__ my_flags, const int* __rest
   __shared__ int s_cnt[kMaxRanks][kMaxKeys];
   __shared__ int s_ok;
   const int el = n_keys / world;
-  pdl_trigger();
   pdl_wait();
   if (threadIdx.x == 0) s_ok = 1;
   __syncthreads();
@@ -325,6 +329,7 @@ ep_wait_dispatch_kernel(const uint32_t* __restrict__ my_flags, const int* __rest
     }
   }
   __syncthreads();
+  pdl_trigger();  // only now: nothing behind this kernel becomes resident while it spins (see ep_wait_kernel)
   for (int i = threadIdx.x; i < world * n_keys; i += blockDim.x)
     s_cnt[i / n_keys][i % n_keys] = s_ok ? my_matrix[i] : 0;
   __syncthreads();
@@ -521,7 +526,7 @@ ep_dispatch_bulk_kernel(const uint8_t* __restrict__ x, const int* __restrict__ p
     const int64_t k = j - lag;
     if (k >= 0) {
       const int b = static_cast<int>(k % bufs);
-      // the same verdict in every lane, so that the warp leaves the loop together
+      // the same decision in every lane, so that the warp leaves the loop together
       if (!__all_sync(0xffffffffu, bulk_bar_wait(smem_addr32(&bars[b]), static_cast<uint32_t>((k / bufs) & 1), kBulkWaitLimitNs))) {
         if (status != nullptr) atomicCAS(status, 0u, DICE_STATUS_WAIT_SMEM_FULL);
         if (lane == 0) {

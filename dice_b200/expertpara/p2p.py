@@ -161,7 +161,9 @@ class PeerExchange:
         self.seg_slab_dev = torch.tensor(self.seg_slab, dtype=torch.int32, device=self.device)
         # finished 256-row blocks of the expert FFN's output (see follow_ffn); None where the kernels have no counters
         self.rows_done = None
-        if self.dtype == torch.bfloat16 and len(self.seg_slab) <= 256:
+        row_bytes = self.hidden * 2
+        bulk = os.environ.get("DICE_EP_P2P_BULK", "1") != "0" and row_bytes % 16 == 0 and row_bytes <= 16384
+        if self.dtype == torch.bfloat16 and len(self.seg_slab) <= 256 and bulk:  # (the push follows in its bulk form)
             self.rows_done = torch.zeros(self.capacity_rows // 256 + len(self.seg_slab) + 1, dtype=torch.int32,
                                          device=self.device)
         self._fork = torch.cuda.Event()
