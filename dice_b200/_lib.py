@@ -80,6 +80,7 @@ SIGNATURES = {
         c_int,
         [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_uint32, c_int,
          c_void_p, c_void_p]),
+    "dice_ep_set_wait_limit_ms": (c_int, [c_int]),
     "dice_ep_return_rows_following": (
         c_int,
         [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_uint32, c_int,

@@ -46,6 +46,10 @@ namespace {
 constexpr int kMaxRanks = 16;
 constexpr int kMaxKeys = 64;  // experts
 constexpr uint64_t kPeerWaitLimitNs = 2000ull * 1000ull * 1000ull;
+// How long a kernel waits for another rank (a flag) or for the GEMM it follows (block counters) before it records
+// the expired wait and returns: 2 s unless dice_ep_set_wait_limit_ms() changed it on this device.  Ranks that drift
+// apart by more than this between two exchanges (one of them stalled on the host) fail instead of waiting.
+__device__ unsigned long long g_peer_wait_limit_ns = kPeerWaitLimitNs;
 
 struct PeerTable {
   void* ptr[kMaxRanks];
@@ -76,11 +80,12 @@ constexpr int kStateNoCounts = 2;
 // true when *flag reached `seq` within the time limit
 __device__ bool wait_flag(const uint32_t* flag, uint32_t seq, uint32_t* status, uint32_t code) {
   const uint64_t t0 = timer_ns();
+  const uint64_t limit = g_peer_wait_limit_ns;
   uint32_t spins = 0;
   for (;;) {
     if (static_cast<int32_t>(ld_acquire_sys(flag) - seq) >= 0) return true;
     if ((++spins & 63u) == 0) {
-      if (timer_ns() - t0 > kPeerWaitLimitNs) {
+      if (timer_ns() - t0 > limit) {
         if (status != nullptr) atomicCAS(status, 0u, code);
         return false;
       }
@@ -655,6 +660,7 @@ ep_return_bulk_kernel(const uint8_t* __restrict__ rows, const int* __restrict__ 
   auto wait_for_block = [&](int need) -> bool {  // all lanes of the warp
     if (need >= s_fnblk || need >= follow.n_ints) return false;
     const uint64_t t0 = timer_ns();
+    const uint64_t limit = g_peer_wait_limit_ns;
     uint32_t spins = 0;
     while (ready_upto <= need) {
       const int b = ready_upto + lane;
@@ -669,7 +675,7 @@ ep_return_bulk_kernel(const uint8_t* __restrict__ rows, const int* __restrict__ 
       ready_upto += run;
       if (run == 0) {
         if ((++spins & 15u) == 0) {  // lane 0's clock decides for the warp
-          const int expired = timer_ns() - t0 > kPeerWaitLimitNs ? 1 : 0;
+          const int expired = timer_ns() - t0 > limit ? 1 : 0;
           if (__shfl_sync(0xffffffffu, expired, 0) != 0) return false;
         }
         __nanosleep(200);
@@ -1083,6 +1089,13 @@ extern "C" __attribute__((visibility("default"))) int dice_debug_push_trace(unsi
   return n;
 }
 #endif
+
+extern "C" int dice_ep_set_wait_limit_ms(int milliseconds) {
+  DICE_CHECK_ARG(milliseconds >= 100 && milliseconds <= 3600 * 1000, DICE_ERR_ARG);
+  const unsigned long long ns = static_cast<unsigned long long>(milliseconds) * 1000ull * 1000ull;
+  DICE_CUDA_OK(cudaMemcpyToSymbol(g_peer_wait_limit_ns, &ns, sizeof(ns)));  // the current device's copy
+  return DICE_OK;
+}
 
 // ---- CUDA IPC plumbing (set-up time only) ---------------------------------------------------
 extern "C" int dice_ipc_export(const void* ptr, uint8_t* out_handle64, uint64_t* out_offset) {

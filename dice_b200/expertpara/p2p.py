@@ -166,6 +166,11 @@ class PeerExchange:
         if self.dtype == torch.bfloat16 and len(self.seg_slab) <= 256 and bulk:  # (the push follows in its bulk form)
             self.rows_done = torch.zeros(self.capacity_rows // 256 + len(self.seg_slab) + 1, dtype=torch.int32,
                                          device=self.device)
+        wait_ms = int(os.environ.get("DICE_EP_P2P_WAIT_MS", "0"))
+        if wait_ms:  # how long a kernel waits for another rank before it gives up (2000 ms by default)
+            from .._lib import check
+
+            check(self.lib.dice_ep_set_wait_limit_ms(wait_ms), "dice_ep_set_wait_limit_ms")
         self._fork = torch.cuda.Event()
         self._fork.record()  # torch creates the CUDA event at its first record; the C side is handed its handle
         self._side_events = [torch.cuda.Event() for _ in range(2 * n_slots)]

@@ -379,6 +379,13 @@ DICE_API int dice_ep_dispatch_rows(const void* x, const int32_t* pos, const int3
 DICE_API int dice_ep_wait_dispatch(const uint32_t* my_flags, const int32_t* my_matrix, int32_t* meta, int rank,
                           int world, int n_experts, int region_rows, uint32_t seq, uint32_t* status,
                           void* stream);
+/* How long the exchange kernels of the CURRENT device wait for another rank (or,
+ * in dice_ep_return_rows_following, for the GEMM) before they record the
+ * expired wait and return: 2000 ms by default, 100 ms .. 1 h accepted.  The
+ * reference's collectives wait for as long as the process group's timeout
+ * (ep_fwd.py:277-291 via torch.distributed); raise the limit where ranks may
+ * stall for seconds between two exchanges. */
+DICE_API int dice_ep_set_wait_limit_ms(int milliseconds);
 /* wait (bounded) until every source raised flag >= seq, then look at the
  * sources' failure marks; what: 0 dispatch, 1 combine; + 2: the kernel is
  * launched in plain stream order (it, and what follows it in the stream, does

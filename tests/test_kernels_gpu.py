@@ -369,6 +369,32 @@ def test_exchange_wait_runs_out_and_reports(cuda_device):
     assert int((flags + 1).sum()) == 48
 
 
+def test_exchange_wait_limit_is_configurable(cuda_device):
+    """dice_ep_set_wait_limit_ms: the bounded waits of the exchange kernels follow the limit set for the device
+    (ranks that may stall for seconds between two exchanges need more than the default 2 s)."""
+    import time
+
+    from dice_b200 import _lib
+
+    ops = _ops()
+    lib = _lib.load()
+    assert lib.dice_ep_set_wait_limit_ms(50) != 0 and lib.dice_ep_set_wait_limit_ms(4 * 3600 * 1000) != 0  # out of range
+    flags = torch.zeros(8, dtype=torch.int32, device=cuda_device)
+    status = torch.zeros(1, dtype=torch.int32, device=cuda_device)
+    st = torch.cuda.current_stream().cuda_stream
+    try:
+        assert lib.dice_ep_set_wait_limit_ms(300) == 0
+        torch.cuda.synchronize()
+        t0 = time.time()
+        assert lib.dice_ep_wait_flags(flags.data_ptr(), 2, 1, 1, status.data_ptr(), st) == 0
+        torch.cuda.synchronize()
+        assert 0.25 < time.time() - t0 < 1.5
+        with pytest.raises(RuntimeError, match="expert outputs"):
+            ops.check_status(status)
+    finally:
+        assert lib.dice_ep_set_wait_limit_ms(2000) == 0
+
+
 def test_exchange_world_of_one(cuda_device):
     """The four exchange kernels on one GPU (world of one rank: every 'peer' is
     the rank itself): dispatch + return reproduce the plain permutation."""
