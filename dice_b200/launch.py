@@ -70,6 +70,10 @@ def install(reference_root: str | None = None):
     if os.environ.get("DICE_EP_P2P", "1") != "0":
         from .expertpara import p2p
 
+        # a sampling script's ranks may stall for seconds between two model calls (saving images, logging):
+        # the exchange kernels wait 30 s for a peer here instead of their 2 s default (the reference's
+        # collectives wait for the process group's timeout)
+        os.environ.setdefault("DICE_EP_P2P_WAIT_MS", "30000")
         p2p.enable(True)
     return models
 
